@@ -1,0 +1,416 @@
+// Bandwidth-bound kernels of the training step: RMSNorm forward/backward, fused
+// cross-entropy (loss + logit gradient in one pass), gradient norm, fused AdamW
+// over flat buffers, casts and the embedding gather.  Each replaces a chain of
+// eager PyTorch kernels in the reference (src/llmlab/model/layers.py:133-141,
+// src/llmlab/training/loss.py:4-22, src/llmlab/train.py:77-79) with one pass
+// over HBM.  All math is fp32; reductions are tree-shaped and order-fixed so the
+// results are bitwise reproducible from run to run.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+#include "sfl.h"
+
+namespace sfl {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum; result valid in every thread.  `scratch` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < (blockDim.x >> 5) ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < (blockDim.x >> 5) ? scratch[lane] : -INFINITY;
+    t = warp_max(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+// ---------------------------------------------------------------- RMSNorm ---
+// One warp per row.
+__global__ void rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                   __nv_bfloat16* __restrict__ y, float* __restrict__ rstd,
+                                   int rows, int dim, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const float* xr = x + static_cast<long>(row) * dim;
+  __nv_bfloat16* yr = y + static_cast<long>(row) * dim;
+  float ss = 0.f;
+  if ((dim & 3) == 0) {
+    for (int i = lane * 4; i < dim; i += 128) {
+      const float4 v = *reinterpret_cast<const float4*>(xr + i);
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+  } else {
+    for (int i = lane; i < dim; i += 32) ss += xr[i] * xr[i];
+  }
+  ss = warp_sum(ss);
+  // Same operation order as the reference: x / sqrt(mean + eps) * w.
+  const float rms = sqrtf(ss / static_cast<float>(dim) + eps);
+  const float inv = 1.0f / rms;
+  if (lane == 0 && rstd != nullptr) rstd[row] = inv;
+  if ((dim & 3) == 0) {
+    for (int i = lane * 4; i < dim; i += 128) {
+      const float4 v = *reinterpret_cast<const float4*>(xr + i);
+      const float4 g = *reinterpret_cast<const float4*>(w + i);
+      uint2 o;
+      o.x = pack_bf16(v.x / rms * g.x, v.y / rms * g.y);
+      o.y = pack_bf16(v.z / rms * g.z, v.w / rms * g.w);
+      *reinterpret_cast<uint2*>(yr + i) = o;
+    }
+  } else {
+    for (int i = lane; i < dim; i += 32) yr[i] = __float2bfloat16_rn(xr[i] / rms * w[i]);
+  }
+}
+
+constexpr int kNormBwdBlocks = 296;  // two CTAs per SM on a 148-SM part
+constexpr int kNormBwdThreads = 256;
+
+// Each block owns a strided set of rows (one warp per row at a time) and keeps a
+// per-thread partial of dw for the columns it touches; partials are combined
+// across the block's warps in shared memory in a fixed order.
+__global__ void __launch_bounds__(kNormBwdThreads)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const float* __restrict__ x,
+                   const float* __restrict__ w, const float* __restrict__ rstd,
+                   const float* __restrict__ dres_in, float* __restrict__ dx_out,
+                   __nv_bfloat16* __restrict__ dx_bf16, float* __restrict__ dw_partial, int rows,
+                   int dim) {
+  extern __shared__ float dw_smem[];  // [warps, dim]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps = blockDim.x >> 5;
+  float* my_dw = dw_smem + static_cast<long>(warp) * dim;
+  for (int i = lane; i < dim; i += 32) my_dw[i] = 0.f;
+  __syncwarp();
+  for (int row = blockIdx.x * warps + warp; row < rows; row += gridDim.x * warps) {
+    const long off = static_cast<long>(row) * dim;
+    const float inv = rstd[row];
+    float dot = 0.f;
+    for (int i = lane; i < dim; i += 32) {
+      const float g = __bfloat162float(dy[off + i]) * w[i];
+      dot += g * x[off + i] * inv;
+    }
+    dot = warp_sum(dot) / static_cast<float>(dim);
+    for (int i = lane; i < dim; i += 32) {
+      const float dyi = __bfloat162float(dy[off + i]);
+      const float xhat = x[off + i] * inv;
+      float dxi = inv * (dyi * w[i] - xhat * dot);
+      if (dres_in != nullptr) dxi += dres_in[off + i];
+      dx_out[off + i] = dxi;
+      if (dx_bf16 != nullptr) dx_bf16[off + i] = __float2bfloat16_rn(dxi);
+      my_dw[i] += dyi * xhat;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    float s = 0.f;
+    for (int k = 0; k < warps; ++k) s += dw_smem[static_cast<long>(k) * dim + i];
+    dw_partial[static_cast<long>(blockIdx.x) * dim + i] = s;
+  }
+}
+
+__global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, int blocks,
+                                         float* __restrict__ dw, int dim, int accumulate) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= dim) return;
+  float s = 0.f;
+  for (int b = 0; b < blocks; ++b) s += partial[static_cast<long>(b) * dim + i];
+  dw[i] = accumulate ? dw[i] + s : s;
+}
+
+// ---------------------------------------------------------- cross entropy ---
+// One CTA per row.  The row (vocab * 2 bytes) is read twice from L1/L2 and the
+// gradient written once; logits never exist in fp32 in memory.
+__global__ void __launch_bounds__(256)
+cross_entropy_kernel(const __nv_bfloat16* __restrict__ logits, long ld,
+                     const int64_t* __restrict__ targets, float* __restrict__ row_loss,
+                     __nv_bfloat16* __restrict__ dlogits, float grad_scale, int vocab) {
+  __shared__ float scratch[33];
+  const int row = blockIdx.x;
+  const __nv_bfloat16* lr = logits + static_cast<long>(row) * ld;
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) mx = fmaxf(mx, __bfloat162float(lr[i]));
+  mx = block_max(mx, scratch);
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) sum += expf(__bfloat162float(lr[i]) - mx);
+  sum = block_sum(sum, scratch);
+  const int64_t tgt = targets[row];
+  if (threadIdx.x == 0) {
+    const float tl = (tgt >= 0 && tgt < vocab) ? __bfloat162float(lr[tgt]) - mx : 0.f;
+    row_loss[row] = logf(sum) - tl;
+  }
+  if (dlogits != nullptr) {
+    __nv_bfloat16* dr = dlogits + static_cast<long>(row) * ld;
+    const float inv = 1.0f / sum;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      float p = expf(__bfloat162float(lr[i]) - mx) * inv;
+      if (i == tgt) p -= 1.0f;
+      dr[i] = __float2bfloat16_rn(p * grad_scale);
+    }
+  }
+}
+
+// -------------------------------------------------------------- optimizer ---
+constexpr int kSqnormThreads = 512;
+constexpr long kSqnormChunk = 1 << 16;  // elements per block
+
+__global__ void __launch_bounds__(kSqnormThreads)
+sqnorm_partial_kernel(const float* __restrict__ x, long n, float* __restrict__ partial) {
+  __shared__ float scratch[33];
+  const long begin = static_cast<long>(blockIdx.x) * kSqnormChunk;
+  const long end = begin + kSqnormChunk < n ? begin + kSqnormChunk : n;
+  float s = 0.f;
+  // begin is a multiple of 4 elements, so float4 loads are aligned when x is.
+  const long vec_end = begin + ((end - begin) & ~3L);
+  if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    for (long i = begin + threadIdx.x * 4L; i < vec_end; i += kSqnormThreads * 4L) {
+      const float4 v = *reinterpret_cast<const float4*>(x + i);
+      s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    for (long i = vec_end + threadIdx.x; i < end; i += kSqnormThreads) s += x[i] * x[i];
+  } else {
+    for (long i = begin + threadIdx.x; i < end; i += kSqnormThreads) s += x[i] * x[i];
+  }
+  s = block_sum(s, scratch);
+  if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+
+__global__ void norm_finalize_kernel(const float* __restrict__ partial, int n, float sum_scale,
+                                     float max_norm, float* __restrict__ out) {
+  __shared__ float scratch[33];
+  // Double accumulation in a fixed order keeps the total independent of n's split.
+  double s = 0.0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) s += static_cast<double>(partial[i]);
+  __shared__ double dsum[256];
+  dsum[threadIdx.x] = s;
+  __syncthreads();
+  for (int o = blockDim.x >> 1; o > 0; o >>= 1) {
+    if (threadIdx.x < o) dsum[threadIdx.x] += dsum[threadIdx.x + o];
+    __syncthreads();
+  }
+  (void)scratch;
+  if (threadIdx.x == 0) {
+    const float norm = sqrtf(static_cast<float>(dsum[0] * static_cast<double>(sum_scale)));
+    out[0] = norm;
+    const float coef = max_norm / (norm + 1e-6f);
+    out[1] = coef < 1.0f ? coef : 1.0f;
+    out[2] = isfinite(norm) ? 1.0f : 0.0f;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
+             float* __restrict__ v, __nv_bfloat16* __restrict__ shadow, long n, float lr,
+             float beta1, float beta2, float eps, float wd, float bias1, float bias2_sqrt,
+             const float* __restrict__ grad_coef, float grad_scale,
+             const float* __restrict__ ok_flag) {
+  if (ok_flag != nullptr && *ok_flag == 0.0f) return;
+  const float coef = grad_coef != nullptr ? *grad_coef : 1.0f;
+  const float step_size = lr / bias1;
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    // Same operation order as torch.optim.AdamW (single-tensor path).
+    float gi = g[i];
+    if (grad_scale != 1.0f) gi *= grad_scale;
+    if (grad_coef != nullptr) gi *= coef;
+    float pi = p[i] * (1.0f - lr * wd);
+    float mi = m[i];
+    mi = mi + (gi - mi) * (1.0f - beta1);
+    float vi = v[i] * beta2 + (1.0f - beta2) * gi * gi;
+    const float denom = sqrtf(vi) / bias2_sqrt + eps;
+    pi = pi - step_size * (mi / denom);
+    p[i] = pi;
+    m[i] = mi;
+    v[i] = vi;
+    if (shadow != nullptr) shadow[i] = __float2bfloat16_rn(pi);
+  }
+}
+
+// ------------------------------------------------------------------- misc ---
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y,
+                                     long n) {
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  const long i0 = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(x) & 15) | (reinterpret_cast<uintptr_t>(y) & 7)) == 0;
+  if (aligned) {
+    const long n4 = n >> 2;
+    for (long i = i0; i < n4; i += stride) {
+      const float4 v = reinterpret_cast<const float4*>(x)[i];
+      uint2 o;
+      o.x = pack_bf16(v.x, v.y);
+      o.y = pack_bf16(v.z, v.w);
+      reinterpret_cast<uint2*>(y)[i] = o;
+    }
+    for (long i = (n4 << 2) + i0; i < n; i += stride) y[i] = __float2bfloat16_rn(x[i]);
+  } else {
+    for (long i = i0; i < n; i += stride) y[i] = __float2bfloat16_rn(x[i]);
+  }
+}
+
+__global__ void scale_f32_kernel(float* __restrict__ x, long n, const float* __restrict__ coef,
+                                 float scale) {
+  const float c = (coef != nullptr ? *coef : 1.0f) * scale;
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+    x[i] *= c;
+}
+
+__global__ void embedding_fwd_kernel(const float* __restrict__ weight,
+                                     const int64_t* __restrict__ ids, float* __restrict__ out,
+                                     int rows, int dim, int vocab) {
+  const int row = blockIdx.x;
+  int64_t id = ids[row];
+  if (id < 0 || id >= vocab) id = 0;  // validated on the host; never index out of range
+  const float* src = weight + id * dim;
+  float* dst = out + static_cast<long>(row) * dim;
+  if ((dim & 3) == 0) {
+    for (int i = threadIdx.x * 4; i < dim; i += blockDim.x * 4)
+      *reinterpret_cast<float4*>(dst + i) = *reinterpret_cast<const float4*>(src + i);
+  } else {
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+inline int grid_for(long n, int threads, int cap = 148 * 8) {
+  long blocks = (n + threads - 1) / threads;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return static_cast<int>(blocks);
+}
+
+}  // namespace sfl
+
+using namespace sfl;
+#define SFL_STREAM(s) static_cast<cudaStream_t>(s)
+#define SFL_RET() return static_cast<int>(cudaGetLastError())
+
+extern "C" int sfl_rmsnorm_fwd(const float* x, const float* w, void* y, float* rstd, int rows,
+                               int dim, float eps, void* stream) {
+  if (rows <= 0 || dim <= 0) return -2;
+  const int warps = 8;
+  rmsnorm_fwd_kernel<<<(rows + warps - 1) / warps, warps * 32, 0, SFL_STREAM(stream)>>>(
+      x, w, static_cast<__nv_bfloat16*>(y), rstd, rows, dim, eps);
+  SFL_RET();
+}
+
+extern "C" int sfl_rmsnorm_bwd_blocks(int rows) {
+  const int warps = kNormBwdThreads / 32;
+  const int need = (rows + warps - 1) / warps;
+  return need < kNormBwdBlocks ? (need < 1 ? 1 : need) : kNormBwdBlocks;
+}
+
+extern "C" int sfl_rmsnorm_bwd(const void* dy, const float* x, const float* w, const float* rstd,
+                               const float* dres_in, float* dx_out, void* dx_bf16,
+                               float* dw_partial, int rows, int dim, void* stream) {
+  if (rows <= 0 || dim <= 0) return -2;
+  const int blocks = sfl_rmsnorm_bwd_blocks(rows);
+  const size_t smem = static_cast<size_t>(kNormBwdThreads / 32) * dim * sizeof(float);
+  if (smem > 200 * 1024) return -2;
+  static bool configured = false;
+  if (!configured && smem > 48 * 1024) {
+    cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         200 * 1024);
+    configured = true;
+  }
+  rmsnorm_bwd_kernel<<<blocks, kNormBwdThreads, smem, SFL_STREAM(stream)>>>(
+      static_cast<const __nv_bfloat16*>(dy), x, w, rstd, dres_in, dx_out,
+      static_cast<__nv_bfloat16*>(dx_bf16), dw_partial, rows, dim);
+  SFL_RET();
+}
+
+extern "C" int sfl_rmsnorm_dw_reduce(const float* partial, int blocks, float* dw, int dim,
+                                     int accumulate, void* stream) {
+  rmsnorm_dw_reduce_kernel<<<(dim + 127) / 128, 128, 0, SFL_STREAM(stream)>>>(partial, blocks, dw,
+                                                                             dim, accumulate);
+  SFL_RET();
+}
+
+extern "C" int sfl_cross_entropy(const void* logits, long ld, const int64_t* targets,
+                                 float* row_loss, void* dlogits, float grad_scale, int rows,
+                                 int vocab, void* stream) {
+  if (rows <= 0 || vocab <= 0) return -2;
+  cross_entropy_kernel<<<rows, 256, 0, SFL_STREAM(stream)>>>(
+      static_cast<const __nv_bfloat16*>(logits), ld, targets, row_loss,
+      static_cast<__nv_bfloat16*>(dlogits), grad_scale, vocab);
+  SFL_RET();
+}
+
+extern "C" int sfl_sqnorm_blocks(long n) {
+  return static_cast<int>((n + kSqnormChunk - 1) / kSqnormChunk);
+}
+
+extern "C" int sfl_sqnorm_partial(const float* x, long n, float* partial, void* stream) {
+  if (n <= 0) return -2;
+  sqnorm_partial_kernel<<<sfl_sqnorm_blocks(n), kSqnormThreads, 0, SFL_STREAM(stream)>>>(x, n,
+                                                                                       partial);
+  SFL_RET();
+}
+
+extern "C" int sfl_norm_finalize(const float* partial, int n, float sum_scale, float max_norm,
+                                 float* out, void* stream) {
+  norm_finalize_kernel<<<1, 256, 0, SFL_STREAM(stream)>>>(partial, n, sum_scale, max_norm, out);
+  SFL_RET();
+}
+
+extern "C" int sfl_adamw(float* p, const float* g, float* m, float* v, void* shadow, long n,
+                         float lr, float beta1, float beta2, float eps, float wd, float bias1,
+                         float bias2, const float* grad_coef, float grad_scale,
+                         const float* ok_flag, void* stream) {
+  if (n <= 0) return 0;
+  adamw_kernel<<<grid_for(n, 256, 148 * 16), 256, 0, SFL_STREAM(stream)>>>(
+      p, g, m, v, static_cast<__nv_bfloat16*>(shadow), n, lr, beta1, beta2, eps, wd, bias1,
+      sqrtf(bias2), grad_coef, grad_scale, ok_flag);
+  SFL_RET();
+}
+
+extern "C" int sfl_cast_f32_to_bf16(const float* x, void* y, long n, void* stream) {
+  if (n <= 0) return 0;
+  cast_f32_bf16_kernel<<<grid_for((n + 3) / 4, 256), 256, 0, SFL_STREAM(stream)>>>(
+      x, static_cast<__nv_bfloat16*>(y), n);
+  SFL_RET();
+}
+
+extern "C" int sfl_scale_f32(float* x, long n, const float* coef, float scale, void* stream) {
+  if (n <= 0) return 0;
+  scale_f32_kernel<<<grid_for(n, 256), 256, 0, SFL_STREAM(stream)>>>(x, n, coef, scale);
+  SFL_RET();
+}
+
+extern "C" int sfl_embedding_fwd(const float* weight, const int64_t* ids, float* out, int rows,
+                                 int dim, int vocab, void* stream) {
+  if (rows <= 0) return -2;
+  embedding_fwd_kernel<<<rows, 128, 0, SFL_STREAM(stream)>>>(weight, ids, out, rows, dim, vocab);
+  SFL_RET();
+}
+
+extern "C" const char* sfl_version(void) { return "sfl_b200 sm_100a"; }

@@ -1,0 +1,618 @@
+// Persistent warp-specialised bf16 GEMM for sm_100a.
+//
+//   D[M,N] = A[M,K] * B[N,K]^T      (fp32 accumulation in tensor memory)
+//
+// One CTA per SM walks output tiles of 128 x BN.  Warp 0 streams operand tiles
+// into a shared-memory ring with TMA, warp 1 issues tcgen05.mma into one of two
+// TMEM accumulator stages, warps 2-5 drain the other stage through a fused
+// epilogue, so the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Either operand may be "K-major" (reduction dimension contiguous in memory) or
+// "MN-major" (the M/N dimension contiguous), which lets one kernel serve the
+// forward (x W^T), input-gradient (dy W) and weight-gradient (dy^T x) products
+// of a linear layer without transposing anything in memory.  The reference
+// computes these through einsum/cuBLAS (src/llmlab/model/layers.py:35).
+//
+// Fused epilogues replace the reference's separate elementwise kernels:
+//   EPI_BF16        plain bf16 store
+//   EPI_F32         fp32 store or accumulate (weight gradients, beta in {0,1})
+//   EPI_RESID       fp32 residual stream update  out = resid + bf16(acc)
+//                   (src/llmlab/model/transformer.py:46-47)
+//   EPI_ROPE        bf16 store of a fused q|k|v projection with interleaved-pair
+//                   rotary embedding on the q and k columns
+//                   (src/llmlab/model/attention.py:44-58)
+//   EPI_SWIGLU      dual accumulator (w1 x | w3 x): stores both and
+//                   silu(w1 x) * w3 x   (src/llmlab/model/layers.py:114-115)
+//   EPI_SWIGLU_BWD  acc = d(silu(a1)*a3); stores d a1 | d a3
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "ptx.cuh"
+#include "sfl.h"
+#include "tensormap.cuh"
+
+namespace sfl {
+
+enum Epilogue : int {
+  EPI_BF16 = 0,
+  EPI_F32 = 1,
+  EPI_RESID = 2,
+  EPI_ROPE = 3,
+  EPI_SWIGLU = 4,
+  EPI_SWIGLU_BWD = 5,
+};
+
+struct GemmParams {
+  int M, N, K;
+  int num_m_tiles, num_n_tiles;
+  void* out;
+  long ldo;
+  void* out2;
+  long ldo2;
+  const void* aux;
+  long ldaux;
+  int beta;
+  // rotary embedding
+  const float* rope_cos;  // [T, head_dim/2]
+  const float* rope_sin;
+  int rope_T;        // sequence length: position = row % rope_T
+  int rope_cols;     // columns [0, rope_cols) are rotated (q and k)
+  int head_dim;
+  // SwiGLU
+  int dual_offset;   // row offset of the second weight matrix inside B
+  int* status;
+};
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int kThreads = 192;
+constexpr int kTileABytes = BM * BK * 2;
+
+template <int BN>
+struct GemmConfig {
+  static constexpr int kTileBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kTileABytes + kTileBBytes;
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+struct __align__(8) GemmBarriers {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort;
+};
+
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort) {
+  for (uint32_t spin = 0; spin < (1u << 23); ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (spin > 2048) {
+      __nanosleep(256);
+      if (*abort) return false;
+    }
+  }
+  return false;
+}
+
+// ------------------------------------------------------------- epilogues ----
+template <int EPI>
+struct EpilogueOp;
+
+__device__ __forceinline__ void store_bf16_row(__nv_bfloat16* dst, const float (&v)[32], int col0,
+                                               int N, bool vec_ok) {
+  if (vec_ok && col0 + 32 <= N) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint4 q;
+      q.x = pack_bf16(v[8 * j + 0], v[8 * j + 1]);
+      q.y = pack_bf16(v[8 * j + 2], v[8 * j + 3]);
+      q.z = pack_bf16(v[8 * j + 4], v[8 * j + 5]);
+      q.w = pack_bf16(v[8 * j + 6], v[8 * j + 7]);
+      *reinterpret_cast<uint4*>(dst + 8 * j) = q;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < N) dst[j] = __float2bfloat16_rn(v[j]);
+  }
+}
+
+template <>
+struct EpilogueOp<EPI_BF16> {
+  static __device__ __forceinline__ void apply(const GemmParams& p, int row, int col0,
+                                               float (&v)[32], float (&)[32]) {
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + static_cast<long>(row) * p.ldo + col0;
+    store_bf16_row(dst, v, col0, p.N, (p.ldo & 7) == 0);
+  }
+};
+
+template <>
+struct EpilogueOp<EPI_F32> {
+  static __device__ __forceinline__ void apply(const GemmParams& p, int row, int col0,
+                                               float (&v)[32], float (&)[32]) {
+    float* dst = static_cast<float*>(p.out) + static_cast<long>(row) * p.ldo + col0;
+    if ((p.ldo & 3) == 0 && col0 + 32 <= p.N) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float4 q = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        if (p.beta) {
+          float4 o = *reinterpret_cast<const float4*>(dst + 4 * j);
+          q.x += o.x; q.y += o.y; q.z += o.z; q.w += o.w;
+        }
+        *reinterpret_cast<float4*>(dst + 4 * j) = q;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) dst[j] = p.beta ? dst[j] + v[j] : v[j];
+    }
+  }
+};
+
+template <>
+struct EpilogueOp<EPI_RESID> {
+  static __device__ __forceinline__ void apply(const GemmParams& p, int row, int col0,
+                                               float (&v)[32], float (&)[32]) {
+    float* dst = static_cast<float*>(p.out) + static_cast<long>(row) * p.ldo + col0;
+    const float* res = static_cast<const float*>(p.aux) + static_cast<long>(row) * p.ldaux + col0;
+    if ((p.ldo & 3) == 0 && (p.ldaux & 3) == 0 && col0 + 32 <= p.N) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float4 r = *reinterpret_cast<const float4*>(res + 4 * j);
+        r.x += bf16_round(v[4 * j]);
+        r.y += bf16_round(v[4 * j + 1]);
+        r.z += bf16_round(v[4 * j + 2]);
+        r.w += bf16_round(v[4 * j + 3]);
+        *reinterpret_cast<float4*>(dst + 4 * j) = r;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) dst[j] = res[j] + bf16_round(v[j]);
+    }
+  }
+};
+
+template <>
+struct EpilogueOp<EPI_ROPE> {
+  static __device__ __forceinline__ void apply(const GemmParams& p, int row, int col0,
+                                               float (&v)[32], float (&)[32]) {
+    if (col0 < p.rope_cols) {
+      // A 32-column chunk never straddles a head because head_dim is a multiple
+      // of 32 here (checked on the host); pairs (2i, 2i+1) are rotated together.
+      const int pos = row % p.rope_T;
+      const int half = p.head_dim >> 1;
+      const int pair0 = (col0 % p.head_dim) >> 1;
+      const float* cs = p.rope_cos + static_cast<long>(pos) * half + pair0;
+      const float* sn = p.rope_sin + static_cast<long>(pos) * half + pair0;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        // The projection output is bf16 before the rotation, as in the reference.
+        const float xe = bf16_round(v[2 * j]);
+        const float xo = bf16_round(v[2 * j + 1]);
+        const float c = cs[j];
+        const float s = sn[j];
+        v[2 * j] = xe * c - xo * s;
+        v[2 * j + 1] = xe * s + xo * c;
+      }
+    }
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + static_cast<long>(row) * p.ldo + col0;
+    store_bf16_row(dst, v, col0, p.N, (p.ldo & 7) == 0);
+  }
+};
+
+template <>
+struct EpilogueOp<EPI_SWIGLU> {
+  // v = w1 x chunk, w = w3 x chunk (same columns)
+  static __device__ __forceinline__ void apply(const GemmParams& p, int row, int col0,
+                                               float (&v)[32], float (&w)[32]) {
+    __nv_bfloat16* a13 = static_cast<__nv_bfloat16*>(p.out2) + static_cast<long>(row) * p.ldo2;
+    const bool vec2 = (p.ldo2 & 7) == 0 && (p.N & 7) == 0;
+    store_bf16_row(a13 + col0, v, col0, p.N, vec2);
+    store_bf16_row(a13 + p.N + col0, w, col0, p.N, vec2);
+    float g[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float a = bf16_round(v[j]);
+      const float b = bf16_round(w[j]);
+      g[j] = a / (1.0f + __expf(-a)) * b;
+    }
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + static_cast<long>(row) * p.ldo + col0;
+    store_bf16_row(dst, g, col0, p.N, (p.ldo & 7) == 0);
+  }
+};
+
+template <>
+struct EpilogueOp<EPI_SWIGLU_BWD> {
+  static __device__ __forceinline__ void apply(const GemmParams& p, int row, int col0,
+                                               float (&v)[32], float (&)[32]) {
+    const __nv_bfloat16* a13 =
+        static_cast<const __nv_bfloat16*>(p.aux) + static_cast<long>(row) * p.ldaux;
+    float d1[32], d3[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (col0 + j < p.N) {
+        const float a = __bfloat162float(a13[col0 + j]);
+        const float b = __bfloat162float(a13[p.N + col0 + j]);
+        const float dg = bf16_round(v[j]);
+        const float sig = 1.0f / (1.0f + __expf(-a));
+        const float silu = a * sig;
+        d3[j] = dg * silu;
+        d1[j] = dg * b * (sig + silu * (1.0f - sig));
+      } else {
+        d1[j] = 0.f;
+        d3[j] = 0.f;
+      }
+    }
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + static_cast<long>(row) * p.ldo;
+    const bool vec = (p.ldo & 7) == 0 && (p.N & 7) == 0;
+    store_bf16_row(dst + col0, d1, col0, p.N, vec);
+    store_bf16_row(dst + p.N + col0, d3, col0, p.N, vec);
+  }
+};
+
+// ---------------------------------------------------------------- kernel ----
+template <int BN, bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const GemmParams p) {
+  using Cfg = GemmConfig<BN>;
+  constexpr bool kDual = (EPI == EPI_SWIGLU);
+  // In dual mode the logical N tile is BN/2 wide: the B tile stacks BN/2 rows of
+  // the first matrix on BN/2 rows of the second.
+  constexpr int BN_OUT = kDual ? BN / 2 : BN;
+  static_assert(!(kDual && B_MN), "dual epilogue expects K-major weights");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(smem + Cfg::kStages * Cfg::kStageBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->tmem_full[s], 1);
+      mbar_init(&bars->tmem_empty[s], 128);
+    }
+    bars->abort = 0;
+    mbar_fence_init();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+  volatile int* abort = &bars->abort;
+
+  if (warp == 0) {
+    // ------------------------------------------------------ TMA producer ----
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % p.num_m_tiles) * BM;
+        const int n0 = (tile / p.num_m_tiles) * BN_OUT;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!wait_or_abort(&bars->empty[stage], phase ^ 1, abort)) {
+            report_status(p.status, kStatusTimeoutEmpty);
+            *abort = 1;
+            ok = false;
+            break;
+          }
+          uint8_t* sA = smem + stage * Cfg::kStageBytes;
+          uint8_t* sB = sA + kTileABytes;
+          mbar_expect_tx(&bars->full[stage], Cfg::kStageBytes);
+          const int k0 = kb * BK;
+          if constexpr (A_MN) {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i)
+              tma_load_2d(sA + i * (BK * 128), &tmA, &bars->full[stage], m0 + i * 64, k0);
+          } else {
+            tma_load_2d(sA, &tmA, &bars->full[stage], k0, m0);
+          }
+          if constexpr (B_MN) {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i)
+              tma_load_2d(sB + i * (BK * 128), &tmB, &bars->full[stage], n0 + i * 64, k0);
+          } else if constexpr (kDual) {
+            tma_load_2d(sB, &tmB, &bars->full[stage], k0, n0);
+            tma_load_2d(sB + (BN / 2) * 128, &tmB, &bars->full[stage], k0, p.dual_offset + n0);
+          } else {
+            tma_load_2d(sB, &tmB, &bars->full[stage], k0, n0);
+          }
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------- MMA issuer ----
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!wait_or_abort(&bars->tmem_empty[acc], acc_phase ^ 1, abort)) {
+          report_status(p.status, kStatusTimeoutTmemEmpty);
+          *abort = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!wait_or_abort(&bars->full[stage], phase, abort)) {
+            report_status(p.status, kStatusTimeoutFull);
+            *abort = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint32_t b_addr = a_addr + kTileABytes;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t a_desc = A_MN ? umma_smem_desc(a_addr + k * 2048, BK * 128, 1024)
+                                         : umma_smem_desc(a_addr + k * 32, 16, 1024);
+            const uint64_t b_desc = B_MN ? umma_smem_desc(b_addr + k * 2048, BK * 128, 1024)
+                                         : umma_smem_desc(b_addr + k * 32, 16, 1024);
+            umma_bf16_ss(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0);
+          }
+          umma_commit(&bars->empty[stage]);
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&bars->tmem_full[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------- epilogue ----
+    const int quarter = warp & 3;  // TMEM lanes this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      const int m0 = (tile % p.num_m_tiles) * BM;
+      const int n0 = (tile / p.num_m_tiles) * BN_OUT;
+      if (!wait_or_abort(&bars->tmem_full[acc], acc_phase, abort)) {
+        report_status(p.status, kStatusTimeoutTmemFull);
+        *abort = 1;
+        break;
+      }
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN_OUT / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;  // warp-uniform
+        uint32_t r[32];
+        float v[32], w[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        if constexpr (kDual) {
+          uint32_t r2[32];
+          tmem_ld_32x32(t_row + BN / 2 + c * 32, r2);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) w[j] = __uint_as_float(r2[j]);
+        } else {
+          tmem_ld_wait();
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (row < p.M) EpilogueOp<EPI>::apply(p, row, col0, v, w);
+      }
+      tc_fence_before();
+      mbar_arrive(&bars->tmem_empty[acc]);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ host ----
+namespace {
+
+struct MapKey {
+  const void* base;
+  uint64_t inner, outer, ld;
+  uint32_t box_inner, box_outer;
+  bool operator<(const MapKey& o) const {
+    return std::tie(base, inner, outer, ld, box_inner, box_outer) <
+           std::tie(o.base, o.inner, o.outer, o.ld, o.box_inner, o.box_outer);
+  }
+};
+
+// Encoding a tensor map costs a few microseconds on the host; training reuses a
+// small set of (pointer, shape) combinations every step, so keep them.
+int cached_map(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+               uint32_t box_inner, uint32_t box_outer) {
+  static std::map<MapKey, CUtensorMap> cache;
+  static std::mutex mu;
+  MapKey key{base, inner, outer, ld, box_inner, box_outer};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return 0;
+  }
+  int rc = make_tensormap_2d_bf16(out, base, inner, outer, ld, box_inner, box_outer);
+  if (rc == 0) {
+    if (cache.size() > 8192) cache.clear();
+    cache.emplace(key, *out);
+  }
+  return rc;
+}
+
+int sm_count() {
+  static int count = 0;
+  if (count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
+    if (count <= 0) count = 148;
+  }
+  return count;
+}
+
+template <int BN, bool A_MN, bool B_MN, int EPI>
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int max_ctas,
+           cudaStream_t stream) {
+  using Cfg = GemmConfig<BN>;
+  auto kernel = gemm_kernel<BN, A_MN, B_MN, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  const int tiles = p.num_m_tiles * p.num_n_tiles;
+  int grid = tiles < sm_count() ? tiles : sm_count();
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  kernel<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <int BN, int EPI>
+int launch_major(bool a_mn, bool b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB,
+                 const GemmParams& p, int max_ctas, cudaStream_t stream) {
+  if constexpr (EPI == EPI_SWIGLU) {
+    if (a_mn || b_mn) return -3;
+    return launch<BN, false, false, EPI>(tmA, tmB, p, max_ctas, stream);
+  } else {
+    if (!a_mn && !b_mn) return launch<BN, false, false, EPI>(tmA, tmB, p, max_ctas, stream);
+    if (!a_mn && b_mn) return launch<BN, false, true, EPI>(tmA, tmB, p, max_ctas, stream);
+    if (a_mn && b_mn) return launch<BN, true, true, EPI>(tmA, tmB, p, max_ctas, stream);
+    return launch<BN, true, false, EPI>(tmA, tmB, p, max_ctas, stream);
+  }
+}
+
+}  // namespace
+}  // namespace sfl
+
+using namespace sfl;
+
+// a: K-major -> [M,K] row-major with pitch lda; MN-major -> [K,M] row-major.
+// b: K-major -> [N,K] row-major with pitch ldb; MN-major -> [K,N] row-major.
+extern "C" int sfl_gemm_bf16(const void* a, long lda, int a_mn, const void* b, long ldb, int b_mn,
+                             int M, int N, int K, const SflGemmEpilogue* epi, int bn_hint,
+                             int max_ctas, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0 || epi == nullptr) return -2;
+  if ((lda & 7) || (ldb & 7)) return -2;  // TMA needs 16-byte row pitches
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return -2;
+  const int kind = epi->kind;
+  const bool dual = kind == EPI_SWIGLU;
+
+  GemmParams p{};
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.out = epi->out;
+  p.ldo = epi->ldo;
+  p.out2 = epi->out2;
+  p.ldo2 = epi->ldo2;
+  p.aux = epi->aux;
+  p.ldaux = epi->ldaux;
+  p.beta = epi->beta;
+  p.rope_cos = epi->rope_cos;
+  p.rope_sin = epi->rope_sin;
+  p.rope_T = epi->rope_T;
+  p.rope_cols = epi->rope_cols;
+  p.head_dim = epi->head_dim;
+  p.dual_offset = epi->dual_offset;
+  p.status = epi->status;
+  if (kind == EPI_ROPE && (p.head_dim % 32 != 0 || p.rope_T <= 0)) return -2;
+
+  // Tile width: pick the one that needs the fewest "tile-time units" of waves.
+  int bn = bn_hint;
+  if (dual) {
+    bn = 256;  // 128 columns of each of the two products
+  } else if (bn != 128 && bn != 256) {
+    const int sms = sm_count();
+    const int mt = (M + BM - 1) / BM;
+    auto cost = [&](int width) {
+      const long tiles = static_cast<long>(mt) * ((N + width - 1) / width);
+      const long waves = (tiles + sms - 1) / sms;
+      return waves * width;
+    };
+    bn = cost(256) <= cost(128) ? 256 : 128;
+  }
+  const int bn_out = dual ? bn / 2 : bn;
+  p.num_m_tiles = (M + BM - 1) / BM;
+  p.num_n_tiles = (N + bn_out - 1) / bn_out;
+
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (a_mn)
+    rc = cached_map(&tmA, a, M, K, lda, 64, BK);
+  else
+    rc = cached_map(&tmA, a, K, M, lda, BK, BM);
+  if (rc) return 1000 + rc;
+  const uint64_t b_rows = dual ? static_cast<uint64_t>(epi->dual_rows) : static_cast<uint64_t>(N);
+  if (b_mn)
+    rc = cached_map(&tmB, b, N, K, ldb, 64, BK);
+  else
+    rc = cached_map(&tmB, b, K, b_rows, ldb, BK, dual ? bn / 2 : bn);
+  if (rc) return 1000 + rc;
+
+#define SFL_DISPATCH(EPI_)                                                                    \
+  case EPI_:                                                                                  \
+    return bn == 256 ? launch_major<256, EPI_>(a_mn, b_mn, tmA, tmB, p, max_ctas, stream)     \
+                     : launch_major<128, EPI_>(a_mn, b_mn, tmA, tmB, p, max_ctas, stream);
+  switch (kind) {
+    SFL_DISPATCH(EPI_BF16)
+    SFL_DISPATCH(EPI_F32)
+    SFL_DISPATCH(EPI_RESID)
+    SFL_DISPATCH(EPI_ROPE)
+    SFL_DISPATCH(EPI_SWIGLU_BWD)
+    case EPI_SWIGLU:
+      return launch_major<256, EPI_SWIGLU>(a_mn, b_mn, tmA, tmB, p, max_ctas, stream);
+    default:
+      return -2;
+  }
+#undef SFL_DISPATCH
+}

@@ -1,0 +1,103 @@
+/* C interface of the sm_100a kernel library (libsfl_b200.so).
+ *
+ * Every function takes raw device pointers plus the CUDA stream to launch on
+ * (as a void*, 0 = legacy default stream) and returns 0 on success.  Nothing
+ * here allocates device memory unless the function's comment says so; callers
+ * (the Python layer) own all buffers.  Kernels that can wait on something
+ * (pipelines, peer flags) bound their waits and report through an optional
+ * `int* status` device word: 0 = ok, see StatusCode in ptx.cuh.
+ */
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ GEMM -- */
+enum {
+  SFL_EPI_BF16 = 0,       /* out bf16 [M,N]                                         */
+  SFL_EPI_F32 = 1,        /* out fp32 [M,N]; beta=1 accumulates                     */
+  SFL_EPI_RESID = 2,      /* out fp32 = aux fp32 + bf16(acc)                        */
+  SFL_EPI_ROPE = 3,       /* out bf16, rotary embedding on columns [0, rope_cols)   */
+  SFL_EPI_SWIGLU = 4,     /* b = [w1; w3]; out = silu(a1)*a3, out2 = [a1 | a3]      */
+  SFL_EPI_SWIGLU_BWD = 5, /* acc = dg; aux = [a1 | a3]; out = [da1 | da3]           */
+};
+
+typedef struct SflGemmEpilogue {
+  int kind;
+  int beta;
+  void* out;
+  long ldo;
+  void* out2;
+  long ldo2;
+  const void* aux;
+  long ldaux;
+  const float* rope_cos; /* [rope_T, head_dim/2] fp32 (already rounded to bf16 values) */
+  const float* rope_sin;
+  int rope_T;
+  int rope_cols;
+  int head_dim;
+  int dual_offset; /* SWIGLU: row of w3 inside b */
+  int dual_rows;   /* SWIGLU: total rows of b    */
+  int* status;
+} SflGemmEpilogue;
+
+/* D[M,N] = A * B^T with bf16 operands and fp32 accumulation.
+ * a_mn = 0: a is [M,K] row-major (pitch lda); a_mn = 1: a is [K,M] row-major.
+ * b_mn = 0: b is [N,K] row-major (pitch ldb); b_mn = 1: b is [K,N] row-major.
+ * Pitches must be multiples of 8 elements and bases 16-byte aligned.
+ * bn_hint: 0 = choose tile width automatically, else 128 or 256.
+ * max_ctas: 0 = one CTA per SM, else an upper bound on the grid. */
+int sfl_gemm_bf16(const void* a, long lda, int a_mn, const void* b, long ldb, int b_mn, int M,
+                  int N, int K, const SflGemmEpilogue* epi, int bn_hint, int max_ctas,
+                  void* stream);
+
+/* --------------------------------------------------------------- RMSNorm -- */
+/* y = bf16(x * rsqrt(mean(x^2) + eps) * w), x fp32 [rows, dim]; rstd fp32 [rows]. */
+int sfl_rmsnorm_fwd(const float* x, const float* w, void* y_bf16, float* rstd, int rows, int dim,
+                    float eps, void* stream);
+/* dx_out = dres_in (may be NULL) + d(norm)/dx, optionally also written as bf16;
+ * dw_partial [sfl_rmsnorm_bwd_blocks(rows), dim] receives per-block partial sums
+ * of dy * xhat which sfl_rmsnorm_dw_reduce folds into dw (dw += sum). */
+int sfl_rmsnorm_bwd_blocks(int rows);
+int sfl_rmsnorm_bwd(const void* dy_bf16, const float* x, const float* w, const float* rstd,
+                    const float* dres_in, float* dx_out, void* dx_out_bf16, float* dw_partial,
+                    int rows, int dim, void* stream);
+int sfl_rmsnorm_dw_reduce(const float* dw_partial, int blocks, float* dw, int dim, int accumulate,
+                          void* stream);
+
+/* --------------------------------------------------------- cross entropy -- */
+/* logits bf16 [rows, vocab] (pitch ld).  Writes per-row loss (fp32) and, when
+ * dlogits != NULL, (softmax - onehot) * grad_scale as bf16 (may alias logits). */
+int sfl_cross_entropy(const void* logits_bf16, long ld, const int64_t* targets, float* row_loss,
+                      void* dlogits_bf16, float grad_scale, int rows, int vocab, void* stream);
+
+/* ------------------------------------------------------------- optimizer -- */
+/* Sum of squares of a flat fp32 buffer -> partial[blocks]; deterministic. */
+int sfl_sqnorm_blocks(long n);
+int sfl_sqnorm_partial(const float* x, long n, float* partial, void* stream);
+/* out[0] = sqrt(sum(partial[0..n)) * scale); out[1] = clip coefficient
+ * min(1, max_norm / (out[0] + 1e-6)); out[2] = 1 if out[0] is finite else 0. */
+int sfl_norm_finalize(const float* partial, int n, float sum_scale, float max_norm, float* out,
+                      void* stream);
+/* AdamW over a flat fp32 range.  The gradient is multiplied by *grad_coef
+ * (device pointer, may be NULL) and by grad_scale first.  bf16_shadow (may be
+ * NULL) receives the updated parameters rounded to bf16.  Update is skipped
+ * when skip_flag != NULL and *skip_flag == 0 (non-finite gradient norm). */
+int sfl_adamw(float* p, const float* g, float* m, float* v, void* bf16_shadow, long n, float lr,
+              float beta1, float beta2, float eps, float weight_decay, float bias1, float bias2,
+              const float* grad_coef, float grad_scale, const float* ok_flag, void* stream);
+
+/* ------------------------------------------------------------------ misc -- */
+int sfl_cast_f32_to_bf16(const float* x, void* y_bf16, long n, void* stream);
+int sfl_scale_f32(float* x, long n, const float* coef_dev, float scale, void* stream);
+/* out fp32 [rows, dim] = weight[ids[row]] */
+int sfl_embedding_fwd(const float* weight, const int64_t* ids, float* out, int rows, int dim,
+                      int vocab, void* stream);
+/* Library build tag, for diagnostics. */
+const char* sfl_version(void);
+
+#ifdef __cplusplus
+}
+#endif

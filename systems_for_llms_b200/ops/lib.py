@@ -1,0 +1,96 @@
+"""ctypes access to the sm_100a kernel library.
+
+``lib()`` returns the loaded ``libsfl_b200.so`` with argument types declared.
+On a machine with a CUDA device the library is required: a missing or stale
+build raises instead of silently falling back to eager PyTorch, so a GPU run
+can never pass on the wrong code path.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_long, c_void_p
+from functools import lru_cache
+
+import torch
+
+from . import build as _build
+
+
+class GemmEpilogue(Structure):
+    """Mirror of ``SflGemmEpilogue`` in csrc/sfl.h."""
+
+    _fields_ = [
+        ("kind", c_int), ("beta", c_int),
+        ("out", c_void_p), ("ldo", c_long),
+        ("out2", c_void_p), ("ldo2", c_long),
+        ("aux", c_void_p), ("ldaux", c_long),
+        ("rope_cos", c_void_p), ("rope_sin", c_void_p),
+        ("rope_T", c_int), ("rope_cols", c_int), ("head_dim", c_int),
+        ("dual_offset", c_int), ("dual_rows", c_int),
+        ("status", c_void_p),
+    ]
+
+
+EPI_BF16, EPI_F32, EPI_RESID, EPI_ROPE, EPI_SWIGLU, EPI_SWIGLU_BWD = range(6)
+
+_P = c_void_p
+_SIGNATURES = {
+    "sfl_gemm_bf16": [_P, c_long, c_int, _P, c_long, c_int, c_int, c_int, c_int,
+                      POINTER(GemmEpilogue), c_int, c_int, _P],
+    "sfl_rmsnorm_fwd": [_P, _P, _P, _P, c_int, c_int, c_float, _P],
+    "sfl_rmsnorm_bwd_blocks": [c_int],
+    "sfl_rmsnorm_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, _P],
+    "sfl_rmsnorm_dw_reduce": [_P, c_int, _P, c_int, c_int, _P],
+    "sfl_cross_entropy": [_P, c_long, _P, _P, _P, c_float, c_int, c_int, _P],
+    "sfl_sqnorm_blocks": [c_long],
+    "sfl_sqnorm_partial": [_P, c_long, _P, _P],
+    "sfl_norm_finalize": [_P, c_int, c_float, c_float, _P, _P],
+    "sfl_adamw": [_P, _P, _P, _P, _P, c_long, c_float, c_float, c_float, c_float, c_float,
+                  c_float, c_float, _P, c_float, _P, _P],
+    "sfl_cast_f32_to_bf16": [_P, _P, c_long, _P],
+    "sfl_scale_f32": [_P, c_long, _P, c_float, _P],
+    "sfl_embedding_fwd": [_P, _P, _P, c_int, c_int, c_int, _P],
+}
+_OPTIONAL: dict[str, list] = {}
+
+
+def register_signature(name: str, argtypes: list) -> None:
+    """Lets other modules (attention, comm) declare their entry points."""
+    _OPTIONAL[name] = argtypes
+    lib.cache_clear()
+
+
+@lru_cache(maxsize=1)
+def lib() -> ctypes.CDLL:
+    if not _build.LIB_PATH.exists() or not _build.is_current():
+        _build.build()
+    handle = ctypes.CDLL(str(_build.LIB_PATH))
+    for name, argtypes in {**_SIGNATURES, **_OPTIONAL}.items():
+        function = getattr(handle, name)
+        function.argtypes = argtypes
+        function.restype = c_int
+    handle.sfl_version.restype = c_char_p
+    handle.sfl_version.argtypes = []
+    return handle
+
+
+def available() -> bool:
+    """True when kernels can run: a CUDA device of compute capability 10.x."""
+    if not torch.cuda.is_available():
+        return False
+    major, _ = torch.cuda.get_device_capability()
+    return major == 10
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(tensor: torch.Tensor | None) -> int | None:
+    return None if tensor is None else tensor.data_ptr()
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise RuntimeError(f"{what} failed with code {code}")
