@@ -1,0 +1,1041 @@
+// Block-sparse flash attention for sm_100a: forward, dQ and dK/dV kernels.
+//
+// All three kernels share one structure.  A CTA owns a 128-row tile (queries for
+// forward/dQ, keys for dK/dV) of one (batch, head) and walks the 128-wide tiles
+// of the other sequence that a block schedule retains.  Warp 0 streams tiles in
+// with TMA, warp 1 issues tcgen05.mma into tensor memory, and four warps (one
+// thread per tile row) do the softmax math on accumulators read with tcgen05.ld,
+// write the probability / dS tile back to shared memory in the 128-byte-swizzled
+// layout the next MMA reads, and finish with the epilogue.
+//
+// Schedules come in two forms, as in the reference (attention_lab/
+// triton_attention.py:125-323): a CSR over query tiles (row_ptr, col_idx, a
+// "full" flag per stored tile, plus a 64-bit bitmap of the 16x16 sub-blocks that
+// are present so schedules compiled at finer granularity keep their meaning), or
+// an interval form whose tile range is derived from the window arithmetically.
+// Partial tiles evaluate the token-level predicate (causal, left/right window,
+// same-document); full tiles skip it.  Math follows the reference: scores are
+// scaled after the dot product, softmax statistics are fp32, P is rounded to the
+// input dtype before P V, rows without any visible key give O = 0, LSE = -inf,
+// and LSE is a natural logarithm.  The backward pass mirrors attention_lab/
+// backward.py:64-142: delta = rowsum(O dO); dQ owned by query tiles; dK/dV owned
+// by key tiles walking the transposed schedule; no atomics.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+#include "sfl.h"
+#include "tensormap.cuh"
+
+namespace sfl {
+
+constexpr int kTile = 128;          // rows and columns of a score tile
+constexpr int kAttnThreads = 192;   // producer warp, MMA warp, 4 compute warps
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct AttnSchedule {
+  int mode;  // 0 = CSR, 1 = interval
+  const int* row_ptr;
+  const int* col_idx;
+  const uint8_t* full;
+  const unsigned long long* bitmap;  // optional; bit (qs*8+ks) = 16x16 sub-block present
+  int causal;
+  int window_left;   // -1 = unbounded
+  int window_right;  // -1 = unbounded
+  const int* doc;    // optional document label per position
+};
+
+struct AttnParams {
+  int B, H, N;
+  float scale;
+  AttnSchedule sched;
+  // forward outputs / backward inputs
+  void* o;
+  long o_sb, o_sh, o_st;  // element strides of O (and dO) for batch, head, token
+  float* lse;             // [B,H,N]
+  float* delta;           // [B,H,N]
+  // backward outputs (same element strides as the q/k/v they mirror)
+  void* dq;
+  void* dk;
+  void* dv;
+  long g_sb, g_sh, g_st;
+  int is_fp16;
+  int* status;
+};
+
+// ---- element type helpers -------------------------------------------------
+template <bool FP16>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  if constexpr (FP16) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  } else {
+    return pack_bf16(a, b);
+  }
+}
+template <bool FP16>
+__device__ __forceinline__ float round_elem(float a) {
+  if constexpr (FP16) return __half2float(__float2half_rn(a));
+  return bf16_round(a);
+}
+template <bool FP16>
+__device__ __forceinline__ float load_elem(const void* p, long i) {
+  if constexpr (FP16) return __half2float(static_cast<const __half*>(p)[i]);
+  return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+__host__ __device__ constexpr uint32_t idesc_16bit(bool fp16, int m, int n, bool a_mn, bool b_mn) {
+  const uint32_t fmt = fp16 ? 0u : 1u;
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(a_mn) << 15) |
+         (static_cast<uint32_t>(b_mn) << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// ---- schedule walking -----------------------------------------------------
+struct TileRange {
+  int begin, end;            // CSR: [row_ptr[r], row_ptr[r+1]); interval: tile indices
+  int full_begin, full_end;  // interval mode only
+};
+
+// Tiles of the other sequence retained for `tile` (a query tile, or a key tile
+// when `transposed`).  Interval bounds follow the same arithmetic as the host
+// mirror in attention/flash.py (interval_regions).
+__device__ __forceinline__ TileRange tile_range(const AttnSchedule& s, int tile, int N,
+                                                bool transposed) {
+  TileRange r;
+  if (s.mode == 0) {
+    r.begin = s.row_ptr[tile];
+    r.end = s.row_ptr[tile + 1];
+    r.full_begin = r.full_end = 0;
+    return r;
+  }
+  const int first = tile * kTile;
+  const int last = min(first + kTile, N) - 1;
+  // For a query tile: keys in [q - L, q + R].  For a key tile the roles of the
+  // windows swap: queries in [k - R, k + L].
+  int left = transposed ? (s.causal ? 0 : s.window_right) : s.window_left;
+  int right = transposed ? s.window_left : (s.causal ? 0 : s.window_right);
+  const int lo = left < 0 ? 0 : max(0, first - left);
+  const int hi = right < 0 ? N - 1 : min(N - 1, last + right);
+  r.begin = lo / kTile;
+  r.end = hi / kTile + 1;
+  const int first_full = left < 0 ? 0 : max(0, last - left);
+  int fb = (first_full + kTile - 1) / kTile;
+  fb = min(r.end, max(r.begin, fb));
+  int fe = (right < 0 || first + right >= N - 1) ? r.end : (first + right + 1) / kTile;
+  fe = max(fb, min(r.end, fe));
+  r.full_begin = fb;
+  r.full_end = fe;
+  return r;
+}
+
+struct TileInfo {
+  int other;  // index of the tile of the other sequence
+  bool full;
+  unsigned long long bitmap;
+};
+
+__device__ __forceinline__ TileInfo tile_info(const AttnSchedule& s, const TileRange& r, int it) {
+  TileInfo t;
+  if (s.mode == 0) {
+    const int e = r.begin + it;
+    t.other = s.col_idx[e];
+    t.full = s.full[e] != 0;
+    t.bitmap = s.bitmap != nullptr ? s.bitmap[e] : ~0ull;
+  } else {
+    t.other = r.begin + it;
+    t.full = t.other >= r.full_begin && t.other < r.full_end;
+    t.bitmap = ~0ull;
+  }
+  return t;
+}
+
+// Token-level predicate in interval form.  For the thread that owns one row of a
+// score tile, the permitted columns c (relative to the tile's first column) are
+// exactly those with (unsigned)(c - rel_lo) < len; document labels and dropped
+// sub-blocks are applied on top.  Keeping the test to one subtract, one compare
+// and one select per element keeps the unrolled loops small.
+struct RowMask {
+  int rel_lo;
+  uint32_t len;
+};
+
+// Thread owns query q; columns are keys col0 + c.
+__device__ __forceinline__ RowMask row_mask_for_query(const AttnSchedule& s, int q, int col0,
+                                                      int N) {
+  const int lo = s.window_left < 0 ? 0 : max(0, q - s.window_left);
+  int hi = s.causal ? q : (s.window_right < 0 ? N - 1 : q + s.window_right);
+  hi = min(hi, N - 1);
+  RowMask m;
+  m.rel_lo = lo - col0;
+  m.len = (q < N && hi >= lo) ? static_cast<uint32_t>(hi - lo + 1) : 0u;
+  return m;
+}
+
+// Thread owns key k; columns are queries col0 + c.
+__device__ __forceinline__ RowMask row_mask_for_key(const AttnSchedule& s, int k, int col0, int N) {
+  const int lo = s.causal ? k : (s.window_right < 0 ? 0 : max(0, k - s.window_right));
+  const int hi = s.window_left < 0 ? N - 1 : min(N - 1, k + s.window_left);
+  RowMask m;
+  m.rel_lo = lo - col0;
+  m.len = (k < N && hi >= lo) ? static_cast<uint32_t>(hi - lo + 1) : 0u;
+  return m;
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Sets masked scores to -inf.  `group_bits` has bit g set when columns
+// [16g, 16g+16) of this row's sub-block row are present in the schedule.
+__device__ __forceinline__ void apply_mask(float (&x)[kTile], const RowMask& m,
+                                           uint32_t group_bits) {
+#pragma unroll
+  for (int g = 0; g < kTile / 16; ++g) {
+    const uint32_t len = (group_bits >> g) & 1u ? m.len : 0u;
+#pragma unroll
+    for (int c = g * 16; c < g * 16 + 16; ++c)
+      x[c] = static_cast<uint32_t>(c - m.rel_lo) < len ? x[c] : -INFINITY;
+  }
+}
+
+__device__ __forceinline__ void apply_doc_mask(float (&x)[kTile], const int* col_doc, int my_doc) {
+#pragma unroll
+  for (int c = 0; c < kTile; ++c) x[c] = col_doc[c] == my_doc ? x[c] : -INFINITY;
+}
+
+// ---- shared-memory tile writer -------------------------------------------
+// Writes one row (128 values, already packed in pairs) of a [128 x 128] 16-bit
+// tile into the K-major 128-byte-swizzled layout: two column halves of
+// [128 rows][128 bytes]; 16-byte chunk c of row r lives at chunk (c ^ (r & 7)).
+__device__ __forceinline__ void store_row_swizzled(uint8_t* tile, int row,
+                                                   const uint32_t (&packed)[64]) {
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    uint8_t* base = tile + half * (kTile * 128) + row * 128;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      uint4 v = make_uint4(packed[half * 32 + c * 4 + 0], packed[half * 32 + c * 4 + 1],
+                           packed[half * 32 + c * 4 + 2], packed[half * 32 + c * 4 + 3]);
+      *reinterpret_cast<uint4*>(base + ((c ^ (row & 7)) << 4)) = v;
+    }
+  }
+}
+
+// Same layout, one 32-column chunk (16 packed pairs) at a time.
+__device__ __forceinline__ void store_chunk_swizzled(uint8_t* tile, int row, int chunk,
+                                                     const uint32_t (&packed)[16]) {
+  uint8_t* base = tile + (chunk >> 1) * (kTile * 128) + row * 128;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int c16 = (chunk & 1) * 4 + c;
+    *reinterpret_cast<uint4*>(base + ((c16 ^ (row & 7)) << 4)) =
+        make_uint4(packed[c * 4 + 0], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
+  }
+}
+
+// Descriptors of the k-th 16-wide reduction step.
+//   K-major tile of [rows][W] 16-bit elements stored as W/64 column halves.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t base, int rows, int k) {
+  return umma_smem_desc(base + (k >> 2) * (rows * 128) + (k & 3) * 32, 16, 1024);
+}
+//   MN-major view of a [128 reduction rows][W] tile: step k covers rows 16k..16k+15.
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t base, int k) {
+  return umma_smem_desc(base + k * 2048, kTile * 128, 1024);
+}
+
+__device__ __forceinline__ void named_barrier_128() {
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32f(uint32_t taddr, float* dst) {
+  uint32_t r[32];
+  tmem_ld_32x32(taddr, r);
+#pragma unroll
+  for (int i = 0; i < 32; ++i) dst[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const float* src) {
+  uint32_t a[16], b[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    a[i] = __float_as_uint(src[i]);
+    b[i] = __float_as_uint(src[16 + i]);
+  }
+  tmem_st_32x16(taddr, a);
+  tmem_st_32x16(taddr + 16, b);
+}
+
+__device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, volatile int* abort,
+                                             int* status, int code) {
+  for (uint32_t spin = 0; spin < (1u << 23); ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (spin > 2048) {
+      __nanosleep(256);
+      if (*abort) return false;
+    }
+  }
+  report_status(status, code);
+  *abort = 1;
+  return false;
+}
+
+// Load the operand tile(s) for rows [row0, row0+128) of (b, h): D/64 boxes.
+template <int D>
+__device__ __forceinline__ void load_rows(uint8_t* dst, const CUtensorMap* map, uint64_t* bar,
+                                          int row0, int h, int b) {
+#pragma unroll
+  for (int i = 0; i < D / 64; ++i)
+    tma_load_4d(dst + i * (kTile * 128), map, bar, i * 64, row0, h, b);
+}
+
+// ============================================================== forward ====
+template <int D>
+struct FwdSmem {
+  static constexpr int kTileBytes = kTile * D * 2;
+  static constexpr int kPBytes = kTile * kTile * 2;
+  static constexpr int kPBufs = (D == 64) ? 2 : 1;
+  static constexpr int kStages = 2;
+  static constexpr int kBytes = kTileBytes * (1 + 2 * kStages) + kPBytes * kPBufs + 1024 + 1024;
+};
+
+struct FwdBarriers {
+  uint64_t q_full;
+  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+  uint64_t s_full[2];
+  uint64_t p_ready[2];
+  uint64_t pv_done[2];
+  uint32_t tmem_base;
+  int abort;
+  int col_doc[kTile];  // document labels of the current key tile
+};
+
+template <int D, bool FP16>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+  using L = FwdSmem<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + L::kTileBytes;
+  uint8_t* sV = sK + L::kStages * L::kTileBytes;
+  uint8_t* sP = sV + L::kStages * L::kTileBytes;
+  FwdBarriers* bars = reinterpret_cast<FwdBarriers*>(sP + L::kPBufs * L::kPBytes);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Heaviest (last) query tiles first so causal work is balanced across waves.
+  const int num_q_tiles = (p.N + kTile - 1) / kTile;
+  const int q_tile = num_q_tiles - 1 - blockIdx.x;
+  const int bh = blockIdx.y;
+  const int b = bh / p.H, h = bh % p.H;
+  const TileRange range = tile_range(p.sched, q_tile, p.N, false);
+  const int n_tiles = range.end - range.begin;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->k_full[s], 1);
+      mbar_init(&bars->k_empty[s], 1);
+      mbar_init(&bars->v_full[s], 1);
+      mbar_init(&bars->v_empty[s], 1);
+      mbar_init(&bars->s_full[s], 1);
+      mbar_init(&bars->p_ready[s], 128);
+      mbar_init(&bars->pv_done[s], 1);
+    }
+    bars->abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  const uint32_t tS = tmem;        // two score buffers: columns [0,128) and [128,256)
+  const uint32_t tO = tmem + 256;  // output accumulator: D columns
+  volatile int* abort = &bars->abort;
+  constexpr int PB = L::kPBufs;
+
+  if (warp == 0) {
+    if (lane == 0 && n_tiles > 0) {
+      mbar_expect_tx(&bars->q_full, L::kTileBytes);
+      load_rows<D>(sQ, &tmQ, &bars->q_full, q_tile * kTile, h, b);
+      for (int j = 0; j < n_tiles; ++j) {
+        const TileInfo t = tile_info(p.sched, range, j);
+        const int s = j & 1;
+        const uint32_t ph = ((j >> 1) & 1) ^ 1;
+        if (!bounded_wait(&bars->k_empty[s], ph, abort, p.status, kStatusTimeoutEmpty)) break;
+        mbar_expect_tx(&bars->k_full[s], L::kTileBytes);
+        load_rows<D>(sK + s * L::kTileBytes, &tmK, &bars->k_full[s], t.other * kTile, h, b);
+        if (!bounded_wait(&bars->v_empty[s], ph, abort, p.status, kStatusTimeoutEmpty)) break;
+        mbar_expect_tx(&bars->v_full[s], L::kTileBytes);
+        load_rows<D>(sV + s * L::kTileBytes, &tmV, &bars->v_full[s], t.other * kTile, h, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idesc_qk = idesc_16bit(FP16, kTile, kTile, false, false);
+      constexpr uint32_t idesc_pv = idesc_16bit(FP16, kTile, D, false, true);
+      const uint32_t q_addr = smem_u32(sQ);
+      auto issue_qk = [&](int j) -> bool {
+        const int s = j & 1;
+        if (!bounded_wait(&bars->k_full[s], (j >> 1) & 1, abort, p.status, kStatusTimeoutFull))
+          return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sK + s * L::kTileBytes);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma_bf16_ss(tS + s * kTile, desc_kmajor(q_addr, kTile, k), desc_kmajor(k_addr, kTile, k),
+                       idesc_qk, k != 0);
+        umma_commit(&bars->k_empty[s]);
+        umma_commit(&bars->s_full[s]);
+        return true;
+      };
+      bool ok = bounded_wait(&bars->q_full, 0, abort, p.status, kStatusTimeoutFull);
+      if (ok) ok = issue_qk(0);
+      if (ok && n_tiles > 1) ok = issue_qk(1);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int pb = j % PB;
+        const int s = j & 1;
+        if (!bounded_wait(&bars->p_ready[pb], (j / PB) & 1, abort, p.status,
+                          kStatusTimeoutTmemFull) ||
+            !bounded_wait(&bars->v_full[s], (j >> 1) & 1, abort, p.status, kStatusTimeoutFull))
+          break;
+        tc_fence_after();
+        const uint32_t p_addr = smem_u32(sP + pb * L::kPBytes);
+        const uint32_t v_addr = smem_u32(sV + s * L::kTileBytes);
+#pragma unroll
+        for (int k = 0; k < kTile / 16; ++k)
+          umma_bf16_ss(tO, desc_kmajor(p_addr, kTile, k), desc_mnmajor(v_addr, k), idesc_pv,
+                       (j | k) != 0);
+        umma_commit(&bars->v_empty[s]);
+        umma_commit(&bars->pv_done[pb]);
+        if (j + 2 < n_tiles) ok = issue_qk(j + 2);
+      }
+    }
+  } else {
+    // ------------------------------------------------ softmax + epilogue ----
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int q = q_tile * kTile + row;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const float scale_log2 = p.scale * kLog2e;
+    float m_used = -INFINITY;
+    float l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const TileInfo t = tile_info(p.sched, range, j);
+      const int s = j & 1;
+      const int pb = j % PB;
+      if (!bounded_wait(&bars->s_full[s], (j >> 1) & 1, abort, p.status, kStatusTimeoutTmemFull)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      float x[kTile];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32f(tS + lane_base + s * kTile + c * 32, x + c * 32);
+      tmem_ld_wait();
+      const int k0 = t.other * kTile;
+      const bool ragged = (k0 + kTile > p.N) || (q_tile * kTile + kTile > p.N);
+      if (!t.full || ragged) {
+        const RowMask rm = row_mask_for_query(p.sched, q, k0, p.N);
+        apply_mask(x, rm, static_cast<uint32_t>(t.bitmap >> ((row >> 4) * 8)) & 0xffu);
+        if (p.sched.doc != nullptr) {
+          named_barrier_128();  // previous readers of the label tile are done
+          bars->col_doc[row] = k0 + row < p.N ? p.sched.doc[k0 + row] : -1;
+          named_barrier_128();
+          apply_doc_mask(x, bars->col_doc, q < p.N ? p.sched.doc[q] : -2);
+        }
+      }
+      // Row maximum of the raw scores; the positive scale preserves the order.
+      float mx = x[0];
+#pragma unroll
+      for (int c = 1; c < kTile; ++c) mx = fmaxf(mx, x[c]);
+      mx *= scale_log2;
+      // Lazy rescale: keep a stale maximum until it is off by more than 2^8.
+      const bool grow = mx > m_used + 8.0f;
+      if (__any_sync(0xffffffffu, grow)) {
+        if (j > 0) {
+          if (!bounded_wait(&bars->pv_done[(j - 1) % PB], ((j - 1) / PB) & 1, abort, p.status,
+                            kStatusTimeoutTmemFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const float alpha = grow ? fast_exp2(m_used - mx) : 1.0f;
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            float o[32];
+            tmem_ld_32x32f(tO + lane_base + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] *= alpha;
+            tmem_st_32x32(tO + lane_base + c * 32, o);
+          }
+          tmem_st_wait();
+          l *= alpha;
+        }
+        if (grow) m_used = mx;
+      }
+      uint32_t packed[64];
+      float sum = 0.f;
+      // A row that has seen no key yet keeps m_used = -inf; subtract 0 instead so
+      // masked scores (-inf) still map to probability 0 rather than NaN.
+      const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
+#pragma unroll
+      for (int c = 0; c < kTile; c += 2) {
+        const float p0 = fast_exp2(fmaf(x[c], scale_log2, neg_m));
+        const float p1 = fast_exp2(fmaf(x[c + 1], scale_log2, neg_m));
+        sum += p0 + p1;
+        packed[c >> 1] = pack2<FP16>(p0, p1);
+      }
+      l += sum;
+      if (j >= PB) {
+        if (!bounded_wait(&bars->pv_done[pb], ((j - PB) / PB) & 1, abort, p.status,
+                          kStatusTimeoutTmemFull)) {
+          ok = false;
+          break;
+        }
+      }
+      store_row_swizzled(sP + pb * L::kPBytes, row, packed);
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(&bars->p_ready[pb]);
+    }
+    if (ok && n_tiles > 0)
+      ok = bounded_wait(&bars->pv_done[(n_tiles - 1) % PB], ((n_tiles - 1) / PB) & 1, abort,
+                        p.status, kStatusTimeoutTmemFull);
+    if (ok) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      uint8_t* orow = static_cast<uint8_t*>(p.o) +
+                      2 * (b * p.o_sb + h * p.o_sh + static_cast<long>(q) * p.o_st);
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        float o[32];
+        if (n_tiles > 0) {
+          tmem_ld_32x32f(tO + lane_base + c * 32, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0.f;
+        }
+        if (q < p.N) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 v;
+            v.x = pack2<FP16>(o[8 * i + 0] * inv, o[8 * i + 1] * inv);
+            v.y = pack2<FP16>(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
+            v.z = pack2<FP16>(o[8 * i + 4] * inv, o[8 * i + 5] * inv);
+            v.w = pack2<FP16>(o[8 * i + 6] * inv, o[8 * i + 7] * inv);
+            *reinterpret_cast<uint4*>(orow + (c * 32 + i * 8) * 2) = v;
+          }
+        }
+      }
+      if (q < p.N && p.lse != nullptr)
+        p.lse[(static_cast<long>(b) * p.H + h) * p.N + q] =
+            l > 0.f ? (m_used + log2f(l)) * kLn2 : -INFINITY;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ================================================================ delta ====
+// delta[b,h,t] = sum_d O * dO  (fp32); one warp per row.
+template <bool FP16>
+__global__ void attn_delta_kernel(const void* __restrict__ o, const void* __restrict__ d_o,
+                                  float* __restrict__ delta, int B, int H, int N, int D, long sb,
+                                  long sh, long st) {
+  const int lane = threadIdx.x & 31;
+  const long rowid = static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (rowid >= static_cast<long>(B) * H * N) return;
+  const int t = rowid % N;
+  const int h = (rowid / N) % H;
+  const int b = rowid / (static_cast<long>(N) * H);
+  const long base = b * sb + h * sh + static_cast<long>(t) * st;
+  float s = 0.f;
+  for (int i = lane; i < D; i += 32) s += load_elem<FP16>(o, base + i) * load_elem<FP16>(d_o, base + i);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (lane == 0) delta[rowid] = s;
+}
+
+// ============================================================= backward ====
+// Shared layout of the two backward kernels: an "owned" pair of resident tiles,
+// a ring of streamed tile pairs, and two [128 x 128] tiles written by the compute
+// warps (probabilities and dS) for the accumulation MMAs.
+template <int D>
+struct BwdSmem {
+  static constexpr int kTileBytes = kTile * D * 2;
+  static constexpr int kPBytes = kTile * kTile * 2;
+  static constexpr int kStages = (D == 64) ? 2 : 1;
+  static constexpr int kBytes =
+      2 * kTileBytes + kStages * 2 * kTileBytes + 2 * kPBytes + 1024 + 2048 + 256;
+};
+
+struct BwdBarriers {
+  uint64_t own_full;
+  uint64_t in_full[2], in_empty[2];
+  uint64_t sp_full;    // score and dP accumulators ready
+  uint64_t pds_ready;  // P and dS tiles written (128 arrivals)
+  uint64_t acc_done;   // accumulation MMAs of the tile finished
+  uint32_t tmem_base;
+  int abort;
+};
+
+// dK/dV kernel (KV_OWNED = true): CTA owns a key tile; streams (Q, dO) tiles.
+//   S^T = K Q^T, dP^T = V dO^T, P^T = exp(S^T - lse_q), dS^T = P^T (dP^T - delta_q)
+//   dV += P^T dO,  dK += dS^T Q
+// dQ kernel (KV_OWNED = false): CTA owns a query tile; streams (K, V) tiles.
+//   S = Q K^T, dP = dO V^T, P = exp(S - lse_q), dS = P (dP - delta_q)
+//   dQ += dS K
+template <int D, bool FP16, bool KV_OWNED>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or Q
+                const __grid_constant__ CUtensorMap tmOwnB,  // V (kv-owned) or dO
+                const __grid_constant__ CUtensorMap tmInA,   // Q (kv-owned) or K
+                const __grid_constant__ CUtensorMap tmInB,   // dO (kv-owned) or V
+                const AttnParams p) {
+  using L = BwdSmem<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sOwnA = smem;
+  uint8_t* sOwnB = sOwnA + L::kTileBytes;
+  uint8_t* sIn = sOwnB + L::kTileBytes;  // stages x (A, B)
+  uint8_t* sP = sIn + L::kStages * 2 * L::kTileBytes;
+  uint8_t* sDS = sP + L::kPBytes;
+  float* sStats = reinterpret_cast<float*>(sDS + L::kPBytes);  // -lse[128], delta[128]
+  int* sDoc = reinterpret_cast<int*>(sStats + 2 * kTile);       // labels of the streamed tile
+  BwdBarriers* bars = reinterpret_cast<BwdBarriers*>(reinterpret_cast<uint8_t*>(sStats) + 2048);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = (p.N + kTile - 1) / kTile;
+  const int own_tile = KV_OWNED ? blockIdx.x : num_tiles - 1 - blockIdx.x;
+  const int bh = blockIdx.y;
+  const int b = bh / p.H, h = bh % p.H;
+  const TileRange range = tile_range(p.sched, own_tile, p.N, KV_OWNED);
+  const int n_tiles = range.end - range.begin;
+  constexpr int ST = L::kStages;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->own_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->in_full[s], 1);
+      mbar_init(&bars->in_empty[s], 1);
+    }
+    mbar_init(&bars->sp_full, 1);
+    mbar_init(&bars->pds_ready, 128);
+    mbar_init(&bars->acc_done, 1);
+    bars->abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  const uint32_t tS = tmem;         // scores
+  const uint32_t tDP = tmem + 128;  // dP
+  const uint32_t tAcc0 = tmem + 256;      // dV (kv-owned) or dQ
+  const uint32_t tAcc1 = tmem + 256 + D;  // dK (kv-owned)
+  volatile int* abort = &bars->abort;
+
+  if (warp == 0) {
+    if (lane == 0 && n_tiles > 0) {
+      mbar_expect_tx(&bars->own_full, 2 * L::kTileBytes);
+      load_rows<D>(sOwnA, &tmOwnA, &bars->own_full, own_tile * kTile, h, b);
+      load_rows<D>(sOwnB, &tmOwnB, &bars->own_full, own_tile * kTile, h, b);
+      for (int j = 0; j < n_tiles; ++j) {
+        const TileInfo t = tile_info(p.sched, range, j);
+        const int s = j % ST;
+        if (!bounded_wait(&bars->in_empty[s], ((j / ST) & 1) ^ 1, abort, p.status,
+                          kStatusTimeoutEmpty))
+          break;
+        mbar_expect_tx(&bars->in_full[s], 2 * L::kTileBytes);
+        uint8_t* dst = sIn + s * 2 * L::kTileBytes;
+        load_rows<D>(dst, &tmInA, &bars->in_full[s], t.other * kTile, h, b);
+        load_rows<D>(dst + L::kTileBytes, &tmInB, &bars->in_full[s], t.other * kTile, h, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idesc_s = idesc_16bit(FP16, kTile, kTile, false, false);
+      constexpr uint32_t idesc_acc = idesc_16bit(FP16, kTile, D, false, true);
+      const uint32_t ownA = smem_u32(sOwnA), ownB = smem_u32(sOwnB);
+      const uint32_t p_addr = smem_u32(sP), ds_addr = smem_u32(sDS);
+      bool ok = bounded_wait(&bars->own_full, 0, abort, p.status, kStatusTimeoutFull);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % ST;
+        if (!bounded_wait(&bars->in_full[s], (j / ST) & 1, abort, p.status, kStatusTimeoutFull))
+          break;
+        // The score accumulators are free once the compute warps have consumed
+        // tile j-1, which they signal through pds_ready (waited on below).
+        tc_fence_after();
+        const uint32_t inA = smem_u32(sIn + s * 2 * L::kTileBytes);
+        const uint32_t inB = inA + L::kTileBytes;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)  // S^T = K Q^T   or   S = Q K^T
+          umma_bf16_ss(tS, desc_kmajor(ownA, kTile, k), desc_kmajor(inA, kTile, k), idesc_s, k != 0);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)  // dP^T = V dO^T  or  dP = dO V^T
+          umma_bf16_ss(tDP, desc_kmajor(ownB, kTile, k), desc_kmajor(inB, kTile, k), idesc_s,
+                       k != 0);
+        umma_commit(&bars->sp_full);
+        if (!bounded_wait(&bars->pds_ready, j & 1, abort, p.status, kStatusTimeoutTmemFull)) break;
+        tc_fence_after();
+        if constexpr (KV_OWNED) {
+#pragma unroll
+          for (int k = 0; k < kTile / 16; ++k)  // dV += P^T dO
+            umma_bf16_ss(tAcc0, desc_kmajor(p_addr, kTile, k), desc_mnmajor(inB, k), idesc_acc,
+                         (j | k) != 0);
+#pragma unroll
+          for (int k = 0; k < kTile / 16; ++k)  // dK += dS^T Q
+            umma_bf16_ss(tAcc1, desc_kmajor(ds_addr, kTile, k), desc_mnmajor(inA, k), idesc_acc,
+                         (j | k) != 0);
+        } else {
+#pragma unroll
+          for (int k = 0; k < kTile / 16; ++k)  // dQ += dS K
+            umma_bf16_ss(tAcc0, desc_kmajor(ds_addr, kTile, k), desc_mnmajor(inA, k), idesc_acc,
+                         (j | k) != 0);
+        }
+        umma_commit(&bars->in_empty[s]);
+        umma_commit(&bars->acc_done);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int own_pos = own_tile * kTile + row;  // key index (kv-owned) or query index
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const float scale_log2 = p.scale * kLog2e;
+    const long stat_base = (static_cast<long>(b) * p.H + h) * p.N;
+    float my_lse = 0.f, my_delta = 0.f;
+    if constexpr (!KV_OWNED) {
+      // lse in log2 units; +inf for padding rows makes P vanish.
+      my_lse = own_pos < p.N ? p.lse[stat_base + own_pos] * kLog2e : INFINITY;
+      my_delta = own_pos < p.N ? p.delta[stat_base + own_pos] : 0.f;
+      if (my_lse == -INFINITY) my_lse = INFINITY;  // row without keys: P = 0
+    }
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const TileInfo t = tile_info(p.sched, range, j);
+      const int other0 = t.other * kTile;
+      const bool ragged = (other0 + kTile > p.N) || (own_tile * kTile + kTile > p.N);
+      const bool masked = !t.full || ragged;
+      const bool use_doc = masked && p.sched.doc != nullptr;
+      if (KV_OWNED || use_doc) {
+        // Per-column data of this tile: (negated) log-sum-exp and delta of the
+        // query columns for the key-owned kernel, document labels for both.
+        if (j > 0) named_barrier_128();  // previous tile's readers are done
+        const int ci = other0 + row;
+        if constexpr (KV_OWNED) {
+          float ls = ci < p.N ? p.lse[stat_base + ci] * kLog2e : INFINITY;
+          if (ls == -INFINITY) ls = INFINITY;
+          sStats[row] = -ls;
+          sStats[kTile + row] = ci < p.N ? p.delta[stat_base + ci] : 0.f;
+        }
+        if (use_doc) sDoc[row] = ci < p.N ? p.sched.doc[ci] : -1;
+        named_barrier_128();
+      }
+      if (!bounded_wait(&bars->sp_full, j & 1, abort, p.status, kStatusTimeoutTmemFull)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      RowMask rm{0, 0u};
+      uint32_t group_bits = 0xffu;
+      int my_doc = -2;
+      if (masked) {
+        // The bitmap is indexed (query sub-block, key sub-block).
+        if constexpr (KV_OWNED) {
+          rm = row_mask_for_key(p.sched, own_pos, other0, p.N);
+          group_bits = 0;
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            group_bits |= static_cast<uint32_t>((t.bitmap >> (g * 8 + (row >> 4))) & 1ull) << g;
+        } else {
+          rm = row_mask_for_query(p.sched, own_pos, other0, p.N);
+          group_bits = static_cast<uint32_t>(t.bitmap >> ((row >> 4) * 8)) & 0xffu;
+        }
+        if (use_doc && own_pos < p.N) my_doc = p.sched.doc[own_pos];
+      }
+      // The P and dS tiles are free once the accumulation MMAs of tile j-1 are done;
+      // the tensor pipe runs in issue order, so that already holds when the scores
+      // of tile j have arrived and this wait returns at once.
+      if (j > 0 &&
+          !bounded_wait(&bars->acc_done, (j - 1) & 1, abort, p.status, kStatusTimeoutTmemFull)) {
+        ok = false;
+        break;
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float sv[32], dp[32];
+        uint32_t pp[16], dd[16];
+        tmem_ld_32x32f(tS + lane_base + c * 32, sv);
+        tmem_ld_32x32f(tDP + lane_base + c * 32, dp);
+        tmem_ld_wait();
+        if (masked) {
+#pragma unroll
+          for (int g = 0; g < 2; ++g) {
+            const uint32_t len = (group_bits >> (c * 2 + g)) & 1u ? rm.len : 0u;
+#pragma unroll
+            for (int i = g * 16; i < g * 16 + 16; ++i)
+              sv[i] = static_cast<uint32_t>(c * 32 + i - rm.rel_lo) < len ? sv[i] : -INFINITY;
+          }
+          if (use_doc) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) sv[i] = sDoc[c * 32 + i] == my_doc ? sv[i] : -INFINITY;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float pr[2], ds[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int col = c * 32 + i + e;
+            const float neg_ls = KV_OWNED ? sStats[col] : -my_lse;
+            const float dl = KV_OWNED ? sStats[kTile + col] : my_delta;
+            // exp2(-inf) = 0 covers both masked scores and rows without keys.
+            const float prob = fast_exp2(fmaf(sv[i + e], scale_log2, neg_ls));
+            pr[e] = prob;
+            ds[e] = prob * (dp[i + e] - dl);
+          }
+          pp[i >> 1] = pack2<FP16>(pr[0], pr[1]);
+          dd[i >> 1] = pack2<FP16>(ds[0], ds[1]);
+        }
+        if constexpr (KV_OWNED) store_chunk_swizzled(sP, row, c, pp);
+        store_chunk_swizzled(sDS, row, c, dd);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(&bars->pds_ready);
+    }
+    if (ok && n_tiles > 0)
+      ok = bounded_wait(&bars->acc_done, (n_tiles - 1) & 1, abort, p.status, kStatusTimeoutTmemFull);
+    if (ok) {
+      tc_fence_after();
+      const long goff = 2 * (b * p.g_sb + h * p.g_sh + static_cast<long>(own_pos) * p.g_st);
+      auto write_acc = [&](uint32_t taddr, void* dst_base, float mul) {
+        uint8_t* dst = static_cast<uint8_t*>(dst_base) + goff;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          float a[32];
+          if (n_tiles > 0) {
+            tmem_ld_32x32f(taddr + lane_base + c * 32, a);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) a[i] = 0.f;
+          }
+          if (own_pos < p.N) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 v;
+              v.x = pack2<FP16>(a[8 * i + 0] * mul, a[8 * i + 1] * mul);
+              v.y = pack2<FP16>(a[8 * i + 2] * mul, a[8 * i + 3] * mul);
+              v.z = pack2<FP16>(a[8 * i + 4] * mul, a[8 * i + 5] * mul);
+              v.w = pack2<FP16>(a[8 * i + 6] * mul, a[8 * i + 7] * mul);
+              *reinterpret_cast<uint4*>(dst + (c * 32 + i * 8) * 2) = v;
+            }
+          }
+        }
+      };
+      if constexpr (KV_OWNED) {
+        write_acc(tAcc0, p.dv, 1.0f);
+        write_acc(tAcc1, p.dk, p.scale);
+      } else {
+        write_acc(tAcc0, p.dq, p.scale);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// Rotate (even, odd) pairs by -angle in place: the gradient of the rotary
+// embedding applied in the q|k|v projection epilogue.  x is [rows, ld] with the
+// first `cols` columns rotated; position = row % T.
+__global__ void rope_bwd_kernel(__nv_bfloat16* __restrict__ x, long ld, const float* __restrict__ cos,
+                                const float* __restrict__ sin, long rows, int cols, int T,
+                                int head_dim) {
+  const long pairs = rows * (cols >> 1);
+  const int half = head_dim >> 1;
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < pairs;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long r = i / (cols >> 1);
+    const int c = static_cast<int>(i % (cols >> 1)) * 2;
+    const int pos = static_cast<int>(r % T);
+    const int pi = (c % head_dim) >> 1;
+    const float cs = cos[static_cast<long>(pos) * half + pi];
+    const float sn = sin[static_cast<long>(pos) * half + pi];
+    __nv_bfloat162* ptr = reinterpret_cast<__nv_bfloat162*>(x + r * ld + c);
+    const float2 g = __bfloat1622float2(*ptr);
+    *ptr = __floats2bfloat162_rn(g.x * cs + g.y * sn, -g.x * sn + g.y * cs);
+  }
+}
+
+// ------------------------------------------------------------------ host ----
+namespace {
+
+int make_map(CUtensorMap* map, const void* base, const SflAttnTensor& t, int B, int H, int N, int D) {
+  uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(N),
+                      static_cast<uint64_t>(H), static_cast<uint64_t>(B)};
+  uint64_t strides[4] = {0, static_cast<uint64_t>(t.stride_t) * 2,
+                         static_cast<uint64_t>(t.stride_h) * 2,
+                         static_cast<uint64_t>(t.stride_b) * 2};
+  uint32_t box[4] = {64, kTile, 1, 1};
+  return make_tensormap_nd_b16(map, base, 4, dims, strides, box, 3);
+}
+
+bool strides_ok(const SflAttnTensor& t) {
+  return t.ptr != nullptr && (reinterpret_cast<uintptr_t>(t.ptr) & 15) == 0 &&
+         t.stride_t % 8 == 0 && t.stride_h % 8 == 0 && t.stride_b % 8 == 0;
+}
+
+AttnSchedule to_sched(const SflAttnMask* m, bool transposed) {
+  AttnSchedule s{};
+  s.mode = m->mode;
+  s.row_ptr = transposed ? m->t_row_ptr : m->row_ptr;
+  s.col_idx = transposed ? m->t_col_idx : m->col_idx;
+  s.full = transposed ? m->t_full : m->full;
+  s.bitmap = reinterpret_cast<const unsigned long long*>(transposed ? m->t_bitmap : m->bitmap);
+  s.causal = m->causal;
+  s.window_left = m->window_left;
+  s.window_right = m->window_right;
+  s.doc = m->doc;
+  return s;
+}
+
+template <typename Kernel>
+int set_smem(Kernel kernel, int bytes) {
+  return static_cast<int>(
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+}
+
+}  // namespace
+}  // namespace sfl
+
+using namespace sfl;
+
+extern "C" int sfl_attn_fwd(const SflAttnTensor* q, const SflAttnTensor* k, const SflAttnTensor* v,
+                            const SflAttnTensor* o, float* lse, int B, int H, int N, int D,
+                            float scale, const SflAttnMask* mask, int is_fp16, int* status,
+                            void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if ((D != 64 && D != 128) || B <= 0 || H <= 0 || N <= 0 || mask == nullptr) return -2;
+  if (!strides_ok(*q) || !strides_ok(*k) || !strides_ok(*v) || !strides_ok(*o)) return -2;
+  CUtensorMap tq, tk, tv;
+  if (make_map(&tq, q->ptr, *q, B, H, N, D) || make_map(&tk, k->ptr, *k, B, H, N, D) ||
+      make_map(&tv, v->ptr, *v, B, H, N, D))
+    return -3;
+  AttnParams p{};
+  p.B = B; p.H = H; p.N = N; p.scale = scale;
+  p.sched = to_sched(mask, false);
+  p.o = o->ptr; p.o_sb = o->stride_b; p.o_sh = o->stride_h; p.o_st = o->stride_t;
+  p.lse = lse; p.is_fp16 = is_fp16; p.status = status;
+  dim3 grid((N + kTile - 1) / kTile, B * H);
+#define SFL_FWD(D_, F_)                                                                   \
+  {                                                                                       \
+    auto kern = attn_fwd_kernel<D_, F_>;                                                  \
+    int rc = set_smem(kern, FwdSmem<D_>::kBytes);                                         \
+    if (rc) return rc;                                                                    \
+    kern<<<grid, kAttnThreads, FwdSmem<D_>::kBytes, stream>>>(tq, tk, tv, p);             \
+  }
+  if (D == 64) { if (is_fp16) SFL_FWD(64, true) else SFL_FWD(64, false) }
+  else { if (is_fp16) SFL_FWD(128, true) else SFL_FWD(128, false) }
+#undef SFL_FWD
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int sfl_attn_bwd(const SflAttnTensor* q, const SflAttnTensor* k, const SflAttnTensor* v,
+                            const SflAttnTensor* o, const SflAttnTensor* d_o, const float* lse,
+                            float* delta, const SflAttnTensor* dq, const SflAttnTensor* dk,
+                            const SflAttnTensor* dv, int B, int H, int N, int D, float scale,
+                            const SflAttnMask* mask, int is_fp16, int* status, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if ((D != 64 && D != 128) || B <= 0 || H <= 0 || N <= 0 || mask == nullptr) return -2;
+  for (const SflAttnTensor* t : {q, k, v, o, d_o, dq, dk, dv})
+    if (!strides_ok(*t)) return -2;
+  // dO must share O's strides; dq/dk/dv share one stride triple.
+  if (o->stride_b != d_o->stride_b || o->stride_h != d_o->stride_h || o->stride_t != d_o->stride_t)
+    return -2;
+  if (dq->stride_b != dk->stride_b || dq->stride_b != dv->stride_b || dq->stride_h != dk->stride_h ||
+      dq->stride_h != dv->stride_h || dq->stride_t != dk->stride_t || dq->stride_t != dv->stride_t)
+    return -2;
+  if (mask->mode == 0 && (mask->t_row_ptr == nullptr || mask->t_col_idx == nullptr)) return -2;
+  CUtensorMap tq, tk, tv, tdo;
+  if (make_map(&tq, q->ptr, *q, B, H, N, D) || make_map(&tk, k->ptr, *k, B, H, N, D) ||
+      make_map(&tv, v->ptr, *v, B, H, N, D) || make_map(&tdo, d_o->ptr, *d_o, B, H, N, D))
+    return -3;
+  {
+    const long rows = static_cast<long>(B) * H * N;
+    const int warps = 8;
+    const unsigned blocks = static_cast<unsigned>((rows + warps - 1) / warps);
+    if (is_fp16)
+      attn_delta_kernel<true><<<blocks, warps * 32, 0, stream>>>(
+          o->ptr, d_o->ptr, delta, B, H, N, D, o->stride_b, o->stride_h, o->stride_t);
+    else
+      attn_delta_kernel<false><<<blocks, warps * 32, 0, stream>>>(
+          o->ptr, d_o->ptr, delta, B, H, N, D, o->stride_b, o->stride_h, o->stride_t);
+  }
+  AttnParams p{};
+  p.B = B; p.H = H; p.N = N; p.scale = scale;
+  p.lse = const_cast<float*>(lse); p.delta = delta;
+  p.dq = dq->ptr; p.dk = dk->ptr; p.dv = dv->ptr;
+  p.g_sb = dq->stride_b; p.g_sh = dq->stride_h; p.g_st = dq->stride_t;
+  p.is_fp16 = is_fp16; p.status = status;
+  dim3 grid((N + kTile - 1) / kTile, B * H);
+#define SFL_BWD(D_, F_)                                                                       \
+  {                                                                                           \
+    auto kq = attn_bwd_kernel<D_, F_, false>;                                                 \
+    auto kkv = attn_bwd_kernel<D_, F_, true>;                                                 \
+    int rc = set_smem(kq, BwdSmem<D_>::kBytes);                                               \
+    if (rc) return rc;                                                                        \
+    rc = set_smem(kkv, BwdSmem<D_>::kBytes);                                                  \
+    if (rc) return rc;                                                                        \
+    p.sched = to_sched(mask, false);                                                          \
+    kq<<<grid, kAttnThreads, BwdSmem<D_>::kBytes, stream>>>(tq, tdo, tk, tv, p);              \
+    p.sched = to_sched(mask, true);                                                           \
+    kkv<<<grid, kAttnThreads, BwdSmem<D_>::kBytes, stream>>>(tk, tv, tq, tdo, p);             \
+  }
+  if (D == 64) { if (is_fp16) SFL_BWD(64, true) else SFL_BWD(64, false) }
+  else { if (is_fp16) SFL_BWD(128, true) else SFL_BWD(128, false) }
+#undef SFL_BWD
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int sfl_rope_bwd(void* x_bf16, long ld, const float* cos, const float* sin, long rows,
+                            int cols, int T, int head_dim, void* stream_) {
+  if (rows <= 0 || cols <= 0) return 0;
+  const long pairs = rows * (cols / 2);
+  long blocks = (pairs + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  rope_bwd_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+      static_cast<__nv_bfloat16*>(x_bf16), ld, cos, sin, rows, cols, T, head_dim);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -89,6 +89,50 @@ int sfl_adamw(float* p, const float* g, float* m, float* v, void* bf16_shadow, l
               float beta1, float beta2, float eps, float weight_decay, float bias1, float bias2,
               const float* grad_coef, float grad_scale, const float* ok_flag, void* stream);
 
+/* ------------------------------------------------------------- attention -- */
+/* A [B,H,N,D] view with D contiguous; strides in elements. */
+typedef struct SflAttnTensor {
+  void* ptr;
+  long stride_b, stride_h, stride_t;
+} SflAttnTensor;
+
+/* Block schedule at 128x128 tile granularity plus the token-level predicate.
+ * mode 0: CSR over query tiles (row_ptr/col_idx/full[/bitmap]) and, for the
+ * backward pass, its transpose over key tiles (t_*).  bitmap (optional) holds
+ * one bit per 16x16 sub-block, bit index = (query_sub * 8 + key_sub); absent
+ * sub-blocks are masked.  mode 1: interval schedule derived from the windows.
+ * window_* = -1 means unbounded.  doc (optional) = int32 label per position. */
+typedef struct SflAttnMask {
+  int mode;
+  int causal;
+  int window_left;
+  int window_right;
+  const int* doc;
+  const int* row_ptr;
+  const int* col_idx;
+  const uint8_t* full;
+  const uint64_t* bitmap;
+  const int* t_row_ptr;
+  const int* t_col_idx;
+  const uint8_t* t_full;
+  const uint64_t* t_bitmap;
+} SflAttnMask;
+
+/* O = softmax(scale * Q K^T + mask) V; lse (may be NULL) fp32 [B,H,N] natural log.
+ * 16-bit inputs (bf16, or fp16 when is_fp16), D in {64, 128}. */
+int sfl_attn_fwd(const SflAttnTensor* q, const SflAttnTensor* k, const SflAttnTensor* v,
+                 const SflAttnTensor* o, float* lse, int B, int H, int N, int D, float scale,
+                 const SflAttnMask* mask, int is_fp16, int* status, void* stream);
+/* Gradients of the above.  delta is fp32 [B,H,N] scratch owned by the caller. */
+int sfl_attn_bwd(const SflAttnTensor* q, const SflAttnTensor* k, const SflAttnTensor* v,
+                 const SflAttnTensor* o, const SflAttnTensor* d_o, const float* lse, float* delta,
+                 const SflAttnTensor* dq, const SflAttnTensor* dk, const SflAttnTensor* dv, int B,
+                 int H, int N, int D, float scale, const SflAttnMask* mask, int is_fp16,
+                 int* status, void* stream);
+/* In-place inverse rotary embedding on the first `cols` columns of bf16 x[rows, ld]. */
+int sfl_rope_bwd(void* x_bf16, long ld, const float* cos, const float* sin, long rows, int cols,
+                 int T, int head_dim, void* stream);
+
 /* ------------------------------------------------------------------ misc -- */
 int sfl_cast_f32_to_bf16(const float* x, void* y_bf16, long n, void* stream);
 int sfl_scale_f32(float* x, long n, const float* coef_dev, float scale, void* stream);

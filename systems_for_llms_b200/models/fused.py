@@ -1,0 +1,416 @@
+"""The sm_100a execution engine behind ``TransformerLM`` on a B200.
+
+Design (none of this exists in the reference, which runs every operator as an
+eager PyTorch call: src/llmlab/model/transformer.py:121-139):
+
+* **Flat storage.**  All parameters are re-pointed into one fp32 buffer (the
+  ``nn.Parameter`` objects and ``state_dict`` keys are untouched), with q|k|v
+  and w1|w3 adjacent so the fused projections see one matrix.  A bf16 shadow
+  of the same layout feeds the tensor cores; it is refreshed by the fused
+  optimizer, or by a cast when a parameter was modified through PyTorch.
+  Gradients live in a second flat fp32 buffer that weight-gradient GEMMs
+  accumulate into directly, and that data-parallel wrappers reduce in place.
+* **One autograd node per block.**  Forward is seven kernels (norm, q|k|v+RoPE
+  GEMM, flash attention, output GEMM+residual, norm, w1|w3 GEMM+SwiGLU, w2
+  GEMM+residual); backward is the matching hand-written chain.  With
+  ``activation_checkpointing="block"`` the node stores only its input and
+  replays the forward inside backward.
+* **Fused head.**  Final norm, vocabulary GEMM, log-sum-exp, loss and the logit
+  gradient are one node; fp32 logits never exist.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..attention import flash
+from ..ops import functional as K
+from ..ops import gemm as G
+from ..ops import lib as _lib
+
+ALIGN = 64  # elements; keeps every parameter 256-byte (fp32) / 128-byte (bf16) aligned
+
+
+def autocast_bf16_active() -> bool:
+    return (torch.is_autocast_enabled("cuda")
+            and torch.get_autocast_dtype("cuda") == torch.bfloat16)
+
+
+def eligible(model) -> bool:
+    """Shapes and placement the kernels support; otherwise the portable path runs."""
+    if not _lib.available():
+        return False
+    params = list(model.parameters())
+    if not params or any((not p.is_cuda) or p.dtype != torch.float32 for p in params):
+        return False
+    if len({p.device for p in params}) != 1:
+        return False
+    d_k = model.d_model // model.num_heads
+    return (model.d_model % 64 == 0 and d_k in (64, 128) and model.d_ff % 8 == 0
+            and model.vocab_size >= 8 and all(layer.attn.rope is not None for layer in model.layers)
+            and not getattr(model, "_tp_parallelized", False))
+
+
+def _round_up(value: int, multiple: int) -> int:
+    return -(-value // multiple) * multiple
+
+
+class FusedEngine:
+    def __init__(self, model):
+        self.model = model
+        self.device = next(model.parameters()).device
+        self.d_model, self.num_heads = model.d_model, model.num_heads
+        self.d_k = model.d_model // model.num_heads
+        self.d_ff, self.vocab = model.d_ff, model.vocab_size
+        self._layout()
+        self._flatten()
+        self.flat_grad: torch.Tensor | None = None
+        self._versions = None
+        self._bf16_alias: tuple[int, torch.Tensor] | None = None
+        self.on_block_backward = None   # hook(layer_index) for gradient-reduction overlap
+        rope = model.layers[0].attn.rope
+        # Tables hold the bf16-rounded values the reference multiplies with.
+        self.cos = rope.cos.to(torch.bfloat16).to(torch.float32).contiguous()
+        self.sin = rope.sin.to(torch.bfloat16).to(torch.float32).contiguous()
+
+    # ---------------------------------------------------------------- layout --
+    def _layout(self) -> None:
+        model = self.model
+        order = []
+        for layer in model.layers:
+            order += [layer.attn_norm.weight, layer.attn.q_proj.weight, layer.attn.k_proj.weight,
+                      layer.attn.v_proj.weight, layer.attn.output_proj.weight,
+                      layer.ffn_norm.weight, layer.ffn.w1.weight, layer.ffn.w3.weight,
+                      layer.ffn.w2.weight]
+        order += [model.token_embeddings.weight, model.ln_final.weight, model.lm_head.weight]
+        self.params = order
+        self.offsets: dict[int, int] = {}
+        cursor = 0
+        for p in order:
+            self.offsets[id(p)] = cursor
+            cursor += _round_up(p.numel(), ALIGN)
+        self.total = cursor
+        # Layer boundaries in the flat buffers (for bucketed gradient reduction).
+        self.layer_ranges = []
+        for layer in model.layers:
+            begin = self.offsets[id(layer.attn_norm.weight)]
+            end = self.offsets[id(layer.ffn.w2.weight)] + _round_up(layer.ffn.w2.weight.numel(), ALIGN)
+            self.layer_ranges.append((begin, end))
+        self.tail_range = (self.offsets[id(model.token_embeddings.weight)], self.total)
+
+    def _flatten(self) -> None:
+        flat = torch.zeros(self.total, dtype=torch.float32, device=self.device)
+        for p in self.params:
+            view = self._slice(flat, p)
+            view.copy_(p.data)
+            p.data = view
+        self.flat_param = flat
+        self.flat_shadow = torch.empty(self.total, dtype=torch.bfloat16, device=self.device)
+
+    def _slice(self, flat: torch.Tensor, p: torch.Tensor) -> torch.Tensor:
+        begin = self.offsets[id(p)]
+        return flat[begin:begin + p.numel()].view(p.shape)
+
+    def shadow(self, p: torch.Tensor, rows: int | None = None) -> torch.Tensor:
+        """bf16 view of ``p``; ``rows`` extends it over adjacent matrices (q|k|v, w1|w3)."""
+        begin = self.offsets[id(p)]
+        rows = p.shape[0] if rows is None else rows
+        return self.flat_shadow[begin:begin + rows * p.shape[1]].view(rows, p.shape[1])
+
+    def relocate(self, flat_param: torch.Tensor | None = None,
+                 flat_grad: torch.Tensor | None = None) -> None:
+        """Move parameters / gradients into caller-provided flat buffers (for
+        example peer-mapped memory owned by a data-parallel wrapper)."""
+        if flat_param is not None:
+            if flat_param.numel() < self.total or flat_param.dtype != torch.float32:
+                raise ValueError("parameter buffer too small or not fp32")
+            flat_param[:self.total].copy_(self.flat_param)
+            for p in self.params:
+                p.data = self._slice(flat_param, p)
+            self.flat_param = flat_param
+        if flat_grad is not None:
+            if flat_grad.numel() < self.total or flat_grad.dtype != torch.float32:
+                raise ValueError("gradient buffer too small or not fp32")
+            self.flat_grad = flat_grad
+            for p in self.params:
+                if p.grad is not None:
+                    view = self._slice(flat_grad, p)
+                    view.copy_(p.grad)
+                    p.grad = view
+
+    # ------------------------------------------------------------- gradients --
+    def grad_buffer(self) -> torch.Tensor:
+        if self.flat_grad is None:
+            self.flat_grad = torch.zeros(self.total, dtype=torch.float32, device=self.device)
+        return self.flat_grad
+
+    def grad_view(self, p: torch.Tensor, rows: int | None = None) -> torch.Tensor:
+        begin = self.offsets[id(p)]
+        if rows is None:
+            return self.grad_buffer()[begin:begin + p.numel()].view(p.shape)
+        return self.grad_buffer()[begin:begin + rows * p.shape[1]].view(rows, p.shape[1])
+
+    def claim(self, *params: torch.Tensor) -> bool:
+        """Attach the flat views as ``.grad`` and say whether to accumulate.
+
+        A parameter whose ``.grad`` is ``None`` (after ``zero_grad``) starts a new
+        accumulation: the first kernel overwrites instead of adding, so the flat
+        buffer never needs a separate clearing pass.
+        """
+        fresh = [p.grad is None for p in params]
+        if any(fresh) and not all(fresh):
+            # Mixed state inside one fused matrix: zero the stragglers, then add.
+            for p, is_fresh in zip(params, fresh):
+                if is_fresh:
+                    self.grad_view(p).zero_()
+        accumulate = not all(fresh)
+        for p in params:
+            view = self.grad_view(p)
+            if p.grad is None or p.grad.data_ptr() != view.data_ptr():
+                if p.grad is not None:
+                    view.copy_(p.grad)
+                p.grad = view
+        return accumulate
+
+    # ---------------------------------------------------------------- shadow --
+    def sync_shadow(self) -> None:
+        """Re-cast fp32 -> bf16 if any parameter changed through PyTorch."""
+        versions = tuple(p._version for p in self.params)
+        if versions != self._versions:
+            K.cast_bf16(self.flat_param, self.flat_shadow)
+            self._versions = versions
+
+    def mark_shadow_current(self) -> None:
+        """Called by the fused optimizer, which writes the shadow itself."""
+        self._versions = tuple(p._version for p in self.params)
+
+    # --------------------------------------------------------------- forward --
+    def _prepare(self, input_ids: torch.Tensor):
+        self.sync_shadow()
+        ids = input_ids.reshape(-1, input_ids.shape[-1])
+        return ids, ids.shape[0], ids.shape[1]
+
+    def _trunk(self, ids: torch.Tensor, B: int, T: int) -> torch.Tensor:
+        model = self.model
+        grad = torch.is_grad_enabled()
+        if grad:
+            x = _Embed.apply(model.token_embeddings.weight, ids, self)
+        else:
+            x = K.embedding(model.token_embeddings.weight, ids)
+        recompute = model.activation_checkpointing == "block" and model.training and grad
+        for index in range(len(model.layers)):
+            if grad:
+                x = _Block.apply(x, self, index, B, T, recompute)
+            else:
+                x = block_forward(self, index, x, B, T)[0]
+        return x
+
+    def logits(self, input_ids: torch.Tensor) -> torch.Tensor:
+        ids, B, T = self._prepare(input_ids)
+        x = self._trunk(ids, B, T)
+        if torch.is_grad_enabled():
+            out = _Logits.apply(x, self)
+        else:
+            out = head_logits(self, x)[0]
+        return out[:, :self.vocab].reshape(*input_ids.shape, self.vocab)
+
+    def loss(self, input_ids: torch.Tensor, targets: torch.Tensor, scale: float) -> torch.Tensor:
+        ids, B, T = self._prepare(input_ids)
+        x = self._trunk(ids, B, T)
+        flat_targets = targets.reshape(-1).contiguous()
+        if torch.is_grad_enabled():
+            return _HeadLoss.apply(x, flat_targets, self, float(scale))
+        logits = head_logits(self, x)[0]
+        rows = K.cross_entropy_rows(logits, flat_targets, self.vocab, None, 0.0)
+        return rows.sum() * (scale / rows.numel())
+
+
+# ------------------------------------------------------------ block kernels --
+def block_forward(engine: FusedEngine, index: int, x: torch.Tensor, B: int, T: int):
+    """Returns ``(x_out, saved)`` where ``saved`` holds what backward needs."""
+    layer = engine.model.layers[index]
+    d, dk, H, dff = engine.d_model, engine.d_k, engine.num_heads, engine.d_ff
+    M = B * T
+    x2 = x.reshape(M, d)
+    h1, rstd1 = K.rmsnorm(x2, layer.attn_norm.weight, layer.attn_norm.eps)
+    wqkv = engine.shadow(layer.attn.q_proj.weight, 3 * d)
+    qkv = G.linear_fwd_rope(h1, wqkv, engine.cos, engine.sin, T, 2 * d, dk)
+    heads = qkv.view(B, T, 3, H, dk)
+    q, k, v = (heads[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    attn = torch.empty(M, d, dtype=torch.bfloat16, device=x.device)
+    lse = torch.empty(B, H, T, dtype=torch.float32, device=x.device)
+    mask = flash.causal_mask(x.device, T)
+    flash.flash_fwd(q, k, v, attn.view(B, T, H, dk).permute(0, 2, 1, 3), lse, mask, dk ** -0.5)
+    x_mid = G.linear_fwd_resid(attn, engine.shadow(layer.attn.output_proj.weight), x2)
+    h2, rstd2 = K.rmsnorm(x_mid, layer.ffn_norm.weight, layer.ffn_norm.eps)
+    g, a13 = G.swiglu_fwd(h2, engine.shadow(layer.ffn.w1.weight, 2 * dff), dff)
+    x_out = G.linear_fwd_resid(g, engine.shadow(layer.ffn.w2.weight), x_mid)
+    saved = (x2, rstd1, h1, qkv, attn, lse, x_mid, rstd2, h2, a13, g)
+    return x_out.view(B, T, d), saved
+
+
+def block_backward(engine: FusedEngine, index: int, saved, d_out: torch.Tensor, B: int, T: int):
+    layer = engine.model.layers[index]
+    d, dk, H, dff = engine.d_model, engine.d_k, engine.num_heads, engine.d_ff
+    M = B * T
+    x2, rstd1, h1, qkv, attn, lse, x_mid, rstd2, h2, a13, g = saved
+    dres = d_out.reshape(M, d)
+    if not dres.is_contiguous():
+        dres = dres.contiguous()
+    alias = engine._bf16_alias
+    if alias is not None and alias[0] == dres.data_ptr():
+        dres_bf16 = alias[1]
+    else:
+        dres_bf16 = K.cast_bf16(dres)
+    engine._bf16_alias = None
+    attn_p, ffn = layer.attn, layer.ffn
+
+    # ---- feed-forward half
+    d13 = G.swiglu_bwd(dres_bf16, engine.shadow(ffn.w2.weight), a13)
+    acc = engine.claim(ffn.w2.weight)
+    G.linear_wgrad(dres_bf16, g, engine.grad_view(ffn.w2.weight), acc)
+    dh2 = G.linear_dgrad(d13, engine.shadow(ffn.w1.weight, 2 * dff))
+    acc = engine.claim(ffn.w1.weight, ffn.w3.weight)
+    G.linear_wgrad(d13, h2, engine.grad_view(ffn.w1.weight, 2 * dff), acc)
+    acc = engine.claim(layer.ffn_norm.weight)
+    dres2, dres2_bf16 = K.rmsnorm_bwd(dh2, x_mid, layer.ffn_norm.weight, rstd2, dres,
+                                      engine.grad_view(layer.ffn_norm.weight), acc, want_bf16=True)
+    # ---- attention half
+    d_attn = G.linear_dgrad(dres2_bf16, engine.shadow(attn_p.output_proj.weight))
+    acc = engine.claim(attn_p.output_proj.weight)
+    G.linear_wgrad(dres2_bf16, attn, engine.grad_view(attn_p.output_proj.weight), acc)
+    dqkv = torch.empty_like(qkv)
+    heads = qkv.view(B, T, 3, H, dk)
+    dheads = dqkv.view(B, T, 3, H, dk)
+    q, k, v = (heads[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    dq, dkk, dv = (dheads[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    as_heads = lambda t: t.view(B, T, H, dk).permute(0, 2, 1, 3)
+    mask = flash.causal_mask(d_out.device, T)
+    flash.flash_bwd(q, k, v, as_heads(attn), as_heads(d_attn), lse, dq, dkk, dv, mask, dk ** -0.5)
+    flash.rope_bwd_(dqkv, engine.cos, engine.sin, T, 2 * d, dk)
+    dh1 = G.linear_dgrad(dqkv, engine.shadow(attn_p.q_proj.weight, 3 * d))
+    acc = engine.claim(attn_p.q_proj.weight, attn_p.k_proj.weight, attn_p.v_proj.weight)
+    G.linear_wgrad(dqkv, h1, engine.grad_view(attn_p.q_proj.weight, 3 * d), acc)
+    acc = engine.claim(layer.attn_norm.weight)
+    dx, dx_bf16 = K.rmsnorm_bwd(dh1, x2, layer.attn_norm.weight, rstd1, dres2,
+                                engine.grad_view(layer.attn_norm.weight), acc, want_bf16=True)
+    engine._bf16_alias = (dx.data_ptr(), dx_bf16)
+    if engine.on_block_backward is not None:
+        engine.on_block_backward(index)
+    return dx.view(B, T, d)
+
+
+def head_logits(engine: FusedEngine, x: torch.Tensor):
+    model = engine.model
+    x2 = x.reshape(-1, engine.d_model)
+    h, rstd = K.rmsnorm(x2, model.ln_final.weight, model.ln_final.eps)
+    ld = _round_up(engine.vocab, 8)
+    logits = torch.empty(x2.shape[0], ld, dtype=torch.bfloat16, device=x.device)
+    G.linear_fwd(h, engine.shadow(model.lm_head.weight), logits)
+    return logits, (x2, h, rstd)
+
+
+def head_backward(engine: FusedEngine, saved, dlogits: torch.Tensor) -> torch.Tensor:
+    """``dlogits`` is bf16 ``[M, ld]`` (columns beyond the vocabulary are ignored)."""
+    model = engine.model
+    x2, h, rstd = saved
+    V = engine.vocab
+    w = engine.shadow(model.lm_head.weight)
+    dl = dlogits[:, :V] if dlogits.shape[1] != V else dlogits
+    dh = torch.empty_like(h)
+    epi = G.GemmEpilogue(kind=G.EPI_BF16, out=dh.data_ptr(), ldo=dh.stride(0))
+    G.gemm(dl, w, h.shape[0], engine.d_model, V, epi, b_mn=True)
+    acc = engine.claim(model.lm_head.weight)
+    grad = engine.grad_view(model.lm_head.weight)
+    epi = G.GemmEpilogue(kind=G.EPI_F32, beta=int(acc), out=grad.data_ptr(), ldo=grad.stride(0))
+    G.gemm(dl, h, V, engine.d_model, h.shape[0], epi, a_mn=True, b_mn=True)
+    acc = engine.claim(model.ln_final.weight)
+    dx, dx_bf16 = K.rmsnorm_bwd(dh, x2, model.ln_final.weight, rstd, None,
+                                engine.grad_view(model.ln_final.weight), acc, want_bf16=True)
+    engine._bf16_alias = (dx.data_ptr(), dx_bf16)
+    return dx
+
+
+# ------------------------------------------------------------ autograd nodes --
+class _Embed(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, weight, ids, engine):
+        ctx.engine = engine
+        ctx.save_for_backward(ids)
+        ctx.weight = weight
+        return K.embedding(weight, ids)
+
+    @staticmethod
+    def backward(ctx, grad):
+        (ids,) = ctx.saved_tensors
+        engine, weight = ctx.engine, ctx.weight
+        dense = torch.ops.aten.embedding_dense_backward(
+            grad.reshape(-1, grad.shape[-1]), ids.reshape(-1), weight.shape[0], -1, False)
+        accumulate = engine.claim(weight)
+        view = engine.grad_view(weight)
+        if accumulate:
+            view.add_(dense)
+        else:
+            view.copy_(dense)
+        if engine.on_block_backward is not None:
+            engine.on_block_backward(-1)
+        return None, None, None
+
+
+class _Block(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, engine, index, B, T, recompute):
+        out, saved = block_forward(engine, index, x, B, T)
+        ctx.engine, ctx.index, ctx.B, ctx.T, ctx.recompute = engine, index, B, T, recompute
+        if recompute:
+            ctx.save_for_backward(x)
+        else:
+            ctx.save_for_backward(*saved)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        if ctx.recompute:
+            (x,) = ctx.saved_tensors
+            saved = block_forward(ctx.engine, ctx.index, x, ctx.B, ctx.T)[1]
+        else:
+            saved = ctx.saved_tensors
+        dx = block_backward(ctx.engine, ctx.index, saved, grad, ctx.B, ctx.T)
+        return dx, None, None, None, None, None
+
+
+class _Logits(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, engine):
+        logits, saved = head_logits(engine, x)
+        ctx.engine = engine
+        ctx.shape = x.shape
+        ctx.save_for_backward(*saved)
+        return logits
+
+    @staticmethod
+    def backward(ctx, grad):
+        grad = grad.contiguous() if not grad.is_contiguous() else grad
+        dx = head_backward(ctx.engine, ctx.saved_tensors, grad.to(torch.bfloat16))
+        return dx.view(ctx.shape), None
+
+
+class _HeadLoss(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, targets, engine, scale):
+        logits, saved = head_logits(engine, x)
+        rows = logits.shape[0]
+        # The logit gradient overwrites the logits: one pass produces both.
+        losses = K.cross_entropy_rows(logits, targets, engine.vocab, logits, scale / rows)
+        ctx.engine, ctx.shape = engine, x.shape
+        ctx.save_for_backward(logits, *saved)
+        return losses.sum() * (scale / rows)
+
+    @staticmethod
+    def backward(ctx, grad):
+        dlogits, *saved = ctx.saved_tensors
+        dlogits.mul_(grad.to(torch.bfloat16))
+        dx = head_backward(ctx.engine, saved, dlogits)
+        return dx.view(ctx.shape), None, None, None
