@@ -1,0 +1,4 @@
+"""Import-compatible name for ``systems_for_llms_b200.attention.masks`` (same public functions as the reference's module of this name)."""
+
+from systems_for_llms_b200.attention.masks import *  # noqa: F401,F403
+from systems_for_llms_b200.attention.masks import __doc__ as _target_doc  # noqa: F401

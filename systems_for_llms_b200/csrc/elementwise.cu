@@ -97,9 +97,82 @@ __global__ void rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __r
 constexpr int kNormBwdBlocks = 296;  // two CTAs per SM on a 148-SM part
 constexpr int kNormBwdThreads = 256;
 
-// Each block owns a strided set of rows (one warp per row at a time) and keeps a
-// per-thread partial of dw for the columns it touches; partials are combined
-// across the block's warps in shared memory in a fixed order.
+// Each block owns a strided set of rows, one warp per row at a time.  A lane
+// always touches the same columns (4 consecutive elements every 128), so the
+// weight-gradient partial lives in registers across rows; the row itself is
+// read once and kept in registers between the dot-product and the update.
+// NCH = dim / 128 (dim must be a multiple of 128 and at most 1024 here).
+template <int NCH>
+__global__ void __launch_bounds__(kNormBwdThreads)
+rmsnorm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const float* __restrict__ x,
+                       const float* __restrict__ w, const float* __restrict__ rstd,
+                       const float* __restrict__ dres_in, float* __restrict__ dx_out,
+                       __nv_bfloat16* __restrict__ dx_bf16, float* __restrict__ dw_partial,
+                       int rows) {
+  constexpr int dim = NCH * 128;
+  extern __shared__ float dw_smem[];  // [warps, dim]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps = blockDim.x >> 5;
+  float4 wv[NCH], dwv[NCH];
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    wv[c] = *reinterpret_cast<const float4*>(w + c * 128 + lane * 4);
+    dwv[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  for (int row = blockIdx.x * warps + warp; row < rows; row += gridDim.x * warps) {
+    const long off = static_cast<long>(row) * dim;
+    const float inv = rstd[row];
+    float4 xh[NCH], g[NCH];
+    float dot = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int col = c * 128 + lane * 4;
+      const float4 xv = *reinterpret_cast<const float4*>(x + off + col);
+      const uint2 dq = *reinterpret_cast<const uint2*>(dy + off + col);
+      const float2 d01 = unpack_bf16(dq.x), d23 = unpack_bf16(dq.y);
+      xh[c] = make_float4(xv.x * inv, xv.y * inv, xv.z * inv, xv.w * inv);
+      g[c] = make_float4(d01.x, d01.y, d23.x, d23.y);
+      dot += g[c].x * wv[c].x * xh[c].x + g[c].y * wv[c].y * xh[c].y +
+             g[c].z * wv[c].z * xh[c].z + g[c].w * wv[c].w * xh[c].w;
+    }
+    dot = warp_sum(dot) / static_cast<float>(dim);
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int col = c * 128 + lane * 4;
+      float4 d;
+      d.x = inv * (g[c].x * wv[c].x - xh[c].x * dot);
+      d.y = inv * (g[c].y * wv[c].y - xh[c].y * dot);
+      d.z = inv * (g[c].z * wv[c].z - xh[c].z * dot);
+      d.w = inv * (g[c].w * wv[c].w - xh[c].w * dot);
+      if (dres_in != nullptr) {
+        const float4 r = *reinterpret_cast<const float4*>(dres_in + off + col);
+        d.x += r.x; d.y += r.y; d.z += r.z; d.w += r.w;
+      }
+      *reinterpret_cast<float4*>(dx_out + off + col) = d;
+      if (dx_bf16 != nullptr) {
+        uint2 o;
+        o.x = pack_bf16(d.x, d.y);
+        o.y = pack_bf16(d.z, d.w);
+        *reinterpret_cast<uint2*>(dx_bf16 + off + col) = o;
+      }
+      dwv[c].x += g[c].x * xh[c].x;
+      dwv[c].y += g[c].y * xh[c].y;
+      dwv[c].z += g[c].z * xh[c].z;
+      dwv[c].w += g[c].w * xh[c].w;
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < NCH; ++c)
+    *reinterpret_cast<float4*>(dw_smem + static_cast<long>(warp) * dim + c * 128 + lane * 4) = dwv[c];
+  __syncthreads();
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    float s = 0.f;
+    for (int k = 0; k < warps; ++k) s += dw_smem[static_cast<long>(k) * dim + i];
+    dw_partial[static_cast<long>(blockIdx.x) * dim + i] = s;
+  }
+}
+
+// Generic fallback for any row width.
 __global__ void __launch_bounds__(kNormBwdThreads)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const float* __restrict__ x,
                    const float* __restrict__ w, const float* __restrict__ rstd,
@@ -342,9 +415,24 @@ extern "C" int sfl_rmsnorm_bwd(const void* dy, const float* x, const float* w, c
                          200 * 1024);
     configured = true;
   }
-  rmsnorm_bwd_kernel<<<blocks, kNormBwdThreads, smem, SFL_STREAM(stream)>>>(
-      static_cast<const __nv_bfloat16*>(dy), x, w, rstd, dres_in, dx_out,
-      static_cast<__nv_bfloat16*>(dx_bf16), dw_partial, rows, dim);
+  const __nv_bfloat16* dyp = static_cast<const __nv_bfloat16*>(dy);
+  __nv_bfloat16* dxb = static_cast<__nv_bfloat16*>(dx_bf16);
+  cudaStream_t st = SFL_STREAM(stream);
+#define SFL_NORM_BWD(NCH)                                                                     \
+  case NCH:                                                                                   \
+    rmsnorm_bwd_vec_kernel<NCH><<<blocks, kNormBwdThreads, smem, st>>>(                       \
+        dyp, x, w, rstd, dres_in, dx_out, dxb, dw_partial, rows);                             \
+    break;
+  if (dim % 128 == 0 && dim <= 1024) {
+    switch (dim / 128) {
+      SFL_NORM_BWD(1) SFL_NORM_BWD(2) SFL_NORM_BWD(3) SFL_NORM_BWD(4)
+      SFL_NORM_BWD(5) SFL_NORM_BWD(6) SFL_NORM_BWD(7) SFL_NORM_BWD(8)
+    }
+  } else {
+    rmsnorm_bwd_kernel<<<blocks, kNormBwdThreads, smem, st>>>(dyp, x, w, rstd, dres_in, dx_out,
+                                                              dxb, dw_partial, rows, dim);
+  }
+#undef SFL_NORM_BWD
   SFL_RET();
 }
 

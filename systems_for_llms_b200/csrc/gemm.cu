@@ -231,32 +231,47 @@ struct EpilogueOp<EPI_SWIGLU> {
   }
 };
 
+// Loads 32 consecutive bf16 values of a row as fp32 (vectorised when aligned).
+__device__ __forceinline__ void load_bf16_row(const __nv_bfloat16* src, float (&v)[32], int col0,
+                                              int N, bool vec_ok) {
+  if (vec_ok && col0 + 32 <= N) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint4 q = *reinterpret_cast<const uint4*>(src + 8 * j);
+      const float2 a = unpack_bf16(q.x), b = unpack_bf16(q.y), c = unpack_bf16(q.z),
+                   d = unpack_bf16(q.w);
+      v[8 * j + 0] = a.x; v[8 * j + 1] = a.y; v[8 * j + 2] = b.x; v[8 * j + 3] = b.y;
+      v[8 * j + 4] = c.x; v[8 * j + 5] = c.y; v[8 * j + 6] = d.x; v[8 * j + 7] = d.y;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = col0 + j < N ? __bfloat162float(src[j]) : 0.f;
+  }
+}
+
 template <>
 struct EpilogueOp<EPI_SWIGLU_BWD> {
   static __device__ __forceinline__ void apply(const GemmParams& p, int row, int col0,
                                                float (&v)[32], float (&)[32]) {
     const __nv_bfloat16* a13 =
         static_cast<const __nv_bfloat16*>(p.aux) + static_cast<long>(row) * p.ldaux;
-    float d1[32], d3[32];
+    const bool vec_in = (p.ldaux & 7) == 0 && (p.N & 7) == 0;
+    float a1[32], a3[32];
+    load_bf16_row(a13 + col0, a1, col0, p.N, vec_in);
+    load_bf16_row(a13 + p.N + col0, a3, col0, p.N, vec_in);
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
-      if (col0 + j < p.N) {
-        const float a = __bfloat162float(a13[col0 + j]);
-        const float b = __bfloat162float(a13[p.N + col0 + j]);
-        const float dg = bf16_round(v[j]);
-        const float sig = 1.0f / (1.0f + __expf(-a));
-        const float silu = a * sig;
-        d3[j] = dg * silu;
-        d1[j] = dg * b * (sig + silu * (1.0f - sig));
-      } else {
-        d1[j] = 0.f;
-        d3[j] = 0.f;
-      }
+      const float a = a1[j];
+      const float dg = bf16_round(v[j]);
+      const float sig = 1.0f / (1.0f + __expf(-a));
+      const float silu = a * sig;
+      a1[j] = dg * a3[j] * (sig + silu * (1.0f - sig));  // d a1
+      a3[j] = dg * silu;                                  // d a3
     }
     __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + static_cast<long>(row) * p.ldo;
     const bool vec = (p.ldo & 7) == 0 && (p.N & 7) == 0;
-    store_bf16_row(dst + col0, d1, col0, p.N, vec);
-    store_bf16_row(dst + p.N + col0, d3, col0, p.N, vec);
+    store_bf16_row(dst + col0, a1, col0, p.N, vec);
+    store_bf16_row(dst + p.N + col0, a3, col0, p.N, vec);
   }
 };
 

@@ -8,6 +8,7 @@
  * `int* status` device word: 0 = ok, see StatusCode in ptx.cuh.
  */
 #pragma once
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -132,6 +133,61 @@ int sfl_attn_bwd(const SflAttnTensor* q, const SflAttnTensor* k, const SflAttnTe
 /* In-place inverse rotary embedding on the first `cols` columns of bf16 x[rows, ld]. */
 int sfl_rope_bwd(void* x_bf16, long ld, const float* cos, const float* sin, long rows, int cols,
                  int T, int head_dim, void* stream);
+
+/* --------------------------------------------------------- communication -- */
+/* Symmetric (same size on every rank) device buffers shared through CUDA IPC. */
+int sfl_ipc_alloc(void** ptr, size_t bytes);               /* cudaMalloc + zero fill  */
+int sfl_ipc_free(void* ptr);
+int sfl_ipc_get_handle(void* ptr, void* handle64);         /* 64-byte opaque handle   */
+int sfl_ipc_open_handle(const void* handle64, void** ptr); /* map a peer's buffer     */
+int sfl_ipc_close_handle(void* ptr);
+long sfl_comm_flag_bytes(void); /* size every rank's flag buffer must have           */
+int sfl_comm_slots(void);       /* independent barrier slots (one per bucket/use)    */
+int sfl_comm_max_ctas(void);
+/* Polling budget of peer waits in ~200 ns iterations (default 2^23, about 2 s). */
+int sfl_comm_set_spin_limit(unsigned iterations);
+
+typedef struct SflComm {
+  int rank, world;   /* world <= 8                                               */
+  void* data[8];     /* peer pointers of the primary symmetric buffer            */
+  void* data2[8];    /* peer pointers of a second symmetric buffer (optional)    */
+  void* flags[8];    /* peer pointers of the flag buffers (sfl_comm_flag_bytes)  */
+} SflComm;
+
+/* All functions below: `slot` selects a barrier slot, `epoch` must increase by
+ * one for each use of that slot on every rank, `ctas` sizes the grid (<= max).
+ * accumulate_partial = 1 adds this call's squared-norm partials to the slot's
+ * running partials instead of replacing them (several buckets sharing a slot).
+ * Offsets/counts are in fp32 elements (multiples of 4) unless named *_bytes. */
+
+/* data[*][offset:offset+count] <- scale * sum over ranks; squared-norm partials
+ * of the reduced values are left in the flag buffer for sfl_comm_norm_finalize. */
+int sfl_allreduce_f32(const SflComm* comm, long offset, long count, float scale, int slot,
+                      unsigned epoch, int accumulate_partial, int ctas, int* status, void* stream);
+/* Rank r reduces slice r of the range into local_out (slice-relative, compact)
+ * or in place when local_out is NULL. */
+int sfl_reduce_scatter_f32(const SflComm* comm, long offset, long count, float scale,
+                           float* local_out, int slot, unsigned epoch, int accumulate_partial,
+                           int ctas, int* status, void* stream);
+/* out[0]=global norm over the listed slots (+ *extra_sq), out[1]=clip coef, out[2]=finite. */
+int sfl_comm_norm_finalize(const SflComm* comm, const int* slots_dev, int n_slots, int ctas,
+                           float max_norm, const float* extra_sq, float* out, void* stream);
+/* AdamW on this rank's slice of data[rank][offset:offset+count] using the
+ * reduced gradient slice, then write fp32 parameters to data[*] and bf16 to data2[*]. */
+int sfl_adamw_allgather(const SflComm* comm, long offset, long count, const float* grad, float* m,
+                        float* v, float lr, float beta1, float beta2, float eps, float wd,
+                        float bias1, float bias2, const float* coef, const float* ok, int slot,
+                        unsigned epoch, int ctas, int* status, void* stream);
+/* Pull chunk r (chunk_bytes at offset_bytes + r*chunk_bytes) from every peer r. */
+int sfl_allgather_bytes(const SflComm* comm, long offset_bytes, long chunk_bytes, int slot,
+                        unsigned epoch, int ctas, int* status, void* stream);
+/* data2[*][out_off] (fp32 [rows, cols]) <- resid + bf16(sum_r data[r][in_off] (bf16)). */
+int sfl_reduce_rows_resid(const SflComm* comm, long in_off_bytes, long out_off_bytes,
+                          const float* resid, long rows, int cols, int slot, unsigned epoch,
+                          int ctas, int* status, void* stream);
+/* data2[*][out_off] (fp32, count elements) <- sum_r data[r][in_off] (fp32). */
+int sfl_allreduce_rows_f32(const SflComm* comm, long in_off_bytes, long out_off_bytes, long count,
+                           int slot, unsigned epoch, int ctas, int* status, void* stream);
 
 /* ------------------------------------------------------------------ misc -- */
 int sfl_cast_f32_to_bf16(const float* x, void* y_bf16, long n, void* stream);

@@ -69,7 +69,8 @@ class FusedEngine:
         self.flat_grad: torch.Tensor | None = None
         self._versions = None
         self._bf16_alias: tuple[int, torch.Tensor] | None = None
-        self.on_block_backward = None   # hook(layer_index) for gradient-reduction overlap
+        # hook(offset): every gradient at flat offset >= offset is final for this backward
+        self.on_block_backward = None
         rope = model.layers[0].attn.rope
         # Tables hold the bf16-rounded values the reference multiplies with.
         self.cos = rope.cos.to(torch.bfloat16).to(torch.float32).contiguous()
@@ -78,13 +79,16 @@ class FusedEngine:
     # ---------------------------------------------------------------- layout --
     def _layout(self) -> None:
         model = self.model
-        order = []
+        # Embeddings first and the head last: backward then finalises gradients from
+        # the end of the flat buffer towards its start, which is the order in which
+        # a data-parallel wrapper can reduce fixed-size buckets.
+        order = [model.token_embeddings.weight]
         for layer in model.layers:
             order += [layer.attn_norm.weight, layer.attn.q_proj.weight, layer.attn.k_proj.weight,
                       layer.attn.v_proj.weight, layer.attn.output_proj.weight,
                       layer.ffn_norm.weight, layer.ffn.w1.weight, layer.ffn.w3.weight,
                       layer.ffn.w2.weight]
-        order += [model.token_embeddings.weight, model.ln_final.weight, model.lm_head.weight]
+        order += [model.ln_final.weight, model.lm_head.weight]
         self.params = order
         self.offsets: dict[int, int] = {}
         cursor = 0
@@ -92,13 +96,13 @@ class FusedEngine:
             self.offsets[id(p)] = cursor
             cursor += _round_up(p.numel(), ALIGN)
         self.total = cursor
-        # Layer boundaries in the flat buffers (for bucketed gradient reduction).
+        # Start offset of every block and of the head in the flat buffers.
         self.layer_ranges = []
         for layer in model.layers:
             begin = self.offsets[id(layer.attn_norm.weight)]
             end = self.offsets[id(layer.ffn.w2.weight)] + _round_up(layer.ffn.w2.weight.numel(), ALIGN)
             self.layer_ranges.append((begin, end))
-        self.tail_range = (self.offsets[id(model.token_embeddings.weight)], self.total)
+        self.head_offset = self.offsets[id(model.ln_final.weight)]
 
     def _flatten(self) -> None:
         flat = torch.zeros(self.total, dtype=torch.float32, device=self.device)
@@ -298,7 +302,7 @@ def block_backward(engine: FusedEngine, index: int, saved, d_out: torch.Tensor, 
                                 engine.grad_view(layer.attn_norm.weight), acc, want_bf16=True)
     engine._bf16_alias = (dx.data_ptr(), dx_bf16)
     if engine.on_block_backward is not None:
-        engine.on_block_backward(index)
+        engine.on_block_backward(engine.layer_ranges[index][0])
     return dx.view(B, T, d)
 
 
@@ -330,6 +334,8 @@ def head_backward(engine: FusedEngine, saved, dlogits: torch.Tensor) -> torch.Te
     dx, dx_bf16 = K.rmsnorm_bwd(dh, x2, model.ln_final.weight, rstd, None,
                                 engine.grad_view(model.ln_final.weight), acc, want_bf16=True)
     engine._bf16_alias = (dx.data_ptr(), dx_bf16)
+    if engine.on_block_backward is not None:
+        engine.on_block_backward(engine.head_offset)
     return dx
 
 
@@ -355,7 +361,7 @@ class _Embed(torch.autograd.Function):
         else:
             view.copy_(dense)
         if engine.on_block_backward is not None:
-            engine.on_block_backward(-1)
+            engine.on_block_backward(0)
         return None, None, None
 
 

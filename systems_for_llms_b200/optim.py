@@ -95,6 +95,29 @@ class FusedAdamW(torch.optim.AdamW):
         return stats[0]
 
     @torch.no_grad()
+    def step_with_stats(self, stats: torch.Tensor) -> torch.Tensor:
+        """Update with a clip coefficient that is already on the device.
+
+        ``stats`` is ``[norm, coefficient, finite flag]`` as produced by the fused
+        gradient reduction (``BucketedDDP.finish``); returns the norm.
+        """
+        if not self._fused_ready():
+            raise RuntimeError("step_with_stats needs gradients in the engine's flat buffer")
+        engine = self.engine
+        self._ensure_flat_state()
+        exp_avg, exp_avg_sq, steps = self._flat_state
+        group = self.param_groups[0]
+        self._step_count = int(steps[0].item()) + 1
+        steps += 1
+        beta1, beta2 = group["betas"]
+        K.adamw_step(engine.flat_param, engine.flat_grad, exp_avg, exp_avg_sq, engine.flat_shadow,
+                     step=self._step_count, lr=group["lr"], beta1=beta1, beta2=beta2,
+                     eps=group["eps"], weight_decay=group["weight_decay"], coef=stats[1:2],
+                     ok_flag=stats[2:3])
+        engine.mark_shadow_current()
+        return stats[0]
+
+    @torch.no_grad()
     def step(self, closure=None):
         if self._flat_state is not None and self._fused_ready():
             # Gradients were clipped (or not) by the caller; plain update.
