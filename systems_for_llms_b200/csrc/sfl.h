@@ -134,6 +134,16 @@ int sfl_attn_bwd(const SflAttnTensor* q, const SflAttnTensor* k, const SflAttnTe
 int sfl_rope_bwd(void* x_bf16, long ld, const float* cos, const float* sin, long rows, int cols,
                  int T, int head_dim, void* stream);
 
+/* ---------------------------------------------------------------- decode -- */
+/* Single-token attention: q [B,Hq,D], k/v [B,Hkv,N,D] (contiguous, 16-bit),
+ * lengths int32 [B] (clamped to [0,N]), out [B,Hq,D].  Hq/Hkv in {1,2,4,8},
+ * D in {64,128}, splits in [1,128].  For splits > 1 the caller provides fp32
+ * scratch part_m/part_l [B,Hq,splits], part_u [B,Hq,splits,D] and an int32
+ * counters [B,Hkv] array that is zero on entry (the kernel leaves it zero). */
+int sfl_decode(const void* q, const void* k, const void* v, const int* lengths, float* part_m,
+               float* part_l, float* part_u, int* counters, void* out, int B, int Hq, int Hkv,
+               int N, int D, int splits, float scale, int tile_variant, int is_fp16, void* stream);
+
 /* --------------------------------------------------------- communication -- */
 /* Symmetric (same size on every rank) device buffers shared through CUDA IPC. */
 int sfl_ipc_alloc(void** ptr, size_t bytes);               /* cudaMalloc + zero fill  */

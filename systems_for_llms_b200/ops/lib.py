@@ -61,18 +61,55 @@ def register_signature(name: str, argtypes: list) -> None:
     lib.cache_clear()
 
 
+# Kernels launched per call of each entry point (default 1, 0 for host-only calls).
+_KERNELS_PER_CALL = {"sfl_attn_bwd": 3, "sfl_rmsnorm_bwd_blocks": 0, "sfl_sqnorm_blocks": 0,
+                     "sfl_ipc_alloc": 0, "sfl_ipc_free": 0, "sfl_ipc_get_handle": 0,
+                     "sfl_ipc_open_handle": 0, "sfl_ipc_close_handle": 0,
+                     "sfl_comm_set_spin_limit": 0, "sfl_comm_flag_bytes": 0, "sfl_comm_slots": 0,
+                     "sfl_comm_max_ctas": 0}
+_launches = [0]
+
+
+def launch_count() -> int:
+    """Number of this library's kernels launched by the current process so far."""
+    return _launches[0]
+
+
+class _Library:
+    """The loaded shared object with typed entry points that count their launches."""
+
+    def __init__(self, handle: ctypes.CDLL):
+        self._handle = handle
+
+    def _bind(self, name: str, argtypes: list):
+        function = getattr(self._handle, name)
+        function.argtypes = argtypes
+        function.restype = c_int
+        weight = _KERNELS_PER_CALL.get(name, 1)
+        counter = _launches
+
+        def call(*args):
+            counter[0] += weight
+            return function(*args)
+
+        setattr(self, name, call if weight else function)
+
+    def __getattr__(self, name):   # entry points without a declared signature
+        return getattr(self._handle, name)
+
+
 @lru_cache(maxsize=1)
-def lib() -> ctypes.CDLL:
+def lib() -> "_Library":
     if not _build.LIB_PATH.exists() or not _build.is_current():
         _build.build()
     handle = ctypes.CDLL(str(_build.LIB_PATH))
+    library = _Library(handle)
     for name, argtypes in {**_SIGNATURES, **_OPTIONAL}.items():
-        function = getattr(handle, name)
-        function.argtypes = argtypes
-        function.restype = c_int
+        library._bind(name, argtypes)
     handle.sfl_version.restype = c_char_p
     handle.sfl_version.argtypes = []
-    return handle
+    handle.sfl_comm_flag_bytes.restype = c_long
+    return library
 
 
 def available() -> bool:

@@ -1,0 +1,129 @@
+"""Flash attention kernels against a dense fp32 oracle (needs a B200).
+
+Tolerances follow the reference harness: forward bf16 0.02 / fp16 0.005,
+backward bf16 atol 0.025 rtol 0.035 / fp16 0.004, 0.006 (attention_lab/
+benchmark.py:227-228, backward_study.py:47).
+"""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    from systems_for_llms_b200.ops import lib
+    if not lib.available():
+        pytest.skip("kernels need a compute-capability 10.x device")
+    return torch.device("cuda")
+
+
+def dense_mask(N, spec, docs, schedule, dev):
+    q = torch.arange(N)[:, None]
+    k = torch.arange(N)[None, :]
+    mask = torch.ones(N, N, dtype=torch.bool)
+    if spec.causal:
+        mask &= k <= q
+    if spec.window_left is not None:
+        mask &= k >= q - spec.window_left
+    if spec.window_right is not None:
+        mask &= k <= q + spec.window_right
+    if spec.same_document:
+        d = torch.tensor(docs)
+        mask &= d[:, None] == d[None, :]
+    if schedule is not None:
+        keep = torch.zeros(N, N, dtype=torch.bool)
+        for r in range(len(schedule.row_ptr) - 1):
+            for e in range(schedule.row_ptr[r], schedule.row_ptr[r + 1]):
+                c = schedule.col_idx[e]
+                keep[r * schedule.block_q:(r + 1) * schedule.block_q,
+                     c * schedule.block_k:(c + 1) * schedule.block_k] = True
+        mask &= keep
+    return mask.to(dev)
+
+
+def cases():
+    from systems_for_llms_b200.attention.masks import MaskSpec, strided_schedule
+    docs = [i // 300 for i in range(1024)]
+    strided, strided_spec = strided_schedule(1024, 64, 4, 1)
+    return [
+        ("causal-256", 1, 2, 256, 64, MaskSpec(causal=True), "interval", None, None, torch.bfloat16),
+        ("causal-1024", 2, 4, 1024, 64, MaskSpec(causal=True), "interval", None, None, torch.bfloat16),
+        ("causal-d128", 1, 2, 1024, 128, MaskSpec(causal=True), "interval", None, None, torch.bfloat16),
+        ("dense-512", 1, 2, 512, 64, MaskSpec(), "interval", None, None, torch.bfloat16),
+        ("window-ragged", 1, 2, 1000, 64, MaskSpec(window_left=100, window_right=50), "interval",
+         None, None, torch.bfloat16),
+        ("causal-window-127", 1, 2, 1000, 64, MaskSpec(causal=True, window_left=127), "interval",
+         None, None, torch.bfloat16),
+        ("csr-ragged-asym", 1, 2, 777, 64, MaskSpec(causal=True), "csr", None, (64, 32),
+         torch.bfloat16),
+        ("csr-documents", 1, 2, 1024, 64, MaskSpec(causal=True, same_document=True), "csr", docs,
+         (128, 128), torch.bfloat16),
+        ("strided", 1, 2, 1024, 64, strided_spec, "csr", None, strided, torch.bfloat16),
+        ("fp16-d128", 1, 2, 512, 128, MaskSpec(causal=True), "interval", None, None, torch.float16),
+    ]
+
+
+@pytest.mark.parametrize("case", cases(), ids=lambda c: c[0])
+def test_forward_and_backward(dev, case):
+    from systems_for_llms_b200.attention import flash
+    from systems_for_llms_b200.attention.backward import training_attention
+    from systems_for_llms_b200.attention.masks import BlockSchedule, compile_mask
+    from systems_for_llms_b200.ops.gemm import check_status
+    name, B, H, N, D, spec, impl, docs, blocks, dtype = case
+    generator = torch.Generator(device=dev).manual_seed(0)
+    q, k, v = (torch.randn(B, H, N, D, device=dev, generator=generator).to(dtype) for _ in range(3))
+    schedule = None
+    if isinstance(blocks, BlockSchedule):
+        schedule = blocks
+    elif impl == "csr":
+        schedule = compile_mask(N, spec, blocks[0], blocks[1], docs)
+    mask = dense_mask(N, spec, docs, schedule if isinstance(blocks, BlockSchedule) else None, dev)
+    before = [t.clone() for t in (q, k, v)]
+    out, lse = flash.attention(q, k, v, schedule, spec, document_ids=docs, implementation=impl,
+                               return_lse=True)
+    torch.cuda.synchronize()
+    check_status()
+    assert all(torch.equal(a, b) for a, b in zip(before, (q, k, v)))
+    qr, kr, vr = (t.float().requires_grad_(True) for t in (q, k, v))
+    scores = (qr @ kr.transpose(-1, -2) / math.sqrt(D)).masked_fill(~mask, float("-inf"))
+    probs = torch.nan_to_num(torch.softmax(scores, -1), 0.0)
+    ref = probs @ vr
+    fwd_tol = 0.02 if dtype == torch.bfloat16 else 0.005
+    torch.testing.assert_close(out.float(), ref, atol=fwd_tol, rtol=fwd_tol)
+    ref_lse = torch.logsumexp(scores, -1)
+    finite = torch.isfinite(ref_lse)
+    torch.testing.assert_close(lse[finite], ref_lse[finite], atol=1e-3, rtol=1e-4)
+    assert torch.equal(torch.isinf(lse), ~finite)
+    # autograd wrapper
+    upstream = torch.randn_like(out)
+    ref.backward(upstream.float())
+    qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+    got = training_attention(qg, kg, vg, spec, docs, implementation=impl, schedule=schedule)
+    got.backward(upstream)
+    torch.cuda.synchronize()
+    check_status()
+    atol, rtol = (0.025, 0.035) if dtype == torch.bfloat16 else (0.004, 0.006)
+    for mine, theirs in ((qg.grad, qr.grad), (kg.grad, kr.grad), (vg.grad, vr.grad)):
+        torch.testing.assert_close(mine.float(), theirs, atol=atol, rtol=rtol)
+
+
+def test_input_validation(dev):
+    from systems_for_llms_b200.attention import flash
+    from systems_for_llms_b200.attention.masks import MaskSpec
+    q = torch.randn(1, 2, 128, 64, device=dev, dtype=torch.bfloat16)
+    with pytest.raises(ValueError):
+        flash.attention(q.cpu(), q.cpu(), q.cpu(), None, MaskSpec(causal=True))
+    with pytest.raises(ValueError):
+        flash.attention(q.requires_grad_(True), q, q, None, MaskSpec(causal=True))
+    q = q.detach()
+    with pytest.raises(ValueError):
+        flash.attention(q, q, q, None, MaskSpec(same_document=True), implementation="interval")
+    with pytest.raises(ValueError):
+        flash.attention(q[..., :32].contiguous(), q[..., :32].contiguous(),
+                        q[..., :32].contiguous(), None, MaskSpec())
+    with pytest.raises(TypeError):
+        flash.attention(q.float(), q.float(), q.float(), None, MaskSpec())

@@ -1,0 +1,162 @@
+"""sm_100a kernels against plain PyTorch fp32 references (needs a B200)."""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    from systems_for_llms_b200.ops import lib
+    if not lib.available():
+        pytest.skip("kernels need a compute-capability 10.x device")
+    lib.lib()   # a missing or stale library must fail loudly here, not fall back
+    return torch.device("cuda")
+
+
+def rnd(dev, *shape, scale=1.0, seed=0):
+    generator = torch.Generator(device=dev).manual_seed(seed)
+    return (torch.randn(*shape, device=dev, generator=generator) * scale).to(torch.bfloat16)
+
+
+def rel(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).abs().max() / (b.abs().max() + 1e-9)).item()
+
+
+def check(dev):
+    from systems_for_llms_b200.ops.gemm import check_status
+    torch.cuda.synchronize()
+    check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 512, 256), (300, 200, 136),
+                                   (4096, 3072, 1024), (1000, 10000, 512)])
+def test_gemm_forward(dev, M, N, K):
+    from systems_for_llms_b200.ops import gemm as G
+    x, w = rnd(dev, M, K, seed=1), rnd(dev, N, K, seed=2)
+    out = G.linear_fwd(x, w)
+    check(dev)
+    assert rel(out, x.float() @ w.float().t()) < 1e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (300, 200, 136), (2048, 1024, 2752)])
+def test_gemm_dgrad_and_wgrad(dev, M, N, K):
+    from systems_for_llms_b200.ops import gemm as G
+    dy, w, x = rnd(dev, M, N, seed=1), rnd(dev, N, K, seed=2), rnd(dev, M, K, seed=3)
+    assert rel(G.linear_dgrad(dy, w), dy.float() @ w.float()) < 1e-2
+    grad = torch.randn(N, K, device=dev)
+    start = grad.clone()
+    G.linear_wgrad(dy, x, grad, True)
+    check(dev)
+    expect = dy.float().t() @ x.float()
+    assert rel(grad, start + expect) < 1e-4
+    G.linear_wgrad(dy, x, grad, False)
+    check(dev)
+    assert rel(grad, expect) < 1e-4
+
+
+def test_gemm_epilogues(dev):
+    from systems_for_llms_b200.ops import gemm as G
+    M, K, F = 512, 256, 344
+    x = rnd(dev, M, K, seed=1)
+    w = rnd(dev, 1024, K, scale=0.05, seed=2)
+    resid = torch.randn(M, 1024, device=dev)
+    out = G.linear_fwd_resid(x, w, resid)
+    # the product is rounded to bf16 before the add; a flipped rounding moves one bf16 ulp
+    assert rel(out, resid + (x.float() @ w.float().t()).bfloat16().float()) < 5e-3
+    # rotary epilogue
+    B, T, H, D = 2, 256, 2, 64
+    wq = rnd(dev, 3 * H * D, K, scale=0.05, seed=3)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device=dev).float() / D))
+    angles = torch.arange(T, device=dev).float()[:, None] * inv[None]
+    cos, sin = (f(angles).bfloat16().float().contiguous() for f in (torch.cos, torch.sin))
+    got = G.linear_fwd_rope(x, wq, cos, sin, T, 2 * H * D, D).view(B, T, 3, H, D)
+    y = (x.float() @ wq.float().t()).bfloat16().float().view(B, T, 3, H, D)
+    want = y.clone()
+    for part in range(2):
+        even, odd = y[:, :, part, :, 0::2], y[:, :, part, :, 1::2]
+        c, s = cos[None, :, None, :], sin[None, :, None, :]
+        want[:, :, part, :, 0::2] = even * c - odd * s
+        want[:, :, part, :, 1::2] = even * s + odd * c
+    assert rel(got, want) < 1e-2
+    # SwiGLU forward and backward
+    w13 = rnd(dev, 2 * F, K, scale=0.05, seed=4)
+    g, a13 = G.swiglu_fwd(x, w13, F)
+    a = (x.float() @ w13.float().t()).bfloat16().float()
+    assert rel(a13, a) < 1e-2
+    assert rel(g, torch.nn.functional.silu(a[:, :F]) * a[:, F:]) < 1e-2
+    dy, w2 = rnd(dev, M, K, seed=5), rnd(dev, K, F, scale=0.05, seed=6)
+    d13 = G.swiglu_bwd(dy, w2, a13)
+    check(dev)
+    a1 = a13[:, :F].float().requires_grad_(True)
+    a3 = a13[:, F:].float().requires_grad_(True)
+    (torch.nn.functional.silu(a1) * a3).backward((dy.float() @ w2.float()).bfloat16().float())
+    assert rel(d13, torch.cat([a1.grad, a3.grad], 1)) < 1e-2
+
+
+@pytest.mark.parametrize("rows,dim", [(4096, 1024), (37, 16), (5, 50), (300, 384)])
+def test_rmsnorm_forward_backward(dev, rows, dim):
+    from systems_for_llms_b200.ops import functional as K
+    x, w = torch.randn(rows, dim, device=dev), torch.randn(dim, device=dev)
+    y, rstd = K.rmsnorm(x, w, 1e-5)
+    xr, wr = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    ref = xr / torch.sqrt((xr * xr).mean(-1, keepdim=True) + 1e-5) * wr
+    assert rel(y, ref.detach().bfloat16()) < 1e-2
+    dy = torch.randn(rows, dim, device=dev).bfloat16()
+    dres = torch.randn(rows, dim, device=dev)
+    ref.backward(dy.float())
+    dw = torch.ones(dim, device=dev)
+    dx, dxb = K.rmsnorm_bwd(dy, x, w, rstd, dres, dw, True, want_bf16=True)
+    check(dev)
+    assert rel(dx, xr.grad + dres) < 1e-5
+    assert rel(dxb, (xr.grad + dres).bfloat16()) < 1e-2
+    assert rel(dw, wr.grad + 1) < 1e-4
+
+
+@pytest.mark.parametrize("rows,vocab", [(512, 10000), (16, 32), (7, 1000)])
+def test_cross_entropy(dev, rows, vocab):
+    from systems_for_llms_b200.ops import functional as K
+    ld = -(-vocab // 8) * 8
+    logits = (torch.randn(rows, ld, device=dev) * 3).bfloat16()
+    targets = torch.randint(0, vocab, (rows,), device=dev)
+    dl = torch.empty_like(logits)
+    losses = K.cross_entropy_rows(logits, targets, vocab, dl, 0.5)
+    check(dev)
+    wide = logits[:, :vocab].float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(wide, targets, reduction="none")
+    (ref.sum() * 0.5).backward()
+    assert rel(losses, ref.detach()) < 1e-5
+    assert rel(dl[:, :vocab], wide.grad.bfloat16()) < 1e-2
+
+
+def test_adamw_and_norm(dev):
+    from systems_for_llms_b200.ops import functional as K
+    n = 1_000_003
+    g = torch.randn(n, device=dev)
+    p = torch.randn(n, device=dev)
+    m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    shadow = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    stats = K.grad_norm_and_coef(g, 1.0)
+    norm = torch.linalg.vector_norm(g)
+    assert abs(stats[0].item() - norm.item()) / norm.item() < 1e-6
+    ref = torch.nn.Parameter(p.clone())
+    opt = torch.optim.AdamW([ref], lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
+    for step in (1, 2, 3):
+        ref.grad = g * stats[1]
+        opt.step()
+        K.adamw_step(p, g, m, v, shadow, step=step, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8,
+                     weight_decay=0.1, coef=stats[1:2], ok_flag=stats[2:3])
+    check(dev)
+    assert (p - ref.detach()).abs().max().item() < 2e-6
+    assert torch.equal(shadow, p.bfloat16())
+    # a non-finite norm suppresses the update
+    before = p.clone()
+    bad = K.grad_norm_and_coef(torch.full((8,), float("nan"), device=dev), 1.0)
+    K.adamw_step(p, g, m, v, shadow, step=4, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8,
+                 weight_decay=0.1, coef=bad[1:2], ok_flag=bad[2:3])
+    check(dev)
+    assert torch.equal(p, before) and bad[2].item() == 0.0
