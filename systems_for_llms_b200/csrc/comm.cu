@@ -413,6 +413,7 @@ allgather_kernel(const CommView c, long offset_bytes, long chunk_bytes, int slot
 // partial[rows, cols] in the symmetric buffer `c` at byte offset in_off; the
 // result out = resid + bf16(sum of partials) (fp32) is written to every peer's
 // symmetric buffer `o` at byte offset out_off.  Rows are split across ranks.
+template <bool OUT_BF16>
 __global__ void __launch_bounds__(256)
 reduce_rows_resid_kernel(const CommView c, const CommView o, long in_off, long out_off,
                          const float* __restrict__ resid, long rows, int cols, int slot,
@@ -454,11 +455,21 @@ reduce_rows_resid_kernel(const CommView c, const CommView o, long in_off, long o
     lo.z += bf16_round(acc[2]); lo.w += bf16_round(acc[3]);
     hi.x += bf16_round(acc[4]); hi.y += bf16_round(acc[5]);
     hi.z += bf16_round(acc[6]); hi.w += bf16_round(acc[7]);
+    if constexpr (OUT_BF16) {
+      uint4 packed;
+      packed.x = pack_bf16(lo.x, lo.y);
+      packed.y = pack_bf16(lo.z, lo.w);
+      packed.z = pack_bf16(hi.x, hi.y);
+      packed.w = pack_bf16(hi.z, hi.w);
 #pragma unroll 1
-    for (int p = 0; p < o.world; ++p) {
-      float* dst = reinterpret_cast<float*>(o.data[p] + out_off) + elem;
-      st_peer_f4(dst, lo);
-      st_peer_f4(dst + 4, hi);
+      for (int p = 0; p < o.world; ++p) st_peer_u4(o.data[p] + out_off + elem * 2, packed);
+    } else {
+#pragma unroll 1
+      for (int p = 0; p < o.world; ++p) {
+        float* dst = reinterpret_cast<float*>(o.data[p] + out_off) + elem;
+        st_peer_f4(dst, lo);
+        st_peer_f4(dst + 4, hi);
+      }
     }
   }
   done_barrier(c, slot, epoch, status);
@@ -602,8 +613,20 @@ extern "C" int sfl_reduce_rows_resid(const SflComm* comm, long in_off, long out_
   if (comm == nullptr || comm->world < 1 || comm->world > kMaxPeers) return -2;
   if ((cols & 7) || (in_off & 15) || (out_off & 15) || slot < 0 || slot >= kSlots) return -2;
   ctas = clamp_ctas(ctas);
-  reduce_rows_resid_kernel<<<ctas, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  reduce_rows_resid_kernel<false><<<ctas, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       to_view(comm, 0), to_view(comm, 1), in_off, out_off, resid, rows, cols, slot, epoch, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int sfl_reduce_rows_bf16(const SflComm* comm, long in_off, long out_off, long rows,
+                                    int cols, int slot, unsigned epoch, int ctas, int* status,
+                                    void* stream) {
+  if (comm == nullptr || comm->world < 1 || comm->world > kMaxPeers) return -2;
+  if ((cols & 7) || (in_off & 15) || (out_off & 15) || slot < 0 || slot >= kSlots) return -2;
+  ctas = clamp_ctas(ctas);
+  reduce_rows_resid_kernel<true><<<ctas, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      to_view(comm, 0), to_view(comm, 1), in_off, out_off, nullptr, rows, cols, slot, epoch,
+      status);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -195,6 +195,9 @@ int sfl_allgather_bytes(const SflComm* comm, long offset_bytes, long chunk_bytes
 int sfl_reduce_rows_resid(const SflComm* comm, long in_off_bytes, long out_off_bytes,
                           const float* resid, long rows, int cols, int slot, unsigned epoch,
                           int ctas, int* status, void* stream);
+/* data2[*][out_off] (bf16 [rows, cols]) <- bf16(sum_r data[r][in_off] (bf16)), fp32 sum. */
+int sfl_reduce_rows_bf16(const SflComm* comm, long in_off_bytes, long out_off_bytes, long rows,
+                         int cols, int slot, unsigned epoch, int ctas, int* status, void* stream);
 /* data2[*][out_off] (fp32, count elements) <- sum_r data[r][in_off] (fp32). */
 int sfl_allreduce_rows_f32(const SflComm* comm, long in_off_bytes, long out_off_bytes, long count,
                            int slot, unsigned epoch, int ctas, int* status, void* stream);

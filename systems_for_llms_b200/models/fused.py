@@ -48,9 +48,13 @@ def eligible(model) -> bool:
     if len({p.device for p in params}) != 1:
         return False
     d_k = model.d_model // model.num_heads
-    return (model.d_model % 64 == 0 and d_k in (64, 128) and model.d_ff % 8 == 0
-            and model.vocab_size >= 8 and all(layer.attn.rope is not None for layer in model.layers)
-            and not getattr(model, "_tp_parallelized", False))
+    first = model.layers[0]
+    local_ff = first.ffn.w1.weight.shape[0]            # d_ff, or d_ff / tp under tensor parallelism
+    local_attn = first.attn.q_proj.weight.shape[0]     # d_model, or d_model / tp
+    return (model.d_model % 64 == 0 and d_k in (64, 128) and local_ff % 8 == 0
+            and local_attn % d_k == 0 and (local_attn * model.d_model) % ALIGN == 0
+            and (local_ff * model.d_model) % ALIGN == 0
+            and model.vocab_size >= 8 and all(layer.attn.rope is not None for layer in model.layers))
 
 
 def _round_up(value: int, multiple: int) -> int:
@@ -61,9 +65,15 @@ class FusedEngine:
     def __init__(self, model):
         self.model = model
         self.device = next(model.parameters()).device
-        self.d_model, self.num_heads = model.d_model, model.num_heads
+        self.d_model = model.d_model
         self.d_k = model.d_model // model.num_heads
-        self.d_ff, self.vocab = model.d_ff, model.vocab_size
+        first = model.layers[0]
+        # Widths held by this rank (the full widths unless tensor parallel).
+        self.attn_width = first.attn.q_proj.weight.shape[0]
+        self.num_heads = self.attn_width // self.d_k
+        self.d_ff = first.ffn.w1.weight.shape[0]
+        self.vocab = model.vocab_size
+        self.tp = None   # parallel.tensor_parallel.TensorParallelComm when sharded
         self._layout()
         self._flatten()
         self.flat_grad: torch.Tensor | None = None
@@ -235,29 +245,39 @@ class FusedEngine:
 def block_forward(engine: FusedEngine, index: int, x: torch.Tensor, B: int, T: int):
     """Returns ``(x_out, saved)`` where ``saved`` holds what backward needs."""
     layer = engine.model.layers[index]
-    d, dk, H, dff = engine.d_model, engine.d_k, engine.num_heads, engine.d_ff
+    d, dk, H, dff, aw = engine.d_model, engine.d_k, engine.num_heads, engine.d_ff, engine.attn_width
+    tp = engine.tp
     M = B * T
     x2 = x.reshape(M, d)
     h1, rstd1 = K.rmsnorm(x2, layer.attn_norm.weight, layer.attn_norm.eps)
-    wqkv = engine.shadow(layer.attn.q_proj.weight, 3 * d)
-    qkv = G.linear_fwd_rope(h1, wqkv, engine.cos, engine.sin, T, 2 * d, dk)
+    wqkv = engine.shadow(layer.attn.q_proj.weight, 3 * aw)
+    qkv = G.linear_fwd_rope(h1, wqkv, engine.cos, engine.sin, T, 2 * aw, dk)
     heads = qkv.view(B, T, 3, H, dk)
     q, k, v = (heads[:, :, i].permute(0, 2, 1, 3) for i in range(3))
-    attn = torch.empty(M, d, dtype=torch.bfloat16, device=x.device)
+    attn = torch.empty(M, aw, dtype=torch.bfloat16, device=x.device)
     lse = torch.empty(B, H, T, dtype=torch.float32, device=x.device)
     mask = flash.causal_mask(x.device, T)
     flash.flash_fwd(q, k, v, attn.view(B, T, H, dk).permute(0, 2, 1, 3), lse, mask, dk ** -0.5)
-    x_mid = G.linear_fwd_resid(attn, engine.shadow(layer.attn.output_proj.weight), x2)
+    wo = engine.shadow(layer.attn.output_proj.weight)
+    if tp is None:
+        x_mid = G.linear_fwd_resid(attn, wo, x2)
+    else:   # row-parallel: bf16 partial sums -> one kernel sums peers, adds the residual
+        x_mid = tp.reduce_residual(G.linear_fwd(attn, wo, tp.partial(M, d)), x2, 2 * index)
     h2, rstd2 = K.rmsnorm(x_mid, layer.ffn_norm.weight, layer.ffn_norm.eps)
     g, a13 = G.swiglu_fwd(h2, engine.shadow(layer.ffn.w1.weight, 2 * dff), dff)
-    x_out = G.linear_fwd_resid(g, engine.shadow(layer.ffn.w2.weight), x_mid)
+    w2 = engine.shadow(layer.ffn.w2.weight)
+    if tp is None:
+        x_out = G.linear_fwd_resid(g, w2, x_mid)
+    else:
+        x_out = tp.reduce_residual(G.linear_fwd(g, w2, tp.partial(M, d)), x_mid, 2 * index + 1)
     saved = (x2, rstd1, h1, qkv, attn, lse, x_mid, rstd2, h2, a13, g)
     return x_out.view(B, T, d), saved
 
 
 def block_backward(engine: FusedEngine, index: int, saved, d_out: torch.Tensor, B: int, T: int):
     layer = engine.model.layers[index]
-    d, dk, H, dff = engine.d_model, engine.d_k, engine.num_heads, engine.d_ff
+    d, dk, H, dff, aw = engine.d_model, engine.d_k, engine.num_heads, engine.d_ff, engine.attn_width
+    tp = engine.tp
     M = B * T
     x2, rstd1, h1, qkv, attn, lse, x_mid, rstd2, h2, a13, g = saved
     dres = d_out.reshape(M, d)
@@ -275,7 +295,11 @@ def block_backward(engine: FusedEngine, index: int, saved, d_out: torch.Tensor, 
     d13 = G.swiglu_bwd(dres_bf16, engine.shadow(ffn.w2.weight), a13)
     acc = engine.claim(ffn.w2.weight)
     G.linear_wgrad(dres_bf16, g, engine.grad_view(ffn.w2.weight), acc)
-    dh2 = G.linear_dgrad(d13, engine.shadow(ffn.w1.weight, 2 * dff))
+    if tp is None:
+        dh2 = G.linear_dgrad(d13, engine.shadow(ffn.w1.weight, 2 * dff))
+    else:   # column-parallel input gradient: partial over ranks, summed by one kernel
+        dh2 = tp.reduce_bf16(G.linear_dgrad(d13, engine.shadow(ffn.w1.weight, 2 * dff),
+                                            tp.partial(M, d)))
     acc = engine.claim(ffn.w1.weight, ffn.w3.weight)
     G.linear_wgrad(d13, h2, engine.grad_view(ffn.w1.weight, 2 * dff), acc)
     acc = engine.claim(layer.ffn_norm.weight)
@@ -293,10 +317,14 @@ def block_backward(engine: FusedEngine, index: int, saved, d_out: torch.Tensor, 
     as_heads = lambda t: t.view(B, T, H, dk).permute(0, 2, 1, 3)
     mask = flash.causal_mask(d_out.device, T)
     flash.flash_bwd(q, k, v, as_heads(attn), as_heads(d_attn), lse, dq, dkk, dv, mask, dk ** -0.5)
-    flash.rope_bwd_(dqkv, engine.cos, engine.sin, T, 2 * d, dk)
-    dh1 = G.linear_dgrad(dqkv, engine.shadow(attn_p.q_proj.weight, 3 * d))
+    flash.rope_bwd_(dqkv, engine.cos, engine.sin, T, 2 * aw, dk)
+    if tp is None:
+        dh1 = G.linear_dgrad(dqkv, engine.shadow(attn_p.q_proj.weight, 3 * aw))
+    else:
+        dh1 = tp.reduce_bf16(G.linear_dgrad(dqkv, engine.shadow(attn_p.q_proj.weight, 3 * aw),
+                                            tp.partial(M, d)))
     acc = engine.claim(attn_p.q_proj.weight, attn_p.k_proj.weight, attn_p.v_proj.weight)
-    G.linear_wgrad(dqkv, h1, engine.grad_view(attn_p.q_proj.weight, 3 * d), acc)
+    G.linear_wgrad(dqkv, h1, engine.grad_view(attn_p.q_proj.weight, 3 * aw), acc)
     acc = engine.claim(layer.attn_norm.weight)
     dx, dx_bf16 = K.rmsnorm_bwd(dh1, x2, layer.attn_norm.weight, rstd1, dres2,
                                 engine.grad_view(layer.attn_norm.weight), acc, want_bf16=True)

@@ -49,6 +49,7 @@ for _name, _args in {
                             c_float, c_float, c_float, _P, _P, c_int, c_uint, c_int, _P, _P],
     "sfl_allgather_bytes": [_C, c_long, c_long, c_int, c_uint, c_int, _P, _P],
     "sfl_reduce_rows_resid": [_C, c_long, c_long, _P, c_long, c_int, c_int, c_uint, c_int, _P, _P],
+    "sfl_reduce_rows_bf16": [_C, c_long, c_long, c_long, c_int, c_int, c_uint, c_int, _P, _P],
     "sfl_allreduce_rows_f32": [_C, c_long, c_long, c_long, c_int, c_uint, c_int, _P, _P],
 }.items():
     _lib.register_signature(_name, _args)
@@ -213,6 +214,13 @@ class PeerComm:
             ctypes.byref(self.struct(partial, out)), in_off, out_off, _lib.ptr(resid), rows, cols,
             slot, self.next_epoch(slot), self.ctas, self.status.data_ptr(), _lib.stream_ptr())
         _lib.check(code, "sfl_reduce_rows_resid")
+
+    def reduce_rows_bf16(self, partial: SymmetricBuffer, out: SymmetricBuffer, in_off: int,
+                         out_off: int, rows: int, cols: int, slot: int) -> None:
+        code = _lib.lib().sfl_reduce_rows_bf16(
+            ctypes.byref(self.struct(partial, out)), in_off, out_off, rows, cols, slot,
+            self.next_epoch(slot), self.ctas, self.status.data_ptr(), _lib.stream_ptr())
+        _lib.check(code, "sfl_reduce_rows_bf16")
 
     def allreduce_rows_f32(self, partial: SymmetricBuffer, out: SymmetricBuffer, in_off: int,
                            out_off: int, count: int, slot: int) -> None:

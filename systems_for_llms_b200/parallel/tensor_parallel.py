@@ -221,3 +221,96 @@ def reconstruct_state_dict(model) -> dict:
         dist.all_gather(pieces, tensor.contiguous(), group=model._tp_group)
         full[name] = torch.cat(pieces, dim=dimension)
     return full
+
+
+class TensorParallelComm:
+    """Peer-memory buffers and reductions for the fused tensor-parallel engine.
+
+    ``partial(M, d)`` is where a row-parallel GEMM writes its bf16 partial sums;
+    ``reduce_residual`` sums the peers' partials, adds the fp32 residual and
+    returns the fp32 result, which lives in a per-(layer, position) slot of a
+    symmetric pool so it can serve as the saved activation without a copy;
+    ``reduce_bf16`` does the same without a residual for input gradients.
+    A peer may write into this rank's buffers only after this rank has entered
+    the same collective (ready barrier), which is after it finished every use of
+    the previous contents in stream order.
+    """
+
+    def __init__(self, device, group, num_layers: int):
+        from . import comm as pm
+        self.pm = pm
+        self.device, self.group, self.num_layers = device, group, num_layers
+        self.comm = pm.PeerComm(device, group, ctas=96)
+        self.rows = self.cols = 0
+        self.partial_buf = self.pool = self.small = None
+        self._calls = 0
+
+    def _ensure(self, rows: int, cols: int) -> None:
+        if rows <= self.rows and cols == self.cols:
+            return
+        for buffer in (self.partial_buf, self.pool, self.small):
+            if buffer is not None:
+                buffer.close()
+        pm = self.pm
+        self.rows, self.cols = rows, cols
+        self.partial_buf = pm.SymmetricBuffer(rows * cols * 2, self.device, self.group)
+        self.pool = pm.SymmetricBuffer(2 * self.num_layers * rows * cols * 4, self.device,
+                                       self.group)
+        self.small = pm.SymmetricBuffer(rows * cols * 2, self.device, self.group)
+
+    def partial(self, rows: int, cols: int) -> torch.Tensor:
+        self._ensure(rows, cols)
+        return self.partial_buf.view(torch.bfloat16, rows * cols).view(rows, cols)
+
+    def _slot(self) -> int:
+        self._calls += 1
+        return self._calls % 32
+
+    def reduce_residual(self, partial: torch.Tensor, resid: torch.Tensor, position: int):
+        rows, cols = partial.shape
+        offset = position * self.rows * self.cols * 4
+        self.comm.reduce_rows_resid(self.partial_buf, self.pool, 0, offset, resid, rows, cols,
+                                    self._slot())
+        return self.pool.view(torch.float32, rows * cols, offset).view(rows, cols)
+
+    def reduce_bf16(self, partial: torch.Tensor) -> torch.Tensor:
+        rows, cols = partial.shape
+        self.comm.reduce_rows_bf16(self.partial_buf, self.small, 0, 0, rows, cols, self._slot())
+        return self.small.view(torch.bfloat16, rows * cols).view(rows, cols)
+
+    def close(self) -> None:
+        for buffer in (self.partial_buf, self.pool, self.small):
+            if buffer is not None:
+                buffer.close()
+        self.comm.close()
+
+
+def enable_fused(model, config_autocast) -> object | None:
+    """Attach peer-memory reductions to a parallelised model's fused engine."""
+    with config_autocast:
+        engine = model.fused_engine()
+    if engine is None:
+        return None
+    if engine.tp is None:
+        engine.tp = TensorParallelComm(engine.device, model._tp_group, len(model.layers))
+    return engine
+
+
+@torch.no_grad()
+def fused_grad_stats(model, engine, max_norm: float) -> torch.Tensor:
+    """Device vector ``[norm, clip coefficient, finite]`` of the logical full gradient.
+
+    Every rank sums the squares of its whole flat gradient; replicated parameters
+    were counted ``world`` times, so ``world - 1`` copies of their squared norm
+    are subtracted.
+    """
+    world, _ = _world(model._tp_group)
+    flat = engine.flat_grad[:engine.total]
+    local = torch.linalg.vector_norm(flat, 2, dtype=torch.float32).square()
+    replicated = [p.grad for p in model.parameters()
+                  if p.grad is not None and not hasattr(p, "_tp_shard_dim")]
+    shared = torch.stack(torch._foreach_norm(replicated)).square().sum()
+    dist.all_reduce(local, group=model._tp_group)
+    norm = (local - (world - 1) * shared).clamp_min(0).sqrt()
+    coefficient = (max_norm / (norm + 1e-6)).clamp(max=1.0)
+    return torch.stack([norm, coefficient, torch.isfinite(norm).float()])

@@ -153,6 +153,9 @@ class Strategy:
             from .tensor_parallel import describe_sharding, parallelize_model
             parallelize_model(base_model)
             self.sharding = describe_sharding(base_model)
+            if fused_possible:
+                from .tensor_parallel import enable_fused
+                self.engine = enable_fused(base_model, autocast(config, device))
         elif mode == "fsdp":
             from .fsdp import shard_model
             self.model = shard_model(base_model)
@@ -208,6 +211,10 @@ class Strategy:
                     self.optimizer.step_flat(stats)
                     return stats[0]
                 return self.optimizer.step_with_stats(stats)
+        if mode == "tp" and self.engine is not None:
+            from .tensor_parallel import fused_grad_stats
+            stats = fused_grad_stats(self.base, self.engine, config.grad_clip)
+            return self.optimizer.step_with_stats(stats)
         if mode == "tp":
             from .tensor_parallel import clip_grad_norm_tp
             norm = clip_grad_norm_tp(self.base, config.grad_clip, error_if_nonfinite=True)
@@ -237,6 +244,9 @@ class Strategy:
             self.optimizer.close()
         if self.ddp is not None:
             self.ddp.close()
+        if self.engine is not None and self.engine.tp is not None:
+            self.engine.tp.close()
+            self.engine.tp = None
 
 
 def train_step(strategy: Strategy, data, config, sampler, device, *, global_batch_size,
@@ -400,7 +410,8 @@ def run(config: TrainConfig, output_dir, *, mode="single", global_batch_size=8,
             "execution_path": ("sm_100a fused engine" if strategy.engine is not None
                                else "portable PyTorch operators"),
             "gradient_reduction": ("peer-memory kernels over NVLink"
-                                   if strategy.ddp is not None and strategy.ddp._peer_active()
+                                   if (strategy.ddp is not None and strategy.ddp._peer_active())
+                                   or (strategy.engine is not None and strategy.engine.tp is not None)
                                    else "torch.distributed collectives"),
             "checkpoint_scope": ("optional final model/optimizer state for correctness checks; "
                                  "resume unsupported"),
