@@ -23,6 +23,7 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
+#include <stdio.h>
 
 #include <type_traits>
 
@@ -323,4 +324,93 @@ extern "C" int sfl_decode(const void* q, const void* k, const void* v, const int
   }
   return D == 64 ? dispatch_group<__nv_bfloat16, 64>(p, groups, tile, stream)
                  : dispatch_group<__nv_bfloat16, 128>(p, groups, tile, stream);
+}
+
+// ------------------------------------------------------------------------------
+// Allocation-free variant of sfl_decode (declared in sfl.h as sfl_decode_static).
+//
+// Some callers cannot reach a device allocator at the moment they need to decode:
+// code running inside a CUDA-graph capture or between the nodes of a latency
+// critical serving loop (cudaMalloc synchronises the device and is illegal during
+// capture), plug-ins loaded into a host process whose memory pool they may not
+// touch, and C callers that link this library without PyTorch and therefore have
+// no caching allocator to lean on.  For them the split-KV scratch (per-split
+// maxima, normalisers, partial outputs and the arrival counters) lives in one
+// fixed array inside the library image.  Every GPU that loads the library holds
+// those bytes until the process exits, which is why the capacity is modest.
+namespace sfl {
+
+constexpr long kStaticSlots = 8192;     // max batch * query_heads * splits
+constexpr long kStaticCounters = 1024;  // max batch * kv_heads
+constexpr long kStaticFloats = kStaticSlots * 2 + kStaticSlots * 128;
+constexpr long kStaticBytes = kStaticFloats * 4 + kStaticCounters * 4;
+
+// Layout: part_m[kStaticSlots] | part_l[kStaticSlots] | part_u[kStaticSlots * 128] | counters.
+static __device__ __align__(256) unsigned char g_decode_scratch[kStaticBytes];
+
+// In host code `g_decode_scratch` is only a handle for the runtime, not an
+// address a kernel may dereference; the real device address is looked up once
+// per device and remembered here.
+constexpr int kMaxDevices = 64;
+static void* g_scratch_address[kMaxDevices] = {};
+static thread_local char g_static_error[256] = "";
+
+int fail_static(int code, const char* message) {
+  snprintf(g_static_error, sizeof(g_static_error), "%s", message);
+  return code;
+}
+
+}  // namespace sfl
+
+extern "C" const char* sfl_decode_static_error(void) { return sfl::g_static_error; }
+
+extern "C" long sfl_decode_static_capacity_slots(void) { return sfl::kStaticSlots; }
+
+extern "C" int sfl_decode_static(const void* q, const void* k, const void* v, const int* lengths,
+                                 void* out, int B, int Hq, int Hkv, int N, int D, int splits,
+                                 float scale, int tile_variant, int is_fp16, void* stream_) {
+  using namespace sfl;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || N <= 0 || Hq % Hkv || splits < 1 || splits > 128 ||
+      (D != 64 && D != 128))
+    return fail_static(-2, "sfl_decode_static: unsupported shape (see sfl_decode)");
+  const long slots = static_cast<long>(B) * Hq * splits;
+  if (slots > kStaticSlots || static_cast<long>(B) * Hkv > kStaticCounters) {
+    char text[200];
+    snprintf(text, sizeof(text),
+             "sfl_decode_static: batch*query_heads*splits = %ld exceeds the built-in scratch "
+             "capacity of %ld (or batch*kv_heads > %ld); use sfl_decode with caller scratch",
+             slots, kStaticSlots, kStaticCounters);
+    return fail_static(-10, text);
+  }
+  int device = 0;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess || device < 0 || device >= kMaxDevices)
+    return fail_static(-11, "sfl_decode_static: cannot identify the current device");
+  if (g_scratch_address[device] == nullptr) {
+    // First call on this device: resolve the array's device address.  This is a
+    // runtime query, not an allocation, but it may not be issued while a stream
+    // is capturing, so make the first call before any capture.
+    void* address = nullptr;
+    err = cudaGetSymbolAddress(&address, g_decode_scratch);
+    if (err != cudaSuccess || address == nullptr)
+      return fail_static(-12, "sfl_decode_static: cudaGetSymbolAddress failed");
+    g_scratch_address[device] = address;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  float* base = static_cast<float*>(g_scratch_address[device]);
+  float* part_m = base;
+  float* part_l = base + kStaticSlots;
+  float* part_u = base + 2 * kStaticSlots;
+  int* counters = reinterpret_cast<int*>(base + kStaticFloats);
+  // The array keeps whatever the previous call left.  Partials are fully
+  // rewritten before they are read; the arrival counters must start at zero, so
+  // clear the ones this call uses (a stale count from an interrupted launch would
+  // otherwise pick the wrong "last" CTA).
+  err = cudaMemsetAsync(counters, 0, sizeof(int) * static_cast<size_t>(B) * Hkv, stream);
+  if (err != cudaSuccess) return fail_static(-13, "sfl_decode_static: clearing counters failed");
+  const int rc = sfl_decode(q, k, v, lengths, part_m, part_l, part_u, counters, out, B, Hq, Hkv,
+                            N, D, splits, scale, tile_variant, is_fp16, stream_);
+  if (rc != 0) return fail_static(rc, "sfl_decode_static: kernel launch failed");
+  g_static_error[0] = '\0';
+  return 0;
 }

@@ -144,6 +144,32 @@ int sfl_decode(const void* q, const void* k, const void* v, const int* lengths, 
                float* part_l, float* part_u, int* counters, void* out, int B, int Hq, int Hkv,
                int N, int D, int splits, float scale, int tile_variant, int is_fp16, void* stream);
 
+/* Allocation-free decode.  This entry point has no counterpart in the reference.
+ *
+ * Same computation as sfl_decode, for callers that cannot allocate device
+ * memory where they decode: inside CUDA-graph capture or a serving loop that must
+ * not synchronise (cudaMalloc does both harm), in a plug-in that may not touch its
+ * host's memory pool, or from plain C without a caching allocator.  The split-KV
+ * scratch is a fixed array inside the library image instead of caller memory:
+ *   - capacity: batch * query_heads * splits <= sfl_decode_static_capacity_slots()
+ *     (8192) and batch * kv_heads <= 1024; about 4.2 MB that every GPU which loads
+ *     the library keeps until the process exits.  Larger problems are rejected
+ *     with a nonzero code and a message from sfl_decode_static_error().
+ *   - the caller still passes q, k, v, lengths and out; nothing is allocated or
+ *     freed, neither through the CUDA runtime nor through any library.
+ *   - the first call on each device looks up the array's device address
+ *     (with that device current); make that first call before starting any
+ *     stream capture.
+ *   - all calls on a device share the one array.  It keeps the previous call's
+ *     contents; this function clears the part that must start at zero.  Two calls
+ *     whose kernels overlap on the GPU (different streams, or different threads)
+ *     race on the scratch and give wrong results: serialise them. */
+int sfl_decode_static(const void* q, const void* k, const void* v, const int* lengths, void* out,
+                      int B, int Hq, int Hkv, int N, int D, int splits, float scale,
+                      int tile_variant, int is_fp16, void* stream);
+long sfl_decode_static_capacity_slots(void);
+const char* sfl_decode_static_error(void);
+
 /* --------------------------------------------------------- communication -- */
 /* Symmetric (same size on every rank) device buffers shared through CUDA IPC. */
 int sfl_ipc_alloc(void** ptr, size_t bytes);               /* cudaMalloc + zero fill  */
