@@ -174,6 +174,7 @@ def run_ours(args) -> None:
                 with autocast(config, device):
                     loss = strategy.model.loss(x, y, 1.0 / accumulation)
                 loss.backward()
+                strategy.after_backward()
         return strategy.reduce_and_update()
 
     for step in range(args.warmup):

@@ -202,7 +202,8 @@ __device__ __forceinline__ void slice_of(long count, int world, int rank, long* 
 template <int W, int U, bool WRITE_BACK>
 __global__ void __launch_bounds__(256)
 reduce_kernel(const CommView c, long offset, long count, float scale, int slot, uint32_t epoch,
-              float* __restrict__ local_out, int accumulate_partial, int* status) {
+              float* __restrict__ local_out, int accumulate_partial, int accumulate_out,
+              int* status) {
   if (!ready_barrier(c, slot, epoch, status)) return;
   long begin, end;
   slice_of(count, c.world, c.rank, &begin, &end);
@@ -254,6 +255,10 @@ reduce_kernel(const CommView c, long offset, long count, float scale, int slot, 
       } else {
         float* dst = local_out != nullptr ? local_out + ((i - begin) << 2)
                                           : reinterpret_cast<float*>(c.data[c.rank]) + elem;
+        if (accumulate_out) {
+          const float4 old = *reinterpret_cast<const float4*>(dst);
+          acc[u].x += old.x; acc[u].y += old.y; acc[u].z += old.z; acc[u].w += old.w;
+        }
         *reinterpret_cast<float4*>(dst) = acc[u];
       }
     }
@@ -272,23 +277,27 @@ reduce_kernel(const CommView c, long offset, long count, float scale, int slot, 
 template <bool WRITE_BACK>
 int launch_reduce(const CommView& v, long offset, long count, float scale, int slot,
                   uint32_t epoch, float* local_out, int accumulate, int ctas, int* status,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, int accumulate_out = 0) {
   switch (v.world) {
     case 2:
       reduce_kernel<2, 8, WRITE_BACK><<<ctas, 256, 0, stream>>>(v, offset, count, scale, slot,
-                                                               epoch, local_out, accumulate, status);
+                                                               epoch, local_out, accumulate,
+                                                               accumulate_out, status);
       break;
     case 4:
       reduce_kernel<4, 4, WRITE_BACK><<<ctas, 256, 0, stream>>>(v, offset, count, scale, slot,
-                                                               epoch, local_out, accumulate, status);
+                                                               epoch, local_out, accumulate,
+                                                               accumulate_out, status);
       break;
     case 8:
       reduce_kernel<8, 2, WRITE_BACK><<<ctas, 256, 0, stream>>>(v, offset, count, scale, slot,
-                                                               epoch, local_out, accumulate, status);
+                                                               epoch, local_out, accumulate,
+                                                               accumulate_out, status);
       break;
     default:
       reduce_kernel<0, 1, WRITE_BACK><<<ctas, 256, 0, stream>>>(v, offset, count, scale, slot,
-                                                               epoch, local_out, accumulate, status);
+                                                               epoch, local_out, accumulate,
+                                                               accumulate_out, status);
   }
   return static_cast<int>(cudaGetLastError());
 }
@@ -405,6 +414,38 @@ allgather_kernel(const CommView c, long offset_bytes, long chunk_bytes, int slot
 #pragma unroll
     for (int u = 0; u < U; ++u)
       if (byte[u] >= 0) *reinterpret_cast<uint4*>(c.data[c.rank] + byte[u]) = v[u];
+  }
+  done_barrier(c, slot, epoch, status);
+}
+
+// dst[r * chunk .. (r+1) * chunk) <- peer r's bytes [src_off, src_off + chunk), for
+// every rank r (own slice included); dst is ordinary local memory.
+__global__ void __launch_bounds__(256)
+allgather_into_kernel(const CommView c, long src_off, long chunk_bytes, char* __restrict__ dst,
+                      int slot, uint32_t epoch, int* status) {
+  if (!ready_barrier(c, slot, epoch, status)) return;
+  const long vecs = chunk_bytes >> 4;
+  const long total = vecs * c.world;
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  constexpr int U = 8;
+  for (long i0 = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total;
+       i0 += stride * U) {
+    uint4 v[U];
+    long at[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long i = i0 + u * stride;
+      at[u] = -1;
+      if (i < total) {
+        const int peer = static_cast<int>(i / vecs);
+        const long w = i - peer * vecs;
+        at[u] = peer * chunk_bytes + (w << 4);
+        v[u] = ld_peer_u4(c.data[peer] + src_off + (w << 4));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (at[u] >= 0) *reinterpret_cast<uint4*>(dst + at[u]) = v[u];
   }
   done_barrier(c, slot, epoch, status);
 }
@@ -568,8 +609,8 @@ extern "C" int sfl_reduce_scatter_f32(const SflComm* comm, long offset, long cou
   if (comm == nullptr || comm->world < 1 || comm->world > kMaxPeers) return -2;
   if ((count & 3) || (offset & 3) || slot < 0 || slot >= kSlots) return -2;
   return launch_reduce<false>(to_view(comm, 0), offset, count, scale, slot, epoch, local_out,
-                              accumulate_partial, clamp_ctas(ctas), status,
-                              static_cast<cudaStream_t>(stream));
+                              accumulate_partial & 1, clamp_ctas(ctas), status,
+                              static_cast<cudaStream_t>(stream), (accumulate_partial >> 1) & 1);
 }
 
 extern "C" int sfl_comm_norm_finalize(const SflComm* comm, const int* slots_dev, int n_slots,
@@ -604,6 +645,18 @@ extern "C" int sfl_allgather_bytes(const SflComm* comm, long offset_bytes, long 
   ctas = clamp_ctas(ctas);
   allgather_kernel<<<ctas, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       to_view(comm, 0), offset_bytes, chunk_bytes, slot, epoch, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int sfl_allgather_into(const SflComm* comm, long src_off_bytes, long chunk_bytes,
+                                  void* dst, int slot, unsigned epoch, int ctas, int* status,
+                                  void* stream) {
+  if (comm == nullptr || comm->world < 1 || comm->world > kMaxPeers) return -2;
+  if ((chunk_bytes & 15) || (src_off_bytes & 15) || slot < 0 || slot >= kSlots) return -2;
+  if (reinterpret_cast<uintptr_t>(dst) & 15) return -2;
+  ctas = clamp_ctas(ctas);
+  allgather_into_kernel<<<ctas, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      to_view(comm, 0), src_off_bytes, chunk_bytes, static_cast<char*>(dst), slot, epoch, status);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -201,7 +201,9 @@ typedef struct SflComm {
 int sfl_allreduce_f32(const SflComm* comm, long offset, long count, float scale, int slot,
                       unsigned epoch, int accumulate_partial, int ctas, int* status, void* stream);
 /* Rank r reduces slice r of the range into local_out (slice-relative, compact)
- * or in place when local_out is NULL. */
+ * or in place when local_out is NULL.  Bit 1 of accumulate_partial (value 2) adds
+ * the reduced slice to the existing contents of the destination instead of
+ * overwriting it (gradient accumulation over microbatches). */
 int sfl_reduce_scatter_f32(const SflComm* comm, long offset, long count, float scale,
                            float* local_out, int slot, unsigned epoch, int accumulate_partial,
                            int ctas, int* status, void* stream);
@@ -217,6 +219,10 @@ int sfl_adamw_allgather(const SflComm* comm, long offset, long count, const floa
 /* Pull chunk r (chunk_bytes at offset_bytes + r*chunk_bytes) from every peer r. */
 int sfl_allgather_bytes(const SflComm* comm, long offset_bytes, long chunk_bytes, int slot,
                         unsigned epoch, int ctas, int* status, void* stream);
+/* dst[r*chunk_bytes ...] <- peer r's data[src_off_bytes .. +chunk_bytes) for every r;
+ * dst is local memory (16-byte aligned). */
+int sfl_allgather_into(const SflComm* comm, long src_off_bytes, long chunk_bytes, void* dst,
+                       int slot, unsigned epoch, int ctas, int* status, void* stream);
 /* data2[*][out_off] (fp32 [rows, cols]) <- resid + bf16(sum_r data[r][in_off] (bf16)). */
 int sfl_reduce_rows_resid(const SflComm* comm, long in_off_bytes, long out_off_bytes,
                           const float* resid, long rows, int cols, int slot, unsigned epoch,

@@ -196,6 +196,13 @@ class FusedEngine:
             K.cast_bf16(self.flat_param, self.flat_shadow)
             self._versions = versions
 
+    def prepare_block(self, index: int, backward: bool) -> None:
+        """Called before block ``index`` runs (forward or backward).  The base engine
+        has every weight resident; sharded engines gather the block here."""
+
+    def embedding_table(self) -> torch.Tensor:
+        return self.model.token_embeddings.weight
+
     def mark_shadow_current(self) -> None:
         """Called by the fused optimizer, which writes the shadow itself."""
         self._versions = tuple(p._version for p in self.params)
@@ -212,7 +219,7 @@ class FusedEngine:
         if grad:
             x = _Embed.apply(model.token_embeddings.weight, ids, self)
         else:
-            x = K.embedding(model.token_embeddings.weight, ids)
+            x = K.embedding(self.embedding_table(), ids)
         recompute = model.activation_checkpointing == "block" and model.training and grad
         for index in range(len(model.layers)):
             if grad:
@@ -248,6 +255,7 @@ def block_forward(engine: FusedEngine, index: int, x: torch.Tensor, B: int, T: i
     d, dk, H, dff, aw = engine.d_model, engine.d_k, engine.num_heads, engine.d_ff, engine.attn_width
     tp = engine.tp
     M = B * T
+    engine.prepare_block(index, False)
     x2 = x.reshape(M, d)
     h1, rstd1 = K.rmsnorm(x2, layer.attn_norm.weight, layer.attn_norm.eps)
     wqkv = engine.shadow(layer.attn.q_proj.weight, 3 * aw)
@@ -374,7 +382,7 @@ class _Embed(torch.autograd.Function):
         ctx.engine = engine
         ctx.save_for_backward(ids)
         ctx.weight = weight
-        return K.embedding(weight, ids)
+        return K.embedding(engine.embedding_table(), ids)
 
     @staticmethod
     def backward(ctx, grad):
@@ -406,6 +414,7 @@ class _Block(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad):
+        ctx.engine.prepare_block(ctx.index, True)
         if ctx.recompute:
             (x,) = ctx.saved_tensors
             saved = block_forward(ctx.engine, ctx.index, x, ctx.B, ctx.T)[1]

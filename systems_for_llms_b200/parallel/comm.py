@@ -48,6 +48,7 @@ for _name, _args in {
     "sfl_adamw_allgather": [_C, c_long, c_long, _P, _P, _P, c_float, c_float, c_float, c_float,
                             c_float, c_float, c_float, _P, _P, c_int, c_uint, c_int, _P, _P],
     "sfl_allgather_bytes": [_C, c_long, c_long, c_int, c_uint, c_int, _P, _P],
+    "sfl_allgather_into": [_C, c_long, c_long, _P, c_int, c_uint, c_int, _P, _P],
     "sfl_reduce_rows_resid": [_C, c_long, c_long, _P, c_long, c_int, c_int, c_uint, c_int, _P, _P],
     "sfl_reduce_rows_bf16": [_C, c_long, c_long, c_long, c_int, c_int, c_uint, c_int, _P, _P],
     "sfl_allreduce_rows_f32": [_C, c_long, c_long, c_long, c_int, c_uint, c_int, _P, _P],
@@ -171,10 +172,13 @@ class PeerComm:
 
     def reduce_scatter(self, buffer: SymmetricBuffer, offset: int, count: int, scale: float,
                        out: torch.Tensor | None, slot: int,
-                       accumulate_partial: bool = False) -> None:
+                       accumulate_partial: bool = False, accumulate_out: bool = False) -> None:
+        """Rank r keeps ``scale * sum`` of slice r (compact in ``out``); with
+        ``accumulate_out`` the result is added to what ``out`` already holds."""
+        flags = int(accumulate_partial) | (int(accumulate_out) << 1)
         code = _lib.lib().sfl_reduce_scatter_f32(
             ctypes.byref(self.struct(buffer)), offset, count, scale, _lib.ptr(out), slot,
-            self.next_epoch(slot), int(accumulate_partial), self.ctas, self.status.data_ptr(),
+            self.next_epoch(slot), flags, self.ctas, self.status.data_ptr(),
             _lib.stream_ptr())
         _lib.check(code, "sfl_reduce_scatter_f32")
 
@@ -206,6 +210,14 @@ class PeerComm:
             ctypes.byref(self.struct(buffer)), offset_bytes, chunk_bytes, slot,
             self.next_epoch(slot), self.ctas, self.status.data_ptr(), _lib.stream_ptr())
         _lib.check(code, "sfl_allgather_bytes")
+
+    def allgather_into(self, source: SymmetricBuffer, src_offset_bytes: int, chunk_bytes: int,
+                       dst: torch.Tensor, slot: int) -> None:
+        """``dst`` (local) receives chunk r from every peer r's ``source`` buffer."""
+        code = _lib.lib().sfl_allgather_into(
+            ctypes.byref(self.struct(source)), src_offset_bytes, chunk_bytes, dst.data_ptr(),
+            slot, self.next_epoch(slot), self.ctas, self.status.data_ptr(), _lib.stream_ptr())
+        _lib.check(code, "sfl_allgather_into")
 
     def reduce_rows_resid(self, partial: SymmetricBuffer, out: SymmetricBuffer, in_off: int,
                           out_off: int, resid: torch.Tensor | None, rows: int, cols: int,

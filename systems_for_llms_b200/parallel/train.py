@@ -157,8 +157,15 @@ class Strategy:
                 from .tensor_parallel import enable_fused
                 self.engine = enable_fused(base_model, autocast(config, device))
         elif mode == "fsdp":
-            from .fsdp import shard_model
-            self.model = shard_model(base_model)
+            if fused_possible:
+                with autocast(config, device):
+                    self.engine = base_model.fused_engine()
+            if self.engine is not None:
+                from .fsdp_fused import FusedShardedTransformer
+                self.model = FusedShardedTransformer(base_model, self.engine)
+            else:
+                from .fsdp import shard_model
+                self.model = shard_model(base_model)
         if fused_possible and mode in ("single", "naive", "ddp", "zero1"):
             with autocast(config, device):
                 self.engine = base_model.fused_engine()
@@ -175,6 +182,9 @@ class Strategy:
             self.optimizer = ShardedAdamW(base_model.parameters(), **kwargs)
             if self.engine is not None:
                 self.optimizer.attach_flat(self.ddp, self.engine)
+        elif mode == "fsdp" and self.engine is not None:
+            from .fsdp_fused import ShardedStepper
+            self.optimizer = ShardedStepper(self.model, **kwargs)
         elif mode == "fsdp":
             self.optimizer = torch.optim.AdamW(self.model.parameters(), **kwargs)
         else:
@@ -190,6 +200,11 @@ class Strategy:
         if self.mode == "fsdp":
             self.model.set_requires_gradient_sync(last)
         return nullcontext()
+
+    def after_backward(self) -> None:
+        """Called after every microbatch's backward."""
+        if self.mode == "fsdp" and self.engine is not None:
+            self.model.end_microbatch()
 
     def optimizer_state_bytes(self) -> int:
         if self.mode == "zero1":
@@ -220,6 +235,8 @@ class Strategy:
             norm = clip_grad_norm_tp(self.base, config.grad_clip, error_if_nonfinite=True)
             self.optimizer.step()
             return norm
+        if mode == "fsdp" and self.engine is not None:
+            return self.optimizer.clip_and_step(config.grad_clip)
         if mode == "fsdp":
             norm = fsdp_clip_grad_norm(self.model, config.grad_clip)
             self.optimizer.step()
@@ -244,6 +261,8 @@ class Strategy:
             self.optimizer.close()
         if self.ddp is not None:
             self.ddp.close()
+        if self.mode == "fsdp" and hasattr(self.model, "close"):
+            self.model.close()
         if self.engine is not None and self.engine.tp is not None:
             self.engine.tp.close()
             self.engine.tp = None
@@ -269,6 +288,7 @@ def train_step(strategy: Strategy, data, config, sampler, device, *, global_batc
                 loss = strategy.model.loss(x, y, 1.0 / accumulation)
             loss_sum += loss.detach()
             loss.backward()
+            strategy.after_backward()
             del x, y, loss
     # Reference order: vote on finiteness, then clip and update.  The fused
     # update skips itself on a non-finite norm, so the vote can ride along with
@@ -412,6 +432,7 @@ def run(config: TrainConfig, output_dir, *, mode="single", global_batch_size=8,
             "gradient_reduction": ("peer-memory kernels over NVLink"
                                    if (strategy.ddp is not None and strategy.ddp._peer_active())
                                    or (strategy.engine is not None and strategy.engine.tp is not None)
+                                   or (mode == "fsdp" and strategy.engine is not None)
                                    else "torch.distributed collectives"),
             "checkpoint_scope": ("optional final model/optimizer state for correctness checks; "
                                  "resume unsupported"),
