@@ -1,0 +1,7 @@
+"""Reference module path ``attention_lab.benchmark``; the implementation is ``systems_for_llms_b200.attention.benchmark``."""
+
+from systems_for_llms_b200.attention.benchmark import *  # noqa: F401,F403
+from systems_for_llms_b200.attention import benchmark as _impl
+
+if hasattr(_impl, "main") and __name__ == "__main__":
+    raise SystemExit(_impl.main())

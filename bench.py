@@ -61,21 +61,61 @@ def train_config_dict(steps: int, checkpointing: str) -> dict:
 
 
 class ClockSampler:
-    """Polls nvidia-smi while the timed region runs (reading settings only)."""
+    """Samples SM clock and throttle reasons while the timed region runs (reads only).
+
+    NVML is polled from a thread every 10 ms, so even a timed region of a few
+    tens of milliseconds gets samples; ``nvidia-smi -lms`` is the fallback when
+    the NVML binding cannot be loaded.
+    """
 
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
     NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index, self.samples, self.process = index, [], None
+    def __init__(self, index: int, uuid: str | None = None):
+        self.index, self.uuid = index, uuid
+        self.samples, self.process, self.thread = [], None, None
+        self.stop = threading.Event()
+
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        if self.uuid:
+            try:
+                return pynvml, pynvml.nvmlDeviceGetHandleByUUID(f"GPU-{self.uuid}".encode())
+            except pynvml.NVMLError:
+                pass
+        return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.index)
+
+    def _poll_nvml(self, nvml, handle):
+        bits = (nvml.nvmlClocksThrottleReasonHwSlowdown,
+                nvml.nvmlClocksThrottleReasonHwThermalSlowdown,
+                nvml.nvmlClocksThrottleReasonSwThermalSlowdown,
+                nvml.nvmlClocksThrottleReasonSwPowerCap)
+        peak = nvml.nvmlDeviceGetMaxClockInfo(handle, nvml.NVML_CLOCK_SM)
+        while not self.stop.is_set():
+            try:
+                clock = nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM)
+                mask = nvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                self.samples.append([str(clock), str(peak)]
+                                    + ["Active" if mask & bit else "Not Active" for bit in bits])
+            except nvml.NVMLError:
+                pass
+            self.stop.wait(0.01)
 
     def __enter__(self):
         try:
+            nvml, handle = self._nvml_handle()
+            self.thread = threading.Thread(target=self._poll_nvml, args=(nvml, handle), daemon=True)
+            self.thread.start()
+            return self
+        except Exception:
+            self.thread = None
+        try:
             self.process = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "200"],
+                 "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -89,6 +129,9 @@ class ClockSampler:
                 self.samples.append(parts)
 
     def __exit__(self, *exc):
+        self.stop.set()
+        if self.thread is not None:
+            self.thread.join(timeout=1.0)
         if self.process is not None:
             self.process.terminate()
         return False
@@ -101,6 +144,14 @@ class ClockSampler:
                    if any(s[2 + i].lower().startswith("active") for s in self.samples)]
         return {"sm_mhz": clocks[len(clocks) // 2], "sm_max_mhz": int(self.samples[0][1]),
                 "reasons": reasons, "samples": len(self.samples)}
+
+
+def device_uuid(index: int) -> str | None:
+    try:
+        import torch
+        return str(torch.cuda.get_device_properties(index).uuid)
+    except Exception:
+        return None
 
 
 def env_ranks() -> tuple[int, int, int]:
@@ -184,7 +235,7 @@ def run_ours(args) -> None:
     check_status(device)
     launches_before = kernel_lib.launch_count()
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clocks:
+    with ClockSampler(local_rank, device_uuid(local_rank)) as clocks:
         begin.record()
         for step in range(args.steps):
             set_lr(args.warmup + step)
@@ -221,7 +272,7 @@ def run_ours(args) -> None:
             "data": "synthetic uniform-random token ids, random-init weights", "impl": "ours",
             "config": {"model": "324M decoder (24 layers, d_model 1024, 16 heads, d_ff 2752, vocab 10000)",
                        "global_batch": GLOBAL_BATCH, "seq_len": SEQ, "microbatch": MICROBATCH,
-                       "parallelism": f"{mode}{world}" if world > 1 else "single",
+                       "parallelism": f"{mode}-{world}gpu" if world > 1 else "single",
                        "checkpointing": args.checkpointing,
                        "cache": "working set (weights, gradients, optimizer state, activations: "
                                 "several GB) far exceeds the 126 MB L2 between steps"},
@@ -276,7 +327,7 @@ def run_reference(args) -> None:
                     break
                 time.sleep(0.1)
             workdir = Path(marker.read_text())
-    with ClockSampler(env_ranks()[2]) as clocks:
+    with ClockSampler(env_ranks()[2], device_uuid(env_ranks()[2])) as clocks:
         summary = ref_runner.run(config, workdir, mode=mode, global_batch_size=GLOBAL_BATCH,
                                  microbatch_size=MICROBATCH, warmup_steps=args.warmup,
                                  sync_policy="last", bucket_cap_mb=25.0)
@@ -292,7 +343,7 @@ def run_reference(args) -> None:
             "impl": "reference",
             "config": {"model": "324M decoder (24 layers, d_model 1024, 16 heads, d_ff 2752, vocab 10000)",
                        "global_batch": GLOBAL_BATCH, "seq_len": SEQ, "microbatch": MICROBATCH,
-                       "parallelism": f"{mode}{world}" if world > 1 else "single",
+                       "parallelism": f"{mode}-{world}gpu" if world > 1 else "single",
                        "timing": "the reference's own host-timed synchronized steps, max over ranks"},
             "clocks": clocks.summary(),
             "e2e": {"value": summary["tokens_per_second"], "unit": "tokens/s",

@@ -9,8 +9,10 @@ the kernel and the baselines - native causal / dense SDPA where the mask allows,
 SDPA with an explicit boolean mask otherwise.  ``time_cuda`` captures
 ``inner_repeats`` calls in a CUDA graph and reports the median of ``repeats``
 event-timed replays, so launch overhead is excluded the same way for every
-contestant.  FlexAttention is not a contestant here: it is a Triton code
-generator and this package carries no Triton.
+contestant.  FlexAttention (PyTorch's compiled block-mask attention) is an
+optional third baseline, requested with ``include_flex``; it is library code
+that is only ever timed against, and a failure to compile it is recorded in
+the result rather than raised.
 """
 
 from __future__ import annotations
@@ -19,6 +21,7 @@ import argparse
 import json
 import math
 import statistics
+import time
 
 import torch
 
@@ -89,7 +92,65 @@ def time_cuda(function, *, repeats: int = 20, inner_repeats: int = 10, warmup: i
         end.synchronize()
         samples.append(begin.elapsed_time(end) / inner_repeats)
     return {"median_ms": statistics.median(samples), "min_ms": min(samples),
-            "max_ms": max(samples), "repeats": repeats, "inner_repeats": inner_repeats}
+            "max_ms": max(samples), "samples_ms": samples, "mode": "cuda_graph",
+            "repeats": repeats, "inner_repeats": inner_repeats}
+
+
+_FLEX_CACHE: dict = {}
+
+
+def flex_baseline(q, k, v, spec: MaskSpec, document_ids, want, tolerance, *, contiguous=False,
+                  repeats=20, inner_repeats=10) -> dict:
+    """Time compiled FlexAttention on the same inputs; never raises.
+
+    The mask predicate is written from the spec alone (it never reads a block
+    schedule).  ``contiguous`` hands the library the same fact the interval
+    kernel uses - for causal/window masks the key blocks of a query block form
+    one contiguous run - through its ``BLOCKS_ARE_CONTIGUOUS`` kernel option
+    (reference: attention_lab/benchmark.py:93-102); it is refused for document masks.
+    """
+    record = {"status": "failed", "correct": False, "contiguous_hint": bool(contiguous)}
+    try:
+        if contiguous and spec.same_document:
+            raise ValueError("the contiguous-block hint needs a mask without documents")
+        options = {"BLOCKS_ARE_CONTIGUOUS": True} if contiguous else {}
+        from torch.nn.attention.flex_attention import create_block_mask, flex_attention
+        length = q.shape[2]
+        labels = (None if document_ids is None
+                  else torch.as_tensor(list(document_ids), device=q.device))
+
+        def predicate(b, h, qi, ki):
+            ok = qi >= 0
+            if spec.causal:
+                ok = ok & (ki <= qi)
+            if spec.window_left is not None:
+                ok = ok & (ki >= qi - spec.window_left)
+            if spec.window_right is not None:
+                ok = ok & (ki <= qi + spec.window_right)
+            if spec.same_document:
+                ok = ok & (labels[qi] == labels[ki])
+            return ok
+
+        begin = time.perf_counter()
+        block = create_block_mask(predicate, None, None, length, length, device=q.device,
+                                  BLOCK_SIZE=128)
+        compiled = _FLEX_CACHE.setdefault("fn", torch.compile(flex_attention, dynamic=False))
+        out = compiled(q, k, v, block_mask=block, kernel_options=options)
+        torch.cuda.synchronize()
+        record["first_call_ms"] = (time.perf_counter() - begin) * 1000
+        atol, rtol = tolerance
+        record["max_abs_error"] = (out.float() - want).abs().max().item()
+        record["correct"] = bool(torch.allclose(out.float(), want, atol=atol, rtol=rtol))
+        if record["correct"]:
+            timing = time_cuda(lambda: compiled(q, k, v, block_mask=block,
+                                                kernel_options=options), repeats=repeats,
+                               inner_repeats=inner_repeats)
+            record.update(status="passed", latency_ms=timing["median_ms"], timing=timing)
+        else:
+            record["error"] = "FlexAttention output outside tolerance"
+    except Exception as error:
+        record.update(error_type=type(error).__name__, error=str(error)[:2000])
+    return record
 
 
 def attention_flops(batch: int, heads: int, length: int, dim: int, mask_fraction: float) -> float:
@@ -101,7 +162,8 @@ def run_case(*, batch: int = 1, heads: int = 8, length: int = 1024, dim: int = 6
              schedule: BlockSchedule | None = None, implementation: str = "interval",
              block_q: int = 128, block_k: int = 128, use_full_blocks: bool = True, seed: int = 0,
              backward: bool = False, repeats: int = 20, inner_repeats: int = 10,
-             time_baselines: bool = True, device: str = "cuda") -> dict:
+             warmup: int = 3, time_baselines: bool = True, include_flex: bool = False,
+             flex_contiguous: bool = False, device: str = "cuda") -> dict:
     torch_dtype = DTYPES[dtype]
     generator = torch.Generator().manual_seed(seed)
     q, k, v = (torch.randn(batch, heads, length, dim, generator=generator).to(torch_dtype)
@@ -111,9 +173,12 @@ def run_case(*, batch: int = 1, heads: int = 8, length: int = 1024, dim: int = 6
                                 None if document_ids is None else list(document_ids))
     mask = dense_mask(length, spec, document_ids, schedule).to(device)
     before = [t.clone() for t in (q, k, v)]
+    torch.cuda.synchronize()
+    first_call = time.perf_counter()
     out = flash.attention(q, k, v, schedule, spec, document_ids=document_ids,
                           implementation=implementation, use_full_blocks=use_full_blocks)
     torch.cuda.synchronize()
+    first_call_ms = (time.perf_counter() - first_call) * 1000
     want = reference_attention(q, k, v, mask)
     atol, rtol = TOLERANCE[torch_dtype]
     error = (out.float() - want).abs().max().item()
@@ -125,7 +190,8 @@ def run_case(*, batch: int = 1, heads: int = 8, length: int = 1024, dim: int = 6
                        "window_right": spec.window_right, "same_document": spec.same_document},
               "implementation": implementation, "block_q": block_q, "block_k": block_k,
               "use_full_blocks": use_full_blocks, "seed": seed, "correct": correct,
-              "max_abs_error": error, "mask_density": fraction, "inputs_unchanged": True}
+              "max_abs_error": error, "mask_density": fraction, "first_call_ms": first_call_ms,
+              "status": "passed" if correct else "failed_correctness"}
     if not correct:
         result["error"] = "kernel output outside tolerance or inputs modified"
         return result
@@ -134,7 +200,7 @@ def run_case(*, batch: int = 1, heads: int = 8, length: int = 1024, dim: int = 6
     lse = torch.empty(batch, heads, length, dtype=torch.float32, device=device)
     scale = dim ** -0.5
     timing = time_cuda(lambda: flash.flash_fwd(q, k, v, output, lse, prepared, scale),
-                       repeats=repeats, inner_repeats=inner_repeats)
+                       repeats=repeats, inner_repeats=inner_repeats, warmup=warmup)
     flops = attention_flops(batch, heads, length, dim, fraction)
     result.update(latency_ms=timing["median_ms"], timing=timing,
                   tflops_effective=flops / timing["median_ms"] / 1e9,
@@ -162,6 +228,10 @@ def run_case(*, batch: int = 1, heads: int = 8, length: int = 1024, dim: int = 6
             result["baseline"] = "sdpa_bool_mask"
         result.update(baseline_latency_ms=base["median_ms"],
                       baseline_over_custom=base["median_ms"] / timing["median_ms"])
+    if include_flex:
+        result["flex"] = flex_baseline(q, k, v, spec, document_ids, want, (atol, rtol),
+                                       contiguous=flex_contiguous, repeats=repeats,
+                                       inner_repeats=inner_repeats)
     return result
 
 
