@@ -989,9 +989,15 @@ extern "C" int sfl_attn_bwd(const SflAttnTensor* q, const SflAttnTensor* k, cons
     return -2;
   if (mask->mode == 0 && (mask->t_row_ptr == nullptr || mask->t_col_idx == nullptr)) return -2;
   CUtensorMap tq, tk, tv, tdo;
-  if (make_map(&tq, q->ptr, *q, B, H, N, D) || make_map(&tk, k->ptr, *k, B, H, N, D) ||
-      make_map(&tv, v->ptr, *v, B, H, N, D) || make_map(&tdo, d_o->ptr, *d_o, B, H, N, D))
-    return -3;
+  {
+    // -3000 - 100 * operand - driver code tells which map was refused and why
+    const SflAttnTensor* operands[4] = {q, k, v, d_o};
+    CUtensorMap* maps[4] = {&tq, &tk, &tv, &tdo};
+    for (int i = 0; i < 4; ++i) {
+      const int rc = make_map(maps[i], operands[i]->ptr, *operands[i], B, H, N, D);
+      if (rc) return -3000 - 100 * i - (rc > 0 && rc < 100 ? rc : 99);
+    }
+  }
   {
     const long rows = static_cast<long>(B) * H * N;
     const int warps = 8;

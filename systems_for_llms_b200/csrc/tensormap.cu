@@ -40,10 +40,21 @@ int make_tensormap_nd_b16(CUtensorMap* out, const void* base, int rank, const ui
   if (swizzle == 1) sw = CU_TENSOR_MAP_SWIZZLE_32B;
   if (swizzle == 2) sw = CU_TENSOR_MAP_SWIZZLE_64B;
   if (swizzle == 3) sw = CU_TENSOR_MAP_SWIZZLE_128B;
-  CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank),
-                      const_cast<void*>(base), gdim, gstride, bdim, estride,
-                      CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  auto call = [&] {
+    return encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank),
+                  const_cast<void*>(base), gdim, gstride, bdim, estride,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  };
+  CUresult r = call();
+  if (r == CUDA_ERROR_INVALID_CONTEXT || r == CUDA_ERROR_NOT_INITIALIZED) {
+    // The encoder is a driver entry point and needs a context current on the
+    // calling thread.  A thread that has made no runtime call yet (an autograd
+    // worker running one of these ops as its first CUDA work) has none: a
+    // runtime call binds the device's primary context, then encode again.
+    cudaFree(nullptr);
+    r = call();
+  }
   return static_cast<int>(r);
 }
 

@@ -127,3 +127,25 @@ def test_input_validation(dev):
                         q[..., :32].contiguous(), None, MaskSpec())
     with pytest.raises(TypeError):
         flash.attention(q.float(), q.float(), q.float(), None, MaskSpec())
+
+
+def test_backward_as_first_cuda_work_of_the_autograd_thread(dev):
+    """Tensor maps are encoded through a driver entry point, which needs a context
+    on the calling thread; a fresh process whose autograd worker has done no CUDA
+    runtime call before this backward must still succeed."""
+    import subprocess
+    import sys
+    from pathlib import Path
+    script = (
+        "import torch\n"
+        "from systems_for_llms_b200.attention import backward_study as b\n"
+        "from systems_for_llms_b200.attention.masks import MaskSpec\n"
+        "r = b.numerical_case(129, 64, torch.float16, MaskSpec(causal=True), None)\n"
+        "assert r['status'] == 'passed', r\n"
+        "docs = tuple((i // 7) % 3 - 1 for i in range(65))\n"
+        "r = b.numerical_case(65, 128, torch.bfloat16, MaskSpec(causal=True, same_document=True),"
+        " docs, tile_q=64, tile_k=32)\n"
+        "assert r['status'] == 'passed', r\n")
+    done = subprocess.run([sys.executable, "-c", script], cwd=Path(__file__).resolve().parents[1],
+                          capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0, done.stdout + done.stderr
