@@ -4,8 +4,9 @@
 //
 // One CTA per SM walks output tiles of 128 x BN.  Warp 0 streams operand tiles
 // into a shared-memory ring with TMA, warp 1 issues tcgen05.mma into one of two
-// TMEM accumulator stages, warps 2-5 drain the other stage through a fused
-// epilogue, so the epilogue of tile i overlaps the main loop of tile i+1.
+// TMEM accumulator stages, warps 2-9 drain the other stage through a fused
+// epilogue (two warps per TMEM lane quarter, alternating column chunks), so the
+// epilogue of tile i overlaps the main loop of tile i+1.
 //
 // Either operand may be "K-major" (reduction dimension contiguous in memory) or
 // "MN-major" (the M/N dimension contiguous), which lets one kernel serve the
@@ -24,10 +25,21 @@
 //   EPI_SWIGLU      dual accumulator (w1 x | w3 x): stores both and
 //                   silu(w1 x) * w3 x   (src/llmlab/model/layers.py:114-115)
 //   EPI_SWIGLU_BWD  acc = d(silu(a1)*a3); stores d a1 | d a3
+//
+// Epilogue data path.  When the output (and auxiliary) matrices satisfy TMA's
+// alignment rules, each epilogue warp owns a private strip of shared memory:
+// accumulator rows come out of TMEM one row per thread, are converted and
+// written into a 128-byte-swizzled 32-row staging tile, and one lane hands the
+// tile to the TMA engine (bulk tensor store, or bulk reduce-add for beta = 1), so
+// global traffic is fully coalesced and asynchronous.  Auxiliary operands
+// (the residual stream, the saved SwiGLU pre-activations) arrive the same way,
+// one chunk ahead of their use.  Matrices that break the alignment rules take
+// the direct path: each thread stores its own row.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include <map>
 #include <mutex>
@@ -71,16 +83,47 @@ struct GemmParams {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;  // two per TMEM lane quarter
+constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr int kTileABytes = BM * BK * 2;
 
-template <int BN>
+// Per-epilogue shape of the staged (TMA) data path: accumulator columns handled
+// per step, and how many 4 KB (32 rows x 128 B) tiles each epilogue warp owns.
+// Auxiliary inputs are loaded into the very tiles the results are stored from.
+template <int EPI>
+struct EpiTraits;
+template <> struct EpiTraits<EPI_BF16> { static constexpr int kChunk = 64, kTiles = 1; };
+template <> struct EpiTraits<EPI_F32> { static constexpr int kChunk = 32, kTiles = 1; };
+template <> struct EpiTraits<EPI_RESID> { static constexpr int kChunk = 32, kTiles = 1; };
+template <> struct EpiTraits<EPI_ROPE> { static constexpr int kChunk = 64, kTiles = 1; };
+template <> struct EpiTraits<EPI_SWIGLU> { static constexpr int kChunk = 64, kTiles = 1; };
+template <> struct EpiTraits<EPI_SWIGLU_BWD> { static constexpr int kChunk = 64, kTiles = 2; };
+
+constexpr int kEpiTileBytes = 32 * 128;
+constexpr int kMaxSmemBytes = 232448;  // 227 KB opt-in limit per CTA
+
+template <int BN, int EPI, bool STAGED>
 struct GemmConfig {
   static constexpr int kTileBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kTileABytes + kTileBBytes;
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kEpiWarpBytes = STAGED ? EpiTraits<EPI>::kTiles * kEpiTileBytes : 0;
+  static constexpr int kEpiBytes = kEpiWarps * kEpiWarpBytes;
+  static constexpr int kFixedBytes = 1024 /*align*/ + 512 /*barriers*/ + kEpiBytes;
+  static constexpr int kWantStages = (BN == 256) ? 4 : 6;
+  static constexpr int kFitStages = (kMaxSmemBytes - kFixedBytes) / kStageBytes;
+  static constexpr int kStages = kFitStages < kWantStages ? kFitStages : kWantStages;
+  static_assert(kStages >= 3, "operand ring too shallow");
   static constexpr int kTmemCols = 2 * BN;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kFixedBytes;
+};
+
+struct EpiMaps {
+  // Role of each map per epilogue:
+  //   BF16 / F32 / ROPE : m[0] output
+  //   RESID             : m[0] output, m[1] residual input
+  //   SWIGLU            : m[0] gated output, m[1] w1 x, m[2] w3 x
+  //   SWIGLU_BWD        : m[0] d a1, m[1] d a3, m[2] a1, m[3] a3
+  CUtensorMap m[4];
 };
 
 struct __align__(8) GemmBarriers {
@@ -88,6 +131,7 @@ struct __align__(8) GemmBarriers {
   uint64_t empty[8];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t aux_full[kEpiWarps];  // per epilogue warp: its auxiliary tile(s) have landed
   uint32_t tmem_base;
   int abort;
 };
@@ -104,6 +148,12 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
 }
 
 // ------------------------------------------------------------- epilogues ----
+// silu(a) * b and its derivatives, with the fast reciprocal: results are rounded
+// to bf16 afterwards, far coarser than the two-ulp error of the approximation.
+__device__ __forceinline__ float fast_sigmoid(float a) {
+  return __fdividef(1.0f, 1.0f + __expf(-a));
+}
+
 template <int EPI>
 struct EpilogueOp;
 
@@ -224,7 +274,7 @@ struct EpilogueOp<EPI_SWIGLU> {
     for (int j = 0; j < 32; ++j) {
       const float a = bf16_round(v[j]);
       const float b = bf16_round(w[j]);
-      g[j] = a / (1.0f + __expf(-a)) * b;
+      g[j] = a * fast_sigmoid(a) * b;
     }
     __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + static_cast<long>(row) * p.ldo + col0;
     store_bf16_row(dst, g, col0, p.N, (p.ldo & 7) == 0);
@@ -263,7 +313,7 @@ struct EpilogueOp<EPI_SWIGLU_BWD> {
     for (int j = 0; j < 32; ++j) {
       const float a = a1[j];
       const float dg = bf16_round(v[j]);
-      const float sig = 1.0f / (1.0f + __expf(-a));
+      const float sig = fast_sigmoid(a);
       const float silu = a * sig;
       a1[j] = dg * a3[j] * (sig + silu * (1.0f - sig));  // d a1
       a3[j] = dg * silu;                                  // d a3
@@ -275,12 +325,351 @@ struct EpilogueOp<EPI_SWIGLU_BWD> {
   }
 };
 
+
+// ------------------------------------------------- staged (TMA) epilogue ----
+// A staging tile is 32 rows of 128 bytes in the 128-byte swizzle the tensor maps
+// use: 16-byte chunk c of row r lives at chunk position c ^ (r & 7).  With one
+// row per lane, the eight lanes of a quarter-warp hit eight different chunk
+// positions, so 16-byte accesses are free of bank conflicts.
+__device__ __forceinline__ uint8_t* staged_chunk(uint8_t* tile, int row, int chunk) {
+  return tile + row * 128 + ((chunk ^ (row & 7)) << 4);
+}
+
+__device__ __forceinline__ void stage_bf16_half(uint8_t* tile, int row, int half,
+                                                const float (&v)[32]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint4 q;
+    q.x = pack_bf16(v[8 * j + 0], v[8 * j + 1]);
+    q.y = pack_bf16(v[8 * j + 2], v[8 * j + 3]);
+    q.z = pack_bf16(v[8 * j + 4], v[8 * j + 5]);
+    q.w = pack_bf16(v[8 * j + 6], v[8 * j + 7]);
+    *reinterpret_cast<uint4*>(staged_chunk(tile, row, 4 * half + j)) = q;
+  }
+}
+
+__device__ __forceinline__ void stage_f32(uint8_t* tile, int row, const float (&v)[32]) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    *reinterpret_cast<float4*>(staged_chunk(tile, row, j)) =
+        make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+}
+
+__device__ __forceinline__ void unstage_f32(uint8_t* tile, int row, float (&v)[32]) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float4 q = *reinterpret_cast<const float4*>(staged_chunk(tile, row, j));
+    v[4 * j] = q.x; v[4 * j + 1] = q.y; v[4 * j + 2] = q.z; v[4 * j + 3] = q.w;
+  }
+}
+
+__device__ __forceinline__ void unpack_bf16x8(const uint4& q, float* v) {
+  const float2 a = unpack_bf16(q.x), b = unpack_bf16(q.y), c = unpack_bf16(q.z),
+               d = unpack_bf16(q.w);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+  v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+}
+
+__device__ __forceinline__ void load_acc32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  tmem_ld_32x32(taddr, r);
+  tmem_ld_wait();
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+}
+
+// Rotates the 16 interleaved pairs of a 32-column run that starts at `col`.
+__device__ __forceinline__ void rope_rotate32(const GemmParams& p, int row, int col,
+                                              float (&v)[32]) {
+  const int pos = row % p.rope_T;
+  const int half = p.head_dim >> 1;
+  const int pair0 = (col % p.head_dim) >> 1;
+  const float4* cs = reinterpret_cast<const float4*>(p.rope_cos + static_cast<long>(pos) * half + pair0);
+  const float4* sn = reinterpret_cast<const float4*>(p.rope_sin + static_cast<long>(pos) * half + pair0);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float4 c4 = cs[j], s4 = sn[j];
+    const float c[4] = {c4.x, c4.y, c4.z, c4.w};
+    const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float xe = bf16_round(v[8 * j + 2 * i]);
+      const float xo = bf16_round(v[8 * j + 2 * i + 1]);
+      v[8 * j + 2 * i] = xe * c[i] - xo * sv[i];
+      v[8 * j + 2 * i + 1] = xe * sv[i] + xo * c[i];
+    }
+  }
+}
+
+// Two warps serve each TMEM lane quarter (a warp may only read the 32 lanes
+// selected by warp_id % 4); `part` 0/1 takes the even/odd column chunks of every
+// tile, so each scheduler has two epilogue warps to hide latency with.
+template <int BN, int EPI>
+__device__ __forceinline__ void staged_epilogue(const GemmParams& p, const EpiMaps& em,
+                                                GemmBarriers* bars, uint8_t* warp_smem,
+                                                uint32_t tmem_base, int quarter, int part,
+                                                int lane, int num_tiles, volatile int* abort) {
+  using T = EpiTraits<EPI>;
+  constexpr bool kDual = (EPI == EPI_SWIGLU);
+  constexpr bool kHasAux = (EPI == EPI_RESID || EPI == EPI_SWIGLU_BWD);
+  constexpr int BN_OUT = kDual ? BN / 2 : BN;
+  constexpr int CW = T::kChunk;
+  constexpr int kChunksPerTile = BN_OUT / CW;
+  uint8_t* tile0 = warp_smem;
+  uint8_t* tile1 = warp_smem + kEpiTileBytes;  // only epilogues with two tiles touch it
+  uint64_t* aux_bar = &bars->aux_full[part * 4 + quarter];
+  uint32_t aux_phase = 0;
+  int acc = 0;
+  uint32_t acc_phase = 0;
+
+  auto chunks_in = [&](int tile) {
+    const int n = (p.N - (tile / p.num_m_tiles) * BN_OUT + CW - 1) / CW;
+    return n < kChunksPerTile ? n : kChunksPerTile;
+  };
+  // Auxiliary operands land in the tiles the results are later stored from.
+  auto load_aux = [&](int tile, int c) {  // one lane
+    const int y = (tile % p.num_m_tiles) * BM + quarter * 32;
+    const int x = (tile / p.num_m_tiles) * BN_OUT + c * CW;
+    if constexpr (EPI == EPI_RESID) {
+      mbar_expect_tx(aux_bar, kEpiTileBytes);
+      tma_load_2d(tile0, &em.m[1], aux_bar, x, y);
+    } else if constexpr (EPI == EPI_SWIGLU_BWD) {
+      mbar_expect_tx(aux_bar, 2 * kEpiTileBytes);
+      tma_load_2d(tile0, &em.m[2], aux_bar, x, y);
+      tma_load_2d(tile1, &em.m[3], aux_bar, x, y);
+    }
+  };
+  // First chunk of this warp at or after (tile, c): returns false when none is left.
+  auto next_chunk = [&](int& tile, int& c) {
+    while (tile < num_tiles) {
+      if (c < chunks_in(tile)) return true;
+      tile += gridDim.x;
+      c = part;
+    }
+    return false;
+  };
+  if constexpr (kHasAux) {
+    if (lane == 0) {
+      int t = blockIdx.x, c = part;
+      if (next_chunk(t, c)) load_aux(t, c);
+    }
+  }
+
+  bool ok = true;
+  for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    const int m0 = (tile % p.num_m_tiles) * BM;
+    const int n0 = (tile / p.num_m_tiles) * BN_OUT;
+    const int nchunks = chunks_in(tile);
+    if (!wait_or_abort(&bars->tmem_full[acc], acc_phase, abort)) {
+      report_status(p.status, kStatusTimeoutTmemFull);
+      *abort = 1;
+      break;
+    }
+    tc_fence_after();
+    const int row0 = m0 + quarter * 32;
+    const int row = row0 + lane;
+    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+    for (int c = part; c < nchunks; c += 2) {
+      const int col0 = n0 + c * CW;
+      if constexpr (kHasAux) {
+        if (!wait_or_abort(aux_bar, aux_phase, abort)) {
+          report_status(p.status, kStatusTimeoutFull);
+          *abort = 1;
+          ok = false;
+          break;
+        }
+        aux_phase ^= 1;
+      }
+      if constexpr (EPI == EPI_BF16 || EPI == EPI_ROPE) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float v[32];
+          load_acc32(t_row + c * CW + h * 32, v);
+          if constexpr (EPI == EPI_ROPE) {
+            if (col0 + h * 32 < p.rope_cols) rope_rotate32(p, row, col0 + h * 32, v);
+          }
+          if (h == 0) {
+            if (lane == 0) tma_store_wait_read<0>();  // previous store has left the tile
+            __syncwarp();
+          }
+          stage_bf16_half(tile0, lane, h, v);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&em.m[0], tile0, col0, row0);
+          tma_store_commit();
+        }
+      } else if constexpr (EPI == EPI_F32) {
+        float v[32];
+        load_acc32(t_row + c * CW, v);
+        if (lane == 0) tma_store_wait_read<0>();
+        __syncwarp();
+        stage_f32(tile0, lane, v);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (p.beta) tma_reduce_add_2d(&em.m[0], tile0, col0, row0);
+          else tma_store_2d(&em.m[0], tile0, col0, row0);
+          tma_store_commit();
+        }
+      } else if constexpr (EPI == EPI_RESID) {
+        float v[32], res[32];
+        unstage_f32(tile0, lane, res);
+        load_acc32(t_row + c * CW, v);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) res[j] += bf16_round(v[j]);
+        stage_f32(tile0, lane, res);  // each lane rewrites exactly the bytes it read
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&em.m[0], tile0, col0, row0);
+          tma_store_commit();
+          int t = tile, cn = c + 2;
+          if (next_chunk(t, cn)) {
+            tma_store_wait_read<0>();  // the tile is refilled only after the store has read it
+            load_aux(t, cn);
+          }
+        }
+      } else if constexpr (EPI == EPI_SWIGLU) {
+        // One tile, used three times: w1 x, w3 x, then the gated product.
+        uint4 keep3[8], gated[8];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float v[32], w[32];
+          {
+            uint32_t r[32], r2[32];
+            tmem_ld_32x32(t_row + c * CW + h * 32, r);
+            tmem_ld_32x32(t_row + BN / 2 + c * CW + h * 32, r2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              v[j] = __uint_as_float(r[j]);
+              w[j] = __uint_as_float(r2[j]);
+            }
+          }
+          if (h == 0) {
+            if (lane == 0) tma_store_wait_read<0>();
+            __syncwarp();
+          }
+          stage_bf16_half(tile0, lane, h, v);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            keep3[4 * h + j].x = pack_bf16(w[8 * j + 0], w[8 * j + 1]);
+            keep3[4 * h + j].y = pack_bf16(w[8 * j + 2], w[8 * j + 3]);
+            keep3[4 * h + j].z = pack_bf16(w[8 * j + 4], w[8 * j + 5]);
+            keep3[4 * h + j].w = pack_bf16(w[8 * j + 6], w[8 * j + 7]);
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float a = bf16_round(v[j]);
+            v[j] = a * fast_sigmoid(a) * bf16_round(w[j]);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            gated[4 * h + j].x = pack_bf16(v[8 * j + 0], v[8 * j + 1]);
+            gated[4 * h + j].y = pack_bf16(v[8 * j + 2], v[8 * j + 3]);
+            gated[4 * h + j].z = pack_bf16(v[8 * j + 4], v[8 * j + 5]);
+            gated[4 * h + j].w = pack_bf16(v[8 * j + 6], v[8 * j + 7]);
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&em.m[1], tile0, col0, row0);
+          tma_store_commit();
+          tma_store_wait_read<0>();
+        }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<uint4*>(staged_chunk(tile0, lane, j)) = keep3[j];
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&em.m[2], tile0, col0, row0);
+          tma_store_commit();
+          tma_store_wait_read<0>();
+        }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<uint4*>(staged_chunk(tile0, lane, j)) = gated[j];
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&em.m[0], tile0, col0, row0);
+          tma_store_commit();
+        }
+      } else if constexpr (EPI == EPI_SWIGLU_BWD) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float v[32], a1[32], a3[32];
+          load_acc32(t_row + c * CW + h * 32, v);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            unpack_bf16x8(*reinterpret_cast<const uint4*>(staged_chunk(tile0, lane, 4 * h + j)),
+                          a1 + 8 * j);
+            unpack_bf16x8(*reinterpret_cast<const uint4*>(staged_chunk(tile1, lane, 4 * h + j)),
+                          a3 + 8 * j);
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float a = a1[j];
+            const float dg = bf16_round(v[j]);
+            const float sig = fast_sigmoid(a);
+            const float silu = a * sig;
+            a1[j] = dg * a3[j] * (sig + silu * (1.0f - sig));
+            a3[j] = dg * silu;
+          }
+          stage_bf16_half(tile0, lane, h, a1);  // results replace the inputs they came from
+          stage_bf16_half(tile1, lane, h, a3);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&em.m[0], tile0, col0, row0);
+          tma_store_2d(&em.m[1], tile1, col0, row0);
+          tma_store_commit();
+          int t = tile, cn = c + 2;
+          if (next_chunk(t, cn)) {
+            tma_store_wait_read<0>();
+            load_aux(t, cn);
+          }
+        }
+      }
+    }
+    tc_fence_before();
+    mbar_arrive(&bars->tmem_empty[acc]);
+    if (++acc == 2) {
+      acc = 0;
+      acc_phase ^= 1;
+    }
+  }
+  if (lane == 0) tma_store_wait<0>();
+}
+
+// Staged instantiations exist for the operand layouts the model uses; anything
+// else goes through the direct epilogue.
+template <int EPI, bool A_MN, bool B_MN>
+constexpr bool staged_supported() {
+  switch (EPI) {
+    case EPI_BF16: return !A_MN;
+    case EPI_F32: return A_MN && B_MN;
+    case EPI_RESID: return !A_MN && !B_MN;
+    case EPI_ROPE: return !A_MN && !B_MN;
+    case EPI_SWIGLU: return !A_MN && !B_MN;
+    case EPI_SWIGLU_BWD: return !A_MN && B_MN;
+    default: return false;
+  }
+}
+
 // ---------------------------------------------------------------- kernel ----
-template <int BN, bool A_MN, bool B_MN, int EPI>
+template <int BN, bool A_MN, bool B_MN, int EPI, bool STAGED>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const GemmParams p) {
-  using Cfg = GemmConfig<BN>;
+            const __grid_constant__ EpiMaps em, const GemmParams p) {
+  using Cfg = GemmConfig<BN, EPI, STAGED>;
   constexpr bool kDual = (EPI == EPI_SWIGLU);
   // In dual mode the logical N tile is BN/2 wide: the B tile stacks BN/2 rows of
   // the first matrix on BN/2 rows of the second.
@@ -290,7 +679,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint8_t* epi_smem = smem + Cfg::kStages * Cfg::kStageBytes;  // 1024-byte aligned
+  GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(epi_smem + Cfg::kEpiBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -304,12 +694,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bars->tmem_full[s], 1);
-      mbar_init(&bars->tmem_empty[s], 128);
+      mbar_init(&bars->tmem_empty[s], 32 * kEpiWarps);
     }
+    for (int s = 0; s < kEpiWarps; ++s) mbar_init(&bars->aux_full[s], 1);
     bars->abort = 0;
     mbar_fence_init();
     prefetch_tensormap(&tmA);
     prefetch_tensormap(&tmB);
+    if constexpr (STAGED) {
+      for (int i = 0; i < 4; ++i) prefetch_tensormap(&em.m[i]);
+    }
   }
   if (warp == 1) {
     tmem_alloc(&bars->tmem_base, Cfg::kTmemCols);
@@ -414,9 +808,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
       }
     }
-  } else {
-    // ---------------------------------------------------------- epilogue ----
+  } else if constexpr (STAGED) {
     const int quarter = warp & 3;  // TMEM lanes this warp may read
+    const int part = (warp - 2) >> 2;
+    staged_epilogue<BN, EPI>(p, em, bars, epi_smem + (warp - 2) * Cfg::kEpiWarpBytes, tmem_base,
+                             quarter, part, lane, num_tiles, abort);
+  } else {
+    // --------------------------------------------------- direct epilogue ----
+    const int quarter = warp & 3;
+    const int part = (warp - 2) >> 2;  // even / odd 32-column chunks
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
@@ -431,7 +831,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int row = m0 + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN_OUT / 32; ++c) {
+      for (int c = part; c < BN_OUT / 32; c += 2) {
         const int col0 = n0 + c * 32;
         if (col0 >= p.N) break;  // warp-uniform
         uint32_t r[32];
@@ -474,26 +874,27 @@ struct MapKey {
   const void* base;
   uint64_t inner, outer, ld;
   uint32_t box_inner, box_outer;
+  int elem_bytes;
   bool operator<(const MapKey& o) const {
-    return std::tie(base, inner, outer, ld, box_inner, box_outer) <
-           std::tie(o.base, o.inner, o.outer, o.ld, o.box_inner, o.box_outer);
+    return std::tie(base, inner, outer, ld, box_inner, box_outer, elem_bytes) <
+           std::tie(o.base, o.inner, o.outer, o.ld, o.box_inner, o.box_outer, o.elem_bytes);
   }
 };
 
 // Encoding a tensor map costs a few microseconds on the host; training reuses a
 // small set of (pointer, shape) combinations every step, so keep them.
 int cached_map(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
-               uint32_t box_inner, uint32_t box_outer) {
+               uint32_t box_inner, uint32_t box_outer, int elem_bytes = 2) {
   static std::map<MapKey, CUtensorMap> cache;
   static std::mutex mu;
-  MapKey key{base, inner, outer, ld, box_inner, box_outer};
+  MapKey key{base, inner, outer, ld, box_inner, box_outer, elem_bytes};
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find(key);
   if (it != cache.end()) {
     *out = it->second;
     return 0;
   }
-  int rc = make_tensormap_2d_bf16(out, base, inner, outer, ld, box_inner, box_outer);
+  int rc = make_tensormap_2d(out, base, elem_bytes, inner, outer, ld, box_inner, box_outer);
   if (rc == 0) {
     if (cache.size() > 8192) cache.clear();
     cache.emplace(key, *out);
@@ -512,11 +913,11 @@ int sm_count() {
   return count;
 }
 
-template <int BN, bool A_MN, bool B_MN, int EPI>
-int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int max_ctas,
-           cudaStream_t stream) {
-  using Cfg = GemmConfig<BN>;
-  auto kernel = gemm_kernel<BN, A_MN, B_MN, EPI>;
+template <int BN, bool A_MN, bool B_MN, int EPI, bool STAGED>
+int launch_one(const CUtensorMap& tmA, const CUtensorMap& tmB, const EpiMaps& em,
+               const GemmParams& p, int max_ctas, cudaStream_t stream) {
+  using Cfg = GemmConfig<BN, EPI, STAGED>;
+  auto kernel = gemm_kernel<BN, A_MN, B_MN, EPI, STAGED>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e =
@@ -527,21 +928,32 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, 
   const int tiles = p.num_m_tiles * p.num_n_tiles;
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  kernel<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, p);
+  kernel<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, em, p);
   return static_cast<int>(cudaGetLastError());
+}
+
+template <int BN, bool A_MN, bool B_MN, int EPI>
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const EpiMaps* em, const GemmParams& p,
+           int max_ctas, cudaStream_t stream) {
+  if constexpr (staged_supported<EPI, A_MN, B_MN>()) {
+    if (em != nullptr)
+      return launch_one<BN, A_MN, B_MN, EPI, true>(tmA, tmB, *em, p, max_ctas, stream);
+  }
+  static const EpiMaps none{};
+  return launch_one<BN, A_MN, B_MN, EPI, false>(tmA, tmB, none, p, max_ctas, stream);
 }
 
 template <int BN, int EPI>
 int launch_major(bool a_mn, bool b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB,
-                 const GemmParams& p, int max_ctas, cudaStream_t stream) {
+                 const EpiMaps* em, const GemmParams& p, int max_ctas, cudaStream_t stream) {
   if constexpr (EPI == EPI_SWIGLU) {
     if (a_mn || b_mn) return -3;
-    return launch<BN, false, false, EPI>(tmA, tmB, p, max_ctas, stream);
+    return launch<BN, false, false, EPI>(tmA, tmB, em, p, max_ctas, stream);
   } else {
-    if (!a_mn && !b_mn) return launch<BN, false, false, EPI>(tmA, tmB, p, max_ctas, stream);
-    if (!a_mn && b_mn) return launch<BN, false, true, EPI>(tmA, tmB, p, max_ctas, stream);
-    if (a_mn && b_mn) return launch<BN, true, true, EPI>(tmA, tmB, p, max_ctas, stream);
-    return launch<BN, true, false, EPI>(tmA, tmB, p, max_ctas, stream);
+    if (!a_mn && !b_mn) return launch<BN, false, false, EPI>(tmA, tmB, em, p, max_ctas, stream);
+    if (!a_mn && b_mn) return launch<BN, false, true, EPI>(tmA, tmB, em, p, max_ctas, stream);
+    if (a_mn && b_mn) return launch<BN, true, true, EPI>(tmA, tmB, em, p, max_ctas, stream);
+    return launch<BN, true, false, EPI>(tmA, tmB, em, p, max_ctas, stream);
   }
 }
 
@@ -584,21 +996,81 @@ extern "C" int sfl_gemm_bf16(const void* a, long lda, int a_mn, const void* b, l
 
   // Tile width: pick the one that needs the fewest "tile-time units" of waves.
   int bn = bn_hint;
+  // SFL_GEMM_BN=128|256 overrides the automatic choice (for A/B measurements).
+  static const int forced_bn = [] {
+    const char* v = getenv("SFL_GEMM_BN");
+    return v == nullptr ? 0 : atoi(v);
+  }();
+  if (forced_bn == 128 || forced_bn == 256) bn = forced_bn;
   if (dual) {
     bn = 256;  // 128 columns of each of the two products
   } else if (bn != 128 && bn != 256) {
-    const int sms = sm_count();
-    const int mt = (M + BM - 1) / BM;
-    auto cost = [&](int width) {
-      const long tiles = static_cast<long>(mt) * ((N + width - 1) / width);
-      const long waves = (tiles + sms - 1) / sms;
-      return waves * width;
-    };
-    bn = cost(256) <= cost(128) ? 256 : 128;
+    // 256-wide tiles run the tensor cores measurably closer to peak than 128-wide
+    // ones (the 128-row A tile is re-read from shared memory half as often), so
+    // narrow tiles are only worth it when wide ones would leave more than half
+    // of the SMs without work.
+    const long tiles256 = static_cast<long>((M + BM - 1) / BM) * ((N + 255) / 256);
+    bn = (N <= 128 || 2 * tiles256 <= sm_count()) ? 128 : 256;
   }
   const int bn_out = dual ? bn / 2 : bn;
   p.num_m_tiles = (M + BM - 1) / BM;
   p.num_n_tiles = (N + bn_out - 1) / bn_out;
+
+  // Staged epilogue: every matrix it touches must be addressable by TMA (16-byte
+  // aligned base and row pitch); otherwise the direct epilogue is used.
+  EpiMaps em{};
+  bool staged = false;
+  {
+    auto ok16 = [](const void* ptr, long ld, int elem) {
+      return ptr != nullptr && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0 &&
+             (ld * elem) % 16 == 0 && ld > 0;
+    };
+    auto row_map = [&](CUtensorMap* m, const void* base, long ld, int elem, int cols) {
+      return cached_map(m, base, static_cast<uint64_t>(cols), static_cast<uint64_t>(M),
+                        static_cast<uint64_t>(ld), 128 / elem, 32, elem) == 0;
+    };
+    const __nv_bfloat16* out_b = static_cast<const __nv_bfloat16*>(p.out);
+    const __nv_bfloat16* out2_b = static_cast<const __nv_bfloat16*>(p.out2);
+    const __nv_bfloat16* aux_b = static_cast<const __nv_bfloat16*>(p.aux);
+    switch (kind) {
+      case EPI_BF16:
+        staged = ok16(p.out, p.ldo, 2) && row_map(&em.m[0], p.out, p.ldo, 2, N);
+        break;
+      case EPI_ROPE:
+        staged = ok16(p.out, p.ldo, 2) && p.head_dim % 64 == 0 && p.rope_cols % 64 == 0 &&
+                 (reinterpret_cast<uintptr_t>(p.rope_cos) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(p.rope_sin) & 15) == 0 &&
+                 row_map(&em.m[0], p.out, p.ldo, 2, N);
+        break;
+      case EPI_F32:
+        staged = ok16(p.out, p.ldo, 4) && row_map(&em.m[0], p.out, p.ldo, 4, N);
+        break;
+      case EPI_RESID:
+        staged = ok16(p.out, p.ldo, 4) && ok16(p.aux, p.ldaux, 4) &&
+                 row_map(&em.m[0], p.out, p.ldo, 4, N) && row_map(&em.m[1], p.aux, p.ldaux, 4, N);
+        break;
+      case EPI_SWIGLU:
+        staged = ok16(p.out, p.ldo, 2) && ok16(p.out2, p.ldo2, 2) && N % 8 == 0 &&
+                 row_map(&em.m[0], p.out, p.ldo, 2, N) &&
+                 row_map(&em.m[1], out2_b, p.ldo2, 2, N) &&
+                 row_map(&em.m[2], out2_b + N, p.ldo2, 2, N);
+        break;
+      case EPI_SWIGLU_BWD:
+        staged = ok16(p.out, p.ldo, 2) && ok16(p.aux, p.ldaux, 2) && N % 8 == 0 &&
+                 row_map(&em.m[0], out_b, p.ldo, 2, N) && row_map(&em.m[1], out_b + N, p.ldo, 2, N) &&
+                 row_map(&em.m[2], aux_b, p.ldaux, 2, N) &&
+                 row_map(&em.m[3], aux_b + N, p.ldaux, 2, N);
+        break;
+      default:
+        break;
+    }
+  }
+  // SFL_GEMM_DIRECT_EPILOGUE=1 forces the direct path (for A/B measurements).
+  static const bool force_direct = [] {
+    const char* v = getenv("SFL_GEMM_DIRECT_EPILOGUE");
+    return v != nullptr && v[0] == '1';
+  }();
+  const EpiMaps* em_ptr = (staged && !force_direct) ? &em : nullptr;
 
   CUtensorMap tmA, tmB;
   int rc;
@@ -616,8 +1088,8 @@ extern "C" int sfl_gemm_bf16(const void* a, long lda, int a_mn, const void* b, l
 
 #define SFL_DISPATCH(EPI_)                                                                    \
   case EPI_:                                                                                  \
-    return bn == 256 ? launch_major<256, EPI_>(a_mn, b_mn, tmA, tmB, p, max_ctas, stream)     \
-                     : launch_major<128, EPI_>(a_mn, b_mn, tmA, tmB, p, max_ctas, stream);
+    return bn == 256 ? launch_major<256, EPI_>(a_mn, b_mn, tmA, tmB, em_ptr, p, max_ctas, stream) \
+                     : launch_major<128, EPI_>(a_mn, b_mn, tmA, tmB, em_ptr, p, max_ctas, stream);
   switch (kind) {
     SFL_DISPATCH(EPI_BF16)
     SFL_DISPATCH(EPI_F32)
@@ -625,7 +1097,7 @@ extern "C" int sfl_gemm_bf16(const void* a, long lda, int a_mn, const void* b, l
     SFL_DISPATCH(EPI_ROPE)
     SFL_DISPATCH(EPI_SWIGLU_BWD)
     case EPI_SWIGLU:
-      return launch_major<256, EPI_SWIGLU>(a_mn, b_mn, tmA, tmB, p, max_ctas, stream);
+      return launch_major<256, EPI_SWIGLU>(a_mn, b_mn, tmA, tmB, em_ptr, p, max_ctas, stream);
     default:
       return -2;
   }

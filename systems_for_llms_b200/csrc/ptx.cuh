@@ -128,6 +128,17 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void*
                : "memory");
 }
 
+// Element-wise add of a shared-memory tile into global memory (one atomic add per
+// element, performed at the L2); the element type comes from the tensor map.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* src, int x,
+                                                  int y) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::
+          "l"(reinterpret_cast<uint64_t>(map)),
+      "r"(smem_u32(src)), "r"(x), "r"(y)
+      : "memory");
+}
+
 __device__ __forceinline__ void tma_store_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }

@@ -22,8 +22,12 @@ void* tensormap_encode_fn() {
   return fn;
 }
 
-int make_tensormap_nd_b16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
-                          const uint64_t* strides_bytes, const uint32_t* box, int swizzle) {
+int make_tensormap_nd(CUtensorMap* out, const void* base, int elem_bytes, int rank,
+                      const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                      int swizzle) {
+  if (elem_bytes != 2 && elem_bytes != 4) return -2;
+  const CUtensorMapDataType dtype =
+      elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   auto encode = reinterpret_cast<EncodeFn>(tensormap_encode_fn());
   if (encode == nullptr) return -1;
   cuuint64_t gdim[5];
@@ -41,7 +45,7 @@ int make_tensormap_nd_b16(CUtensorMap* out, const void* base, int rank, const ui
   if (swizzle == 2) sw = CU_TENSOR_MAP_SWIZZLE_64B;
   if (swizzle == 3) sw = CU_TENSOR_MAP_SWIZZLE_128B;
   auto call = [&] {
-    return encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank),
+    return encode(out, dtype, static_cast<cuuint32_t>(rank),
                   const_cast<void*>(base), gdim, gstride, bdim, estride,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -56,6 +60,19 @@ int make_tensormap_nd_b16(CUtensorMap* out, const void* base, int rank, const ui
     r = call();
   }
   return static_cast<int>(r);
+}
+
+int make_tensormap_nd_b16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                          const uint64_t* strides_bytes, const uint32_t* box, int swizzle) {
+  return make_tensormap_nd(out, base, 2, rank, dims, strides_bytes, box, swizzle);
+}
+
+int make_tensormap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner,
+                      uint64_t outer, uint64_t ld_elems, uint32_t box_inner, uint32_t box_outer) {
+  uint64_t dims[2] = {inner, outer};
+  uint64_t strides[2] = {0, ld_elems * static_cast<uint64_t>(elem_bytes)};
+  uint32_t box[2] = {box_inner, box_outer};
+  return make_tensormap_nd(out, base, elem_bytes, 2, dims, strides, box, 3);
 }
 
 int make_tensormap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
