@@ -867,6 +867,222 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   }
 }
 
+
+// ------------------------------------------------- grouped weight gradients ----
+// The weight gradients of one transformer block are up to four products
+// dW_g[N_g, K_g] (+)= dY_g[T, N_g]^T X_g[T, K_g] with a long reduction (T tokens) and
+// small outputs: launched one by one, none of them has enough 128 x 256 tiles to
+// fill 148 SMs.  This kernel walks the tiles of all problems in one persistent
+// launch, so only the last round of the whole group is partially filled.  Operand
+// and output tensor maps are per problem; the pipeline is the one of gemm_kernel
+// with MN-major operands and the staged fp32 epilogue (store, or TMA reduce-add
+// when the gradient accumulates).
+constexpr int kMaxGroup = 4;
+constexpr int kGroupBN = 256;
+
+struct GroupedProblem {
+  int m_tiles, n_tiles;  // 128-row x 256-column tiles of the output
+  int num_kb;            // 64-deep steps of the reduction
+  int tile_begin;        // first global tile index of this problem
+  int cols;              // output columns (K_g)
+  int beta;
+};
+
+struct GroupedParams {
+  int count;
+  int total_tiles;
+  GroupedProblem prob[kMaxGroup];
+  int* status;
+};
+
+struct GroupedMaps {
+  CUtensorMap a[kMaxGroup];    // dY_g as MN-major A
+  CUtensorMap b[kMaxGroup];    // X_g as MN-major B
+  CUtensorMap out[kMaxGroup];  // fp32 gradient
+};
+
+__device__ __forceinline__ int grouped_find(const GroupedParams& p, int tile) {
+  int g = p.count - 1;
+  while (g > 0 && tile < p.prob[g].tile_begin) --g;
+  return g;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+wgrad_grouped_kernel(const __grid_constant__ GroupedMaps maps,
+                     const __grid_constant__ GroupedParams p) {
+  using Cfg = GemmConfig<kGroupBN, EPI_F32, true>;
+  constexpr int BN = kGroupBN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* epi_smem = smem + Cfg::kStages * Cfg::kStageBytes;
+  GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(epi_smem + Cfg::kEpiBytes);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->tmem_full[s], 1);
+      mbar_init(&bars->tmem_empty[s], 32 * kEpiWarps);
+    }
+    bars->abort = 0;
+    mbar_fence_init();
+    for (int g = 0; g < p.count; ++g) {
+      prefetch_tensormap(&maps.a[g]);
+      prefetch_tensormap(&maps.b[g]);
+      prefetch_tensormap(&maps.out[g]);
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+  volatile int* abort = &bars->abort;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+        const int g = grouped_find(p, tile);
+        const GroupedProblem& q = p.prob[g];
+        const int local = tile - q.tile_begin;
+        const int m0 = (local % q.m_tiles) * BM;
+        const int n0 = (local / q.m_tiles) * BN;
+        for (int kb = 0; kb < q.num_kb; ++kb) {
+          if (!wait_or_abort(&bars->empty[stage], phase ^ 1, abort)) {
+            report_status(p.status, kStatusTimeoutEmpty);
+            *abort = 1;
+            ok = false;
+            break;
+          }
+          uint8_t* sA = smem + stage * Cfg::kStageBytes;
+          uint8_t* sB = sA + kTileABytes;
+          mbar_expect_tx(&bars->full[stage], Cfg::kStageBytes);
+          const int k0 = kb * BK;
+#pragma unroll
+          for (int i = 0; i < BM / 64; ++i)
+            tma_load_2d(sA + i * (BK * 128), &maps.a[g], &bars->full[stage], m0 + i * 64, k0);
+#pragma unroll
+          for (int i = 0; i < BN / 64; ++i)
+            tma_load_2d(sB + i * (BK * 128), &maps.b[g], &bars->full[stage], n0 + i * 64, k0);
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, true, true);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+        const int num_kb = p.prob[grouped_find(p, tile)].num_kb;
+        if (!wait_or_abort(&bars->tmem_empty[acc], acc_phase ^ 1, abort)) {
+          report_status(p.status, kStatusTimeoutTmemEmpty);
+          *abort = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!wait_or_abort(&bars->full[stage], phase, abort)) {
+            report_status(p.status, kStatusTimeoutFull);
+            *abort = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint32_t b_addr = a_addr + kTileABytes;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t a_desc = umma_smem_desc(a_addr + k * 2048, BK * 128, 1024);
+            const uint64_t b_desc = umma_smem_desc(b_addr + k * 2048, BK * 128, 1024);
+            umma_bf16_ss(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0);
+          }
+          umma_commit(&bars->empty[stage]);
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&bars->tmem_full[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int part = (warp - 2) >> 2;
+    uint8_t* tile0 = epi_smem + (warp - 2) * Cfg::kEpiWarpBytes;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+      const int g = grouped_find(p, tile);
+      const GroupedProblem& q = p.prob[g];
+      const int local = tile - q.tile_begin;
+      const int m0 = (local % q.m_tiles) * BM;
+      const int n0 = (local / q.m_tiles) * BN;
+      int nchunks = (q.cols - n0 + 31) / 32;
+      if (nchunks > BN / 32) nchunks = BN / 32;
+      if (!wait_or_abort(&bars->tmem_full[acc], acc_phase, abort)) {
+        report_status(p.status, kStatusTimeoutTmemFull);
+        *abort = 1;
+        break;
+      }
+      tc_fence_after();
+      const int row0 = m0 + quarter * 32;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      for (int c = part; c < nchunks; c += 2) {
+        float v[32];
+        load_acc32(t_row + c * 32, v);
+        if (lane == 0) tma_store_wait_read<0>();
+        __syncwarp();
+        stage_f32(tile0, lane, v);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (q.beta) tma_reduce_add_2d(&maps.out[g], tile0, n0 + c * 32, row0);
+          else tma_store_2d(&maps.out[g], tile0, n0 + c * 32, row0);
+          tma_store_commit();
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&bars->tmem_empty[acc]);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+    if (lane == 0) tma_store_wait<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
 // ------------------------------------------------------------------ host ----
 namespace {
 
@@ -1102,4 +1318,54 @@ extern "C" int sfl_gemm_bf16(const void* a, long lda, int a_mn, const void* b, l
       return -2;
   }
 #undef SFL_DISPATCH
+}
+
+// Weight gradients of up to four linear layers in one launch; see the kernel.
+// Every matrix must be addressable by TMA (16-byte aligned base and pitch);
+// returns -2 otherwise so the caller can fall back to one product at a time.
+extern "C" int sfl_gemm_wgrad_grouped(const SflWgradProblem* problems, int count, int* status,
+                                      void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (problems == nullptr || count <= 0 || count > kMaxGroup) return -2;
+  GroupedMaps maps{};
+  GroupedParams p{};
+  p.count = count;
+  p.status = status;
+  int tiles = 0;
+  for (int g = 0; g < count; ++g) {
+    const SflWgradProblem& w = problems[g];
+    if (w.rows <= 0 || w.cols <= 0 || w.tokens <= 0) return -2;
+    auto aligned = [](const void* ptr, long ld, int elem) {
+      return ptr != nullptr && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && ld > 0 &&
+             (ld * elem) % 16 == 0;
+    };
+    if (!aligned(w.dy, w.ld_dy, 2) || !aligned(w.x, w.ld_x, 2) || !aligned(w.grad, w.ld_grad, 4))
+      return -2;
+    int rc = cached_map(&maps.a[g], w.dy, w.rows, w.tokens, w.ld_dy, 64, BK);
+    if (rc == 0) rc = cached_map(&maps.b[g], w.x, w.cols, w.tokens, w.ld_x, 64, BK);
+    if (rc == 0)
+      rc = cached_map(&maps.out[g], w.grad, w.cols, w.rows, w.ld_grad, 32, 32, 4);
+    if (rc) return 1000 + rc;
+    GroupedProblem& q = p.prob[g];
+    q.m_tiles = (w.rows + BM - 1) / BM;
+    q.n_tiles = (w.cols + kGroupBN - 1) / kGroupBN;
+    q.num_kb = (w.tokens + BK - 1) / BK;
+    q.tile_begin = tiles;
+    q.cols = w.cols;
+    q.beta = w.accumulate;
+    tiles += q.m_tiles * q.n_tiles;
+  }
+  p.total_tiles = tiles;
+  using Cfg = GemmConfig<kGroupBN, EPI_F32, true>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(wgrad_grouped_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  wgrad_grouped_kernel<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(maps, p);
+  return static_cast<int>(cudaGetLastError());
 }

@@ -54,6 +54,25 @@ int sfl_gemm_bf16(const void* a, long lda, int a_mn, const void* b, long ldb, in
                   int N, int K, const SflGemmEpilogue* epi, int bn_hint, int max_ctas,
                   void* stream);
 
+/* grad[rows, cols] (+)= dy[tokens, rows]^T x[tokens, cols]; bf16 operands, fp32 grad. */
+typedef struct SflWgradProblem {
+  const void* dy;
+  long ld_dy;
+  const void* x;
+  long ld_x;
+  float* grad;
+  long ld_grad;
+  int rows;
+  int cols;
+  int tokens;
+  int accumulate; /* 0: overwrite grad, 1: add to it */
+} SflWgradProblem;
+
+/* Up to four weight-gradient products in one persistent launch, so that their
+ * tiles share the SMs.  Returns -2 if a matrix breaks TMA's alignment rules
+ * (16-byte base and pitch): compute those with sfl_gemm_bf16 instead. */
+int sfl_gemm_wgrad_grouped(const SflWgradProblem* problems, int count, int* status, void* stream);
+
 /* --------------------------------------------------------------- RMSNorm -- */
 /* y = bf16(x * rsqrt(mean(x^2) + eps) * w), x fp32 [rows, dim]; rstd fp32 [rows]. */
 int sfl_rmsnorm_fwd(const float* x, const float* w, void* y_bf16, float* rstd, int rows, int dim,

@@ -301,22 +301,22 @@ def block_backward(engine: FusedEngine, index: int, saved, d_out: torch.Tensor, 
 
     # ---- feed-forward half
     d13 = G.swiglu_bwd(dres_bf16, engine.shadow(ffn.w2.weight), a13)
-    acc = engine.claim(ffn.w2.weight)
-    G.linear_wgrad(dres_bf16, g, engine.grad_view(ffn.w2.weight), acc)
+    # the four weight gradients of the block run as one grouped launch at the end
+    wgrads = [(dres_bf16, g, engine.grad_view(ffn.w2.weight), engine.claim(ffn.w2.weight))]
     if tp is None:
         dh2 = G.linear_dgrad(d13, engine.shadow(ffn.w1.weight, 2 * dff))
     else:   # column-parallel input gradient: partial over ranks, summed by one kernel
         dh2 = tp.reduce_bf16(G.linear_dgrad(d13, engine.shadow(ffn.w1.weight, 2 * dff),
                                             tp.partial(M, d)))
-    acc = engine.claim(ffn.w1.weight, ffn.w3.weight)
-    G.linear_wgrad(d13, h2, engine.grad_view(ffn.w1.weight, 2 * dff), acc)
+    wgrads.append((d13, h2, engine.grad_view(ffn.w1.weight, 2 * dff),
+                   engine.claim(ffn.w1.weight, ffn.w3.weight)))
     acc = engine.claim(layer.ffn_norm.weight)
     dres2, dres2_bf16 = K.rmsnorm_bwd(dh2, x_mid, layer.ffn_norm.weight, rstd2, dres,
                                       engine.grad_view(layer.ffn_norm.weight), acc, want_bf16=True)
     # ---- attention half
     d_attn = G.linear_dgrad(dres2_bf16, engine.shadow(attn_p.output_proj.weight))
-    acc = engine.claim(attn_p.output_proj.weight)
-    G.linear_wgrad(dres2_bf16, attn, engine.grad_view(attn_p.output_proj.weight), acc)
+    wgrads.append((dres2_bf16, attn, engine.grad_view(attn_p.output_proj.weight),
+                   engine.claim(attn_p.output_proj.weight)))
     dqkv = torch.empty_like(qkv)
     heads = qkv.view(B, T, 3, H, dk)
     dheads = dqkv.view(B, T, 3, H, dk)
@@ -331,8 +331,9 @@ def block_backward(engine: FusedEngine, index: int, saved, d_out: torch.Tensor, 
     else:
         dh1 = tp.reduce_bf16(G.linear_dgrad(dqkv, engine.shadow(attn_p.q_proj.weight, 3 * aw),
                                             tp.partial(M, d)))
-    acc = engine.claim(attn_p.q_proj.weight, attn_p.k_proj.weight, attn_p.v_proj.weight)
-    G.linear_wgrad(dqkv, h1, engine.grad_view(attn_p.q_proj.weight, 3 * aw), acc)
+    wgrads.append((dqkv, h1, engine.grad_view(attn_p.q_proj.weight, 3 * aw),
+                   engine.claim(attn_p.q_proj.weight, attn_p.k_proj.weight, attn_p.v_proj.weight)))
+    G.wgrad_grouped(wgrads)
     acc = engine.claim(layer.attn_norm.weight)
     dx, dx_bf16 = K.rmsnorm_bwd(dh1, x2, layer.attn_norm.weight, rstd1, dres2,
                                 engine.grad_view(layer.attn_norm.weight), acc, want_bf16=True)

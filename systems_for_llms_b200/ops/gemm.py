@@ -18,7 +18,7 @@ import torch
 
 from . import lib as _lib
 from .lib import (EPI_BF16, EPI_F32, EPI_RESID, EPI_ROPE, EPI_SWIGLU, EPI_SWIGLU_BWD,
-                  GemmEpilogue)
+                  GemmEpilogue, WgradProblem)
 
 _status_words: dict[torch.device, torch.Tensor] = {}
 
@@ -150,3 +150,49 @@ def linear_wgrad(dy: torch.Tensor, x: torch.Tensor, grad: torch.Tensor, accumula
         raise ValueError("weight gradients are fp32 and row-contiguous")
     epi = GemmEpilogue(kind=EPI_F32, beta=int(accumulate), out=grad.data_ptr(), ldo=grad.stride(0))
     gemm(dy, x, N, K, M, epi, a_mn=True, b_mn=True)
+
+
+MAX_WGRAD_GROUP = 4
+
+
+def _groupable(dy: torch.Tensor, x: torch.Tensor, grad: torch.Tensor) -> bool:
+    return (dy.stride(0) % 8 == 0 and x.stride(0) % 8 == 0 and grad.stride(0) % 4 == 0
+            and dy.data_ptr() % 16 == 0 and x.data_ptr() % 16 == 0 and grad.data_ptr() % 16 == 0)
+
+
+def wgrad_grouped(problems) -> None:
+    """``grad (+)= dy^T @ x`` for several layers in one persistent launch.
+
+    ``problems`` is a list of ``(dy, x, grad, accumulate)``.  One weight-gradient
+    product has too few output tiles to occupy every SM; walking the tiles of a
+    whole transformer block's four products in one kernel leaves only the last
+    round of the group partially filled.  Products that cannot be addressed by
+    TMA fall back to ``linear_wgrad`` one at a time.
+    """
+    group = []
+    for dy, x, grad, accumulate in problems:
+        if grad.dtype != torch.float32 or grad.stride(1) != 1:
+            raise ValueError("weight gradients are fp32 and row-contiguous")
+        if dy.shape[0] != x.shape[0] or grad.shape != (dy.shape[1], x.shape[1]):
+            raise ValueError("wgrad shapes: dy[T,N], x[T,K], grad[N,K]")
+        if _groupable(dy, x, grad):
+            _operand(dy), _operand(x)
+            group.append((dy, x, grad, accumulate))
+        else:
+            linear_wgrad(dy, x, grad, accumulate)
+    for start in range(0, len(group), MAX_WGRAD_GROUP):
+        chunk = group[start:start + MAX_WGRAD_GROUP]
+        if len(chunk) == 1:
+            linear_wgrad(*chunk[0])
+            continue
+        array = (WgradProblem * len(chunk))()
+        for slot, (dy, x, grad, accumulate) in zip(array, chunk):
+            slot.dy, slot.ld_dy = dy.data_ptr(), dy.stride(0)
+            slot.x, slot.ld_x = x.data_ptr(), x.stride(0)
+            slot.grad, slot.ld_grad = grad.data_ptr(), grad.stride(0)
+            slot.rows, slot.cols, slot.tokens = dy.shape[1], x.shape[1], dy.shape[0]
+            slot.accumulate = int(bool(accumulate))
+        code = _lib.lib().sfl_gemm_wgrad_grouped(array, len(chunk),
+                                                 status_word(chunk[0][0].device).data_ptr(),
+                                                 _lib.stream_ptr())
+        _lib.check(code, "sfl_gemm_wgrad_grouped")

@@ -32,12 +32,23 @@ class GemmEpilogue(Structure):
     ]
 
 
+class WgradProblem(Structure):
+    """Mirror of ``SflWgradProblem`` in csrc/sfl.h."""
+
+    _fields_ = [
+        ("dy", c_void_p), ("ld_dy", c_long), ("x", c_void_p), ("ld_x", c_long),
+        ("grad", c_void_p), ("ld_grad", c_long),
+        ("rows", c_int), ("cols", c_int), ("tokens", c_int), ("accumulate", c_int),
+    ]
+
+
 EPI_BF16, EPI_F32, EPI_RESID, EPI_ROPE, EPI_SWIGLU, EPI_SWIGLU_BWD = range(6)
 
 _P = c_void_p
 _SIGNATURES = {
     "sfl_gemm_bf16": [_P, c_long, c_int, _P, c_long, c_int, c_int, c_int, c_int,
                       POINTER(GemmEpilogue), c_int, c_int, _P],
+    "sfl_gemm_wgrad_grouped": [POINTER(WgradProblem), c_int, _P, _P],
     "sfl_rmsnorm_fwd": [_P, _P, _P, _P, c_int, c_int, c_float, _P],
     "sfl_rmsnorm_bwd_blocks": [c_int],
     "sfl_rmsnorm_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, _P],

@@ -59,6 +59,40 @@ def test_gemm_dgrad_and_wgrad(dev, M, N, K):
     assert rel(grad, expect) < 1e-4
 
 
+def test_wgrad_grouped_matches_separate_products(dev):
+    from systems_for_llms_b200.ops import gemm as G
+    shapes = [(1024, 3072, 1024), (1024, 1024, 1024), (1024, 704, 520), (300, 200, 136)]
+    problems, expected = [], []
+    for index, (tokens, rows, cols) in enumerate(shapes):
+        dy, x = rnd(dev, tokens, rows, seed=10 + index), rnd(dev, tokens, cols, seed=20 + index)
+        grad = torch.randn(rows, cols, device=dev)
+        accumulate = index % 2 == 0
+        product = dy.float().t() @ x.float()
+        expected.append(grad.clone() + product if accumulate else product)
+        problems.append((dy, x, grad, accumulate))
+    G.wgrad_grouped(problems)
+    check(dev)
+    for (_, _, grad, _), want in zip(problems, expected):
+        assert rel(grad, want) < 1e-4
+    # a product TMA cannot address (odd pitch) is computed on its own
+    dy, x = rnd(dev, 64, 24, seed=1), rnd(dev, 64, 40, seed=2)
+    odd = torch.zeros(24, 41, device=dev)[:, :40]
+    G.wgrad_grouped([(dy, x, odd, False), problems[1]])
+    check(dev)
+    assert rel(odd, dy.float().t() @ x.float()) < 1e-4
+    # two launches of the same group are bit-identical (no atomics across tiles)
+    first = [g.clone() for _, _, g, _ in problems]
+    for (_, _, grad, _), start in zip(problems, first):
+        grad.copy_(start)
+    G.wgrad_grouped([(dy_, x_, g_, True) for dy_, x_, g_, _ in problems])
+    once = [g.clone() for _, _, g, _ in problems]
+    for (_, _, grad, _), start in zip(problems, first):
+        grad.copy_(start)
+    G.wgrad_grouped([(dy_, x_, g_, True) for dy_, x_, g_, _ in problems])
+    check(dev)
+    assert all(torch.equal(a, g) for a, (_, _, g, _) in zip(once, problems))
+
+
 def test_gemm_epilogues(dev):
     from systems_for_llms_b200.ops import gemm as G
     M, K, F = 512, 256, 344
