@@ -43,7 +43,7 @@ _lib.register_signature("sfl_attn_fwd", [_A, _A, _A, _A, c_void_p, c_int, c_int,
                                          c_float, POINTER(AttnMask), c_int, c_void_p, c_void_p])
 _lib.register_signature("sfl_attn_bwd", [_A, _A, _A, _A, _A, c_void_p, c_void_p, _A, _A, _A,
                                          c_int, c_int, c_int, c_int, c_float, POINTER(AttnMask),
-                                         c_int, c_void_p, c_void_p])
+                                         c_int, c_void_p, c_void_p, c_void_p, c_void_p])
 _lib.register_signature("sfl_rope_bwd", [c_void_p, c_long, c_void_p, c_void_p, c_long, c_int,
                                          c_int, c_int, c_void_p])
 
@@ -175,9 +175,23 @@ def flash_fwd(q, k, v, out, lse, mask: DeviceMask, scale: float) -> None:
     _lib.check(code, "sfl_attn_fwd")
 
 
-def flash_bwd(q, k, v, out, d_out, lse, dq, dk, dv, mask: DeviceMask, scale: float) -> None:
-    """Launch delta + dQ + dK/dV kernels.  All tensors are [B, H, N, D] views."""
+def flash_bwd(q, k, v, out, d_out, lse, dq, dk, dv, mask: DeviceMask, scale: float,
+              rope: tuple[torch.Tensor, torch.Tensor] | None = None) -> None:
+    """Launch the dQ kernel (which also computes delta) and the dK/dV kernel.
+
+    All tensors are [B, H, N, D] views.  ``rope = (cos, sin)``, fp32 ``[>=N, D/2]``
+    tables of the interleaved-pair rotary embedding that produced q and k, makes
+    the kernels return dq and dk as gradients of the un-rotated projections.
+    """
     B, H, N, D = q.shape
+    cos_ptr = sin_ptr = None
+    if rope is not None:
+        cos, sin = rope
+        for table in (cos, sin):
+            if (table.dtype != torch.float32 or table.dim() != 2 or table.shape[0] < N
+                    or table.shape[1] != D // 2 or not table.is_contiguous()):
+                raise ValueError("rotary tables are contiguous fp32 [>=N, D/2]")
+        cos_ptr, sin_ptr = cos.data_ptr(), sin.data_ptr()
     fp16 = int(q.dtype == torch.float16)
     delta = torch.empty(B, H, N, dtype=torch.float32, device=q.device)
     status = status_word(q.device)
@@ -185,7 +199,8 @@ def flash_bwd(q, k, v, out, d_out, lse, dq, dk, dv, mask: DeviceMask, scale: flo
         ctypes.byref(_view(q)), ctypes.byref(_view(k)), ctypes.byref(_view(v)),
         ctypes.byref(_view(out)), ctypes.byref(_view(d_out)), lse.data_ptr(), delta.data_ptr(),
         ctypes.byref(_view(dq)), ctypes.byref(_view(dk)), ctypes.byref(_view(dv)), B, H, N, D,
-        float(scale), ctypes.byref(mask.struct), fp16, status.data_ptr(), _lib.stream_ptr())
+        float(scale), ctypes.byref(mask.struct), fp16, status.data_ptr(), cos_ptr, sin_ptr,
+        _lib.stream_ptr())
     _lib.check(code, "sfl_attn_bwd")
 
 

@@ -56,6 +56,7 @@ struct AttnParams {
   AttnSchedule sched;
   // forward outputs / backward inputs
   void* o;
+  const void* d_o;        // backward: upstream gradient, laid out like O
   long o_sb, o_sh, o_st;  // element strides of O (and dO) for batch, head, token
   float* lse;             // [B,H,N]
   float* delta;           // [B,H,N]
@@ -64,6 +65,10 @@ struct AttnParams {
   void* dk;
   void* dv;
   long g_sb, g_sh, g_st;
+  // Optional: dQ and dK leave the kernel already multiplied by the transposed
+  // rotary matrix of their position (tables are [N, D/2], interleaved pairs).
+  const float* rope_cos;
+  const float* rope_sin;
   int is_fp16;
   int* status;
 };
@@ -76,6 +81,14 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&h);
   } else {
     return pack_bf16(a, b);
+  }
+}
+template <bool FP16>
+__device__ __forceinline__ float2 unpack2(uint32_t v) {
+  if constexpr (FP16) {
+    return __half22float2(*reinterpret_cast<__half2*>(&v));
+  } else {
+    return unpack_bf16(v);
   }
 }
 template <bool FP16>
@@ -557,26 +570,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
-// ================================================================ delta ====
-// delta[b,h,t] = sum_d O * dO  (fp32); one warp per row.
-template <bool FP16>
-__global__ void attn_delta_kernel(const void* __restrict__ o, const void* __restrict__ d_o,
-                                  float* __restrict__ delta, int B, int H, int N, int D, long sb,
-                                  long sh, long st) {
-  const int lane = threadIdx.x & 31;
-  const long rowid = static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (rowid >= static_cast<long>(B) * H * N) return;
-  const int t = rowid % N;
-  const int h = (rowid / N) % H;
-  const int b = rowid / (static_cast<long>(N) * H);
-  const long base = b * sb + h * sh + static_cast<long>(t) * st;
-  float s = 0.f;
-  for (int i = lane; i < D; i += 32) s += load_elem<FP16>(o, base + i) * load_elem<FP16>(d_o, base + i);
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-  if (lane == 0) delta[rowid] = s;
-}
-
 // ============================================================= backward ====
 // Shared layout of the two backward kernels: an "owned" pair of resident tiles,
 // a ring of streamed tile pairs, and two [128 x 128] tiles written by the compute
@@ -734,8 +727,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
     if constexpr (!KV_OWNED) {
       // lse in log2 units; +inf for padding rows makes P vanish.
       my_lse = own_pos < p.N ? p.lse[stat_base + own_pos] * kLog2e : INFINITY;
-      my_delta = own_pos < p.N ? p.delta[stat_base + own_pos] : 0.f;
       if (my_lse == -INFINITY) my_lse = INFINITY;  // row without keys: P = 0
+      // delta = sum_d O * dO of this query row; published for the key-owned kernel,
+      // which runs after this one.
+      if (own_pos < p.N) {
+        const long off = 2 * (b * p.o_sb + h * p.o_sh + static_cast<long>(own_pos) * p.o_st);
+        const uint4* po = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.o) + off);
+        const uint4* pg = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.d_o) + off);
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+          const uint4 a = po[i], g = pg[i];
+          const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+          const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 x = unpack2<FP16>(aw[e]);
+            const float2 y = unpack2<FP16>(gw[e]);
+            my_delta = fmaf(x.x, y.x, my_delta);
+            my_delta = fmaf(x.y, y.y, my_delta);
+          }
+        }
+        p.delta[stat_base + own_pos] = my_delta;
+      }
     }
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
@@ -836,7 +849,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
     if (ok) {
       tc_fence_after();
       const long goff = 2 * (b * p.g_sb + h * p.g_sh + static_cast<long>(own_pos) * p.g_st);
-      auto write_acc = [&](uint32_t taddr, void* dst_base, float mul) {
+      auto write_acc = [&](uint32_t taddr, void* dst_base, float mul, bool rotate) {
         uint8_t* dst = static_cast<uint8_t*>(dst_base) + goff;
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
@@ -848,24 +861,48 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
 #pragma unroll
             for (int i = 0; i < 32; ++i) a[i] = 0.f;
           }
+          float out_mul = mul;
+          if (rotate && own_pos < p.N) {
+            // gradient of the rotary embedding: rotate each (even, odd) pair back by
+            // its angle, starting from the value rounded to the storage type
+            const long tab = static_cast<long>(own_pos) * (D / 2) + c * 16;
+            const float4* cs = reinterpret_cast<const float4*>(p.rope_cos + tab);
+            const float4* sn = reinterpret_cast<const float4*>(p.rope_sin + tab);
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              const float4 c4 = cs[q4], s4 = sn[q4];
+              const float cc[4] = {c4.x, c4.y, c4.z, c4.w};
+              const float ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int i = 8 * q4 + 2 * e;
+                const float ge = round_elem<FP16>(a[i] * mul);
+                const float go = round_elem<FP16>(a[i + 1] * mul);
+                a[i] = ge * cc[e] + go * ss[e];
+                a[i + 1] = go * cc[e] - ge * ss[e];
+              }
+            }
+            out_mul = 1.0f;
+          }
           if (own_pos < p.N) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               uint4 v;
-              v.x = pack2<FP16>(a[8 * i + 0] * mul, a[8 * i + 1] * mul);
-              v.y = pack2<FP16>(a[8 * i + 2] * mul, a[8 * i + 3] * mul);
-              v.z = pack2<FP16>(a[8 * i + 4] * mul, a[8 * i + 5] * mul);
-              v.w = pack2<FP16>(a[8 * i + 6] * mul, a[8 * i + 7] * mul);
+              v.x = pack2<FP16>(a[8 * i + 0] * out_mul, a[8 * i + 1] * out_mul);
+              v.y = pack2<FP16>(a[8 * i + 2] * out_mul, a[8 * i + 3] * out_mul);
+              v.z = pack2<FP16>(a[8 * i + 4] * out_mul, a[8 * i + 5] * out_mul);
+              v.w = pack2<FP16>(a[8 * i + 6] * out_mul, a[8 * i + 7] * out_mul);
               *reinterpret_cast<uint4*>(dst + (c * 32 + i * 8) * 2) = v;
             }
           }
         }
       };
+      const bool rotate = p.rope_cos != nullptr;
       if constexpr (KV_OWNED) {
-        write_acc(tAcc0, p.dv, 1.0f);
-        write_acc(tAcc1, p.dk, p.scale);
+        write_acc(tAcc0, p.dv, 1.0f, false);
+        write_acc(tAcc1, p.dk, p.scale, rotate);
       } else {
-        write_acc(tAcc0, p.dq, p.scale);
+        write_acc(tAcc0, p.dq, p.scale, rotate);
       }
     }
   }
@@ -976,7 +1013,8 @@ extern "C" int sfl_attn_bwd(const SflAttnTensor* q, const SflAttnTensor* k, cons
                             const SflAttnTensor* o, const SflAttnTensor* d_o, const float* lse,
                             float* delta, const SflAttnTensor* dq, const SflAttnTensor* dk,
                             const SflAttnTensor* dv, int B, int H, int N, int D, float scale,
-                            const SflAttnMask* mask, int is_fp16, int* status, void* stream_) {
+                            const SflAttnMask* mask, int is_fp16, int* status,
+                            const float* rope_cos, const float* rope_sin, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if ((D != 64 && D != 128) || B <= 0 || H <= 0 || N <= 0 || mask == nullptr) return -2;
   for (const SflAttnTensor* t : {q, k, v, o, d_o, dq, dk, dv})
@@ -988,6 +1026,10 @@ extern "C" int sfl_attn_bwd(const SflAttnTensor* q, const SflAttnTensor* k, cons
       dq->stride_h != dv->stride_h || dq->stride_t != dk->stride_t || dq->stride_t != dv->stride_t)
     return -2;
   if (mask->mode == 0 && (mask->t_row_ptr == nullptr || mask->t_col_idx == nullptr)) return -2;
+  if ((rope_cos == nullptr) != (rope_sin == nullptr)) return -2;
+  if (rope_cos != nullptr && ((reinterpret_cast<uintptr_t>(rope_cos) & 15) ||
+                              (reinterpret_cast<uintptr_t>(rope_sin) & 15)))
+    return -2;
   CUtensorMap tq, tk, tv, tdo;
   {
     // -3000 - 100 * operand - driver code tells which map was refused and why
@@ -998,20 +1040,12 @@ extern "C" int sfl_attn_bwd(const SflAttnTensor* q, const SflAttnTensor* k, cons
       if (rc) return -3000 - 100 * i - (rc > 0 && rc < 100 ? rc : 99);
     }
   }
-  {
-    const long rows = static_cast<long>(B) * H * N;
-    const int warps = 8;
-    const unsigned blocks = static_cast<unsigned>((rows + warps - 1) / warps);
-    if (is_fp16)
-      attn_delta_kernel<true><<<blocks, warps * 32, 0, stream>>>(
-          o->ptr, d_o->ptr, delta, B, H, N, D, o->stride_b, o->stride_h, o->stride_t);
-    else
-      attn_delta_kernel<false><<<blocks, warps * 32, 0, stream>>>(
-          o->ptr, d_o->ptr, delta, B, H, N, D, o->stride_b, o->stride_h, o->stride_t);
-  }
   AttnParams p{};
   p.B = B; p.H = H; p.N = N; p.scale = scale;
   p.lse = const_cast<float*>(lse); p.delta = delta;
+  p.o = o->ptr; p.d_o = d_o->ptr;
+  p.o_sb = o->stride_b; p.o_sh = o->stride_h; p.o_st = o->stride_t;
+  p.rope_cos = rope_cos; p.rope_sin = rope_sin;
   p.dq = dq->ptr; p.dk = dk->ptr; p.dv = dv->ptr;
   p.g_sb = dq->stride_b; p.g_sh = dq->stride_h; p.g_st = dq->stride_t;
   p.is_fp16 = is_fp16; p.status = status;

@@ -143,12 +143,16 @@ typedef struct SflAttnMask {
 int sfl_attn_fwd(const SflAttnTensor* q, const SflAttnTensor* k, const SflAttnTensor* v,
                  const SflAttnTensor* o, float* lse, int B, int H, int N, int D, float scale,
                  const SflAttnMask* mask, int is_fp16, int* status, void* stream);
-/* Gradients of the above.  delta is fp32 [B,H,N] scratch owned by the caller. */
+/* Gradients of the above.  delta is fp32 [B,H,N] scratch owned by the caller (the
+ * query-owned kernel fills it, the key-owned kernel reads it).  With rope_cos and
+ * rope_sin (fp32 [N, D/2], 16-byte aligned; both or neither) dq and dk are written
+ * already multiplied by the transposed rotary matrix of their token position, i.e.
+ * as gradients of the un-rotated projections. */
 int sfl_attn_bwd(const SflAttnTensor* q, const SflAttnTensor* k, const SflAttnTensor* v,
                  const SflAttnTensor* o, const SflAttnTensor* d_o, const float* lse, float* delta,
                  const SflAttnTensor* dq, const SflAttnTensor* dk, const SflAttnTensor* dv, int B,
                  int H, int N, int D, float scale, const SflAttnMask* mask, int is_fp16,
-                 int* status, void* stream);
+                 int* status, const float* rope_cos, const float* rope_sin, void* stream);
 /* In-place inverse rotary embedding on the first `cols` columns of bf16 x[rows, ld]. */
 int sfl_rope_bwd(void* x_bf16, long ld, const float* cos, const float* sin, long rows, int cols,
                  int T, int head_dim, void* stream);

@@ -324,8 +324,8 @@ def block_backward(engine: FusedEngine, index: int, saved, d_out: torch.Tensor, 
     dq, dkk, dv = (dheads[:, :, i].permute(0, 2, 1, 3) for i in range(3))
     as_heads = lambda t: t.view(B, T, H, dk).permute(0, 2, 1, 3)
     mask = flash.causal_mask(d_out.device, T)
-    flash.flash_bwd(q, k, v, as_heads(attn), as_heads(d_attn), lse, dq, dkk, dv, mask, dk ** -0.5)
-    flash.rope_bwd_(dqkv, engine.cos, engine.sin, T, 2 * aw, dk)
+    flash.flash_bwd(q, k, v, as_heads(attn), as_heads(d_attn), lse, dq, dkk, dv, mask, dk ** -0.5,
+                    rope=(engine.cos, engine.sin))   # dq, dk come back un-rotated
     if tp is None:
         dh1 = G.linear_dgrad(dqkv, engine.shadow(attn_p.q_proj.weight, 3 * aw))
     else:

@@ -73,7 +73,7 @@ def register_signature(name: str, argtypes: list) -> None:
 
 
 # Kernels launched per call of each entry point (default 1, 0 for host-only calls).
-_KERNELS_PER_CALL = {"sfl_attn_bwd": 3, "sfl_rmsnorm_bwd_blocks": 0, "sfl_sqnorm_blocks": 0,
+_KERNELS_PER_CALL = {"sfl_attn_bwd": 2, "sfl_rmsnorm_bwd_blocks": 0, "sfl_sqnorm_blocks": 0,
                      "sfl_ipc_alloc": 0, "sfl_ipc_free": 0, "sfl_ipc_get_handle": 0,
                      "sfl_ipc_open_handle": 0, "sfl_ipc_close_handle": 0,
                      "sfl_comm_set_spin_limit": 0, "sfl_comm_flag_bytes": 0, "sfl_comm_slots": 0,

@@ -149,3 +149,38 @@ def test_backward_as_first_cuda_work_of_the_autograd_thread(dev):
     done = subprocess.run([sys.executable, "-c", script], cwd=Path(__file__).resolve().parents[1],
                           capture_output=True, text=True, timeout=300)
     assert done.returncode == 0, done.stdout + done.stderr
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_backward_with_fused_rotary_gradient(dev, dtype):
+    """dq/dk returned with ``rope=`` equal the plain gradients rotated back afterwards."""
+    from systems_for_llms_b200.attention import flash
+    from systems_for_llms_b200.ops.gemm import check_status
+    B, H, N, D = 2, 3, 300, 64
+    generator = torch.Generator(device=dev).manual_seed(3)
+    q, k, v, upstream = (torch.randn(B, H, N, D, device=dev, generator=generator).to(dtype)
+                         for _ in range(4))
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device=dev).float() / D))
+    angles = torch.arange(N + 20, device=dev).float()[:, None] * inv[None]
+    cos, sin = (f(angles).bfloat16().float().contiguous() for f in (torch.cos, torch.sin))
+    mask = flash.causal_mask(dev, N)
+    out = torch.empty_like(q)
+    lse = torch.empty(B, H, N, dtype=torch.float32, device=dev)
+    flash.flash_fwd(q, k, v, out, lse, mask, D ** -0.5)
+    plain = [torch.empty_like(q) for _ in range(3)]
+    fused = [torch.empty_like(q) for _ in range(3)]
+    flash.flash_bwd(q, k, v, out, upstream, lse, *plain, mask, D ** -0.5)
+    flash.flash_bwd(q, k, v, out, upstream, lse, *fused, mask, D ** -0.5, rope=(cos, sin))
+    torch.cuda.synchronize()
+    check_status()
+    assert torch.equal(plain[2], fused[2])                 # dv is not rotated
+    c, s = cos[:N][None, None], sin[:N][None, None]
+    for got, base in zip(fused[:2], plain[:2]):
+        even, odd = base[..., 0::2].float(), base[..., 1::2].float()
+        want = torch.empty_like(base, dtype=torch.float32)
+        want[..., 0::2] = even * c + odd * s
+        want[..., 1::2] = odd * c - even * s
+        torch.testing.assert_close(got.float(), want.to(dtype).float(), atol=2e-2, rtol=2e-2)
+    with pytest.raises(ValueError):
+        flash.flash_bwd(q, k, v, out, upstream, lse, *fused, mask, D ** -0.5,
+                        rope=(cos[: N - 1], sin[: N - 1]))
