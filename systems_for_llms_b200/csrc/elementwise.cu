@@ -122,8 +122,15 @@ rmsnorm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const float* __rest
   for (int row = blockIdx.x * warps + warp; row < rows; row += gridDim.x * warps) {
     const long off = static_cast<long>(row) * dim;
     const float inv = rstd[row];
-    float4 xh[NCH], g[NCH];
+    float4 xh[NCH], g[NCH], res[NCH];
     float dot = 0.f;
+    // every load of the row is issued before the first use, so one round trip to
+    // memory covers x, dy and the incoming residual gradient
+#pragma unroll
+    for (int c = 0; c < NCH; ++c)
+      res[c] = dres_in != nullptr
+                   ? *reinterpret_cast<const float4*>(dres_in + off + c * 128 + lane * 4)
+                   : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
       const int col = c * 128 + lane * 4;
@@ -144,10 +151,7 @@ rmsnorm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const float* __rest
       d.y = inv * (g[c].y * wv[c].y - xh[c].y * dot);
       d.z = inv * (g[c].z * wv[c].z - xh[c].z * dot);
       d.w = inv * (g[c].w * wv[c].w - xh[c].w * dot);
-      if (dres_in != nullptr) {
-        const float4 r = *reinterpret_cast<const float4*>(dres_in + off + col);
-        d.x += r.x; d.y += r.y; d.z += r.z; d.w += r.w;
-      }
+      d.x += res[c].x; d.y += res[c].y; d.z += res[c].z; d.w += res[c].w;
       *reinterpret_cast<float4*>(dx_out + off + col) = d;
       if (dx_bf16 != nullptr) {
         uint2 o;
@@ -212,13 +216,35 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const float* __restrict
   }
 }
 
-__global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, int blocks,
-                                         float* __restrict__ dw, int dim, int accumulate) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= dim) return;
-  float s = 0.f;
-  for (int b = 0; b < blocks; ++b) s += partial[static_cast<long>(b) * dim + i];
-  dw[i] = accumulate ? dw[i] + s : s;
+// Each CTA folds 32 columns over all partial rows: eight warps take every eighth
+// row (independent loads in flight), then one warp adds the eight sums in a
+// fixed order, so the result does not depend on scheduling.
+constexpr int kDwReduceWarps = 8;
+__global__ void __launch_bounds__(32 * kDwReduceWarps)
+rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, int blocks, float* __restrict__ dw,
+                         int dim, int accumulate) {
+  __shared__ float part[kDwReduceWarps][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int i = blockIdx.x * 32 + lane;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  if (i < dim) {
+    int b = warp;
+    for (; b + 3 * kDwReduceWarps < blocks; b += 4 * kDwReduceWarps) {
+      s0 += partial[static_cast<long>(b) * dim + i];
+      s1 += partial[static_cast<long>(b + kDwReduceWarps) * dim + i];
+      s2 += partial[static_cast<long>(b + 2 * kDwReduceWarps) * dim + i];
+      s3 += partial[static_cast<long>(b + 3 * kDwReduceWarps) * dim + i];
+    }
+    for (; b < blocks; b += kDwReduceWarps) s0 += partial[static_cast<long>(b) * dim + i];
+  }
+  part[warp][lane] = (s0 + s1) + (s2 + s3);
+  __syncthreads();
+  if (warp == 0 && i < dim) {
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < kDwReduceWarps; ++k) s += part[k][lane];
+    dw[i] = accumulate ? dw[i] + s : s;
+  }
 }
 
 // ---------------------------------------------------------- cross entropy ---
@@ -438,8 +464,8 @@ extern "C" int sfl_rmsnorm_bwd(const void* dy, const float* x, const float* w, c
 
 extern "C" int sfl_rmsnorm_dw_reduce(const float* partial, int blocks, float* dw, int dim,
                                      int accumulate, void* stream) {
-  rmsnorm_dw_reduce_kernel<<<(dim + 127) / 128, 128, 0, SFL_STREAM(stream)>>>(partial, blocks, dw,
-                                                                             dim, accumulate);
+  rmsnorm_dw_reduce_kernel<<<(dim + 31) / 32, 32 * kDwReduceWarps, 0, SFL_STREAM(stream)>>>(
+      partial, blocks, dw, dim, accumulate);
   SFL_RET();
 }
 
