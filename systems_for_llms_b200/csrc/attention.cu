@@ -34,7 +34,8 @@
 namespace sfl {
 
 constexpr int kTile = 128;          // rows and columns of a score tile
-constexpr int kAttnThreads = 192;   // producer warp, MMA warp, 4 compute warps
+constexpr int kAttnThreads = 192;   // forward: producer warp, MMA warp, 4 softmax warps
+constexpr int kBwdThreads = 320;    // backward: producer, MMA, 8 compute warps (2 per TMEM lane quarter)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -266,6 +267,9 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t base, int k) {
 
 __device__ __forceinline__ void named_barrier_128() {
   asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+__device__ __forceinline__ void named_barrier_bwd() {  // the backward kernel's compute warps
+  asm volatile("bar.sync 1, %0;" ::"n"(kBwdThreads - 64) : "memory");
 }
 
 __device__ __forceinline__ void tmem_ld_32x32f(uint32_t taddr, float* dst) {
@@ -586,9 +590,10 @@ struct BwdSmem {
 struct BwdBarriers {
   uint64_t own_full;
   uint64_t in_full[2], in_empty[2];
-  uint64_t sp_full;    // score and dP accumulators ready
-  uint64_t pds_ready;  // P and dS tiles written (128 arrivals)
-  uint64_t acc_done;   // accumulation MMAs of the tile finished
+  // Each streamed tile is processed as two halves of 64 columns; index = half.
+  uint64_t sp_full[2];    // score and dP accumulator halves ready
+  uint64_t pds_ready[2];  // P and dS half tiles written (128 arrivals)
+  uint64_t acc_done[2];   // accumulation MMAs of the half finished
   uint32_t tmem_base;
   int abort;
 };
@@ -600,7 +605,7 @@ struct BwdBarriers {
 //   S = Q K^T, dP = dO V^T, P = exp(S - lse_q), dS = P (dP - delta_q)
 //   dQ += dS K
 template <int D, bool FP16, bool KV_OWNED>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or Q
                 const __grid_constant__ CUtensorMap tmOwnB,  // V (kv-owned) or dO
                 const __grid_constant__ CUtensorMap tmInA,   // Q (kv-owned) or K
@@ -634,9 +639,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
       mbar_init(&bars->in_full[s], 1);
       mbar_init(&bars->in_empty[s], 1);
     }
-    mbar_init(&bars->sp_full, 1);
-    mbar_init(&bars->pds_ready, 128);
-    mbar_init(&bars->acc_done, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->sp_full[s], 1);
+      mbar_init(&bars->pds_ready[s], kBwdThreads - 64);
+      mbar_init(&bars->acc_done[s], 1);
+    }
     bars->abort = 0;
     mbar_fence_init();
   }
@@ -673,51 +680,78 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
     }
   } else if (warp == 1) {
     if (lane == 0 && n_tiles > 0) {
-      constexpr uint32_t idesc_s = idesc_16bit(FP16, kTile, kTile, false, false);
+      // The streamed tile is handled as two halves of 64 columns so that the tensor
+      // pipe works on the scores of half h+1 and the accumulation of half h-1 while
+      // the compute warps turn half h into probabilities: TMEM columns and the
+      // shared P / dS tiles are already stored as two 64-column halves.
+      constexpr uint32_t idesc_s = idesc_16bit(FP16, kTile, 64, false, false);
       constexpr uint32_t idesc_acc = idesc_16bit(FP16, kTile, D, false, true);
       const uint32_t ownA = smem_u32(sOwnA), ownB = smem_u32(sOwnB);
       const uint32_t p_addr = smem_u32(sP), ds_addr = smem_u32(sDS);
-      bool ok = bounded_wait(&bars->own_full, 0, abort, p.status, kStatusTimeoutFull);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j % ST;
-        if (!bounded_wait(&bars->in_full[s], (j / ST) & 1, abort, p.status, kStatusTimeoutFull))
-          break;
-        // The score accumulators are free once the compute warps have consumed
-        // tile j-1, which they signal through pds_ready (waited on below).
+      const int halves = 2 * n_tiles;
+      auto issue_scores = [&](int h) -> bool {
+        const int j = h >> 1, hh = h & 1, s = j % ST;
+        if (hh == 0 &&
+            !bounded_wait(&bars->in_full[s], (j / ST) & 1, abort, p.status, kStatusTimeoutFull))
+          return false;
         tc_fence_after();
-        const uint32_t inA = smem_u32(sIn + s * 2 * L::kTileBytes);
+        const uint32_t inA = smem_u32(sIn + s * 2 * L::kTileBytes) + hh * 64 * 128;
         const uint32_t inB = inA + L::kTileBytes;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)  // S^T = K Q^T   or   S = Q K^T
-          umma_bf16_ss(tS, desc_kmajor(ownA, kTile, k), desc_kmajor(inA, kTile, k), idesc_s, k != 0);
+          umma_bf16_ss(tS + hh * 64, desc_kmajor(ownA, kTile, k), desc_kmajor(inA, kTile, k),
+                       idesc_s, k != 0);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)  // dP^T = V dO^T  or  dP = dO V^T
-          umma_bf16_ss(tDP, desc_kmajor(ownB, kTile, k), desc_kmajor(inB, kTile, k), idesc_s,
-                       k != 0);
-        umma_commit(&bars->sp_full);
-        if (!bounded_wait(&bars->pds_ready, j & 1, abort, p.status, kStatusTimeoutTmemFull)) break;
+          umma_bf16_ss(tDP + hh * 64, desc_kmajor(ownB, kTile, k), desc_kmajor(inB, kTile, k),
+                       idesc_s, k != 0);
+        umma_commit(&bars->sp_full[hh]);
+        return true;
+      };
+      bool ok = bounded_wait(&bars->own_full, 0, abort, p.status, kStatusTimeoutFull);
+      if (ok) ok = issue_scores(0);
+      for (int h = 0; h < halves && ok; ++h) {
+        const int j = h >> 1, hh = h & 1, s = j % ST;
+        // The score halves of h+1 reuse the TMEM columns of h-1, which the compute
+        // warps released when they signalled pds_ready for h-1 (waited on in the
+        // previous iteration).  With a single stage of streamed tiles the next tile
+        // only arrives after this tile's accumulation, so its scores wait for that.
+        const bool more = h + 1 < halves;
+        const bool early = more && !(ST == 1 && hh == 1);
+        if (early && !issue_scores(h + 1)) break;
+        if (!bounded_wait(&bars->pds_ready[hh], j & 1, abort, p.status, kStatusTimeoutTmemFull))
+          break;
         tc_fence_after();
+        const uint32_t inA = smem_u32(sIn + s * 2 * L::kTileBytes);
+        const uint32_t inB = inA + L::kTileBytes;
+        const uint32_t p_half = p_addr + hh * (kTile * 128);
+        const uint32_t ds_half = ds_addr + hh * (kTile * 128);
         if constexpr (KV_OWNED) {
 #pragma unroll
-          for (int k = 0; k < kTile / 16; ++k)  // dV += P^T dO
-            umma_bf16_ss(tAcc0, desc_kmajor(p_addr, kTile, k), desc_mnmajor(inB, k), idesc_acc,
-                         (j | k) != 0);
+          for (int k = 0; k < 4; ++k)  // dV += P^T dO
+            umma_bf16_ss(tAcc0, desc_kmajor(p_half, kTile, k), desc_mnmajor(inB, hh * 4 + k),
+                         idesc_acc, (h | k) != 0);
 #pragma unroll
-          for (int k = 0; k < kTile / 16; ++k)  // dK += dS^T Q
-            umma_bf16_ss(tAcc1, desc_kmajor(ds_addr, kTile, k), desc_mnmajor(inA, k), idesc_acc,
-                         (j | k) != 0);
+          for (int k = 0; k < 4; ++k)  // dK += dS^T Q
+            umma_bf16_ss(tAcc1, desc_kmajor(ds_half, kTile, k), desc_mnmajor(inA, hh * 4 + k),
+                         idesc_acc, (h | k) != 0);
         } else {
 #pragma unroll
-          for (int k = 0; k < kTile / 16; ++k)  // dQ += dS K
-            umma_bf16_ss(tAcc0, desc_kmajor(ds_addr, kTile, k), desc_mnmajor(inA, k), idesc_acc,
-                         (j | k) != 0);
+          for (int k = 0; k < 4; ++k)  // dQ += dS K
+            umma_bf16_ss(tAcc0, desc_kmajor(ds_half, kTile, k), desc_mnmajor(inA, hh * 4 + k),
+                         idesc_acc, (h | k) != 0);
         }
-        umma_commit(&bars->in_empty[s]);
-        umma_commit(&bars->acc_done);
+        if (hh == 1) umma_commit(&bars->in_empty[s]);
+        umma_commit(&bars->acc_done[hh]);
+        if (more && !early && !issue_scores(h + 1)) break;
       }
     }
   } else {
+    // Two warps share each TMEM lane quarter (rows): `part` picks which 32-column
+    // chunk of every 64-column half a warp turns into probabilities, and which
+    // column chunks of the final accumulators it writes out.
     const int quarter = warp & 3;
+    const int part = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;
     const int own_pos = own_tile * kTile + row;  // key index (kv-owned) or query index
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
@@ -747,62 +781,71 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
             my_delta = fmaf(x.y, y.y, my_delta);
           }
         }
-        p.delta[stat_base + own_pos] = my_delta;
+        if (part == 0) p.delta[stat_base + own_pos] = my_delta;
       }
     }
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const TileInfo t = tile_info(p.sched, range, j);
-      const int other0 = t.other * kTile;
-      const bool ragged = (other0 + kTile > p.N) || (own_tile * kTile + kTile > p.N);
-      const bool masked = !t.full || ragged;
-      const bool use_doc = masked && p.sched.doc != nullptr;
-      if (KV_OWNED || use_doc) {
-        // Per-column data of this tile: (negated) log-sum-exp and delta of the
-        // query columns for the key-owned kernel, document labels for both.
-        if (j > 0) named_barrier_128();  // previous tile's readers are done
-        const int ci = other0 + row;
-        if constexpr (KV_OWNED) {
-          float ls = ci < p.N ? p.lse[stat_base + ci] * kLog2e : INFINITY;
-          if (ls == -INFINITY) ls = INFINITY;
-          sStats[row] = -ls;
-          sStats[kTile + row] = ci < p.N ? p.delta[stat_base + ci] : 0.f;
+    // state of the current streamed tile, set up when its first half starts
+    bool masked = false, use_doc = false;
+    RowMask rm{0, 0u};
+    uint32_t group_bits = 0xffu;
+    int my_doc = -2;
+    for (int h = 0; h < 2 * n_tiles && ok; ++h) {
+      const int j = h >> 1, hh = h & 1;
+      if (hh == 0) {
+        const TileInfo t = tile_info(p.sched, range, j);
+        const int other0 = t.other * kTile;
+        const bool ragged = (other0 + kTile > p.N) || (own_tile * kTile + kTile > p.N);
+        masked = !t.full || ragged;
+        use_doc = masked && p.sched.doc != nullptr;
+        if (KV_OWNED || use_doc) {
+          // Per-column data of this tile: (negated) log-sum-exp and delta of the
+          // query columns for the key-owned kernel, document labels for both.
+          if (j > 0) named_barrier_bwd();  // previous tile's readers are done
+          const int ci = other0 + row;
+          if (part == 0) {
+            if constexpr (KV_OWNED) {
+              float ls = ci < p.N ? p.lse[stat_base + ci] * kLog2e : INFINITY;
+              if (ls == -INFINITY) ls = INFINITY;
+              sStats[row] = -ls;
+              sStats[kTile + row] = ci < p.N ? p.delta[stat_base + ci] : 0.f;
+            }
+            if (use_doc) sDoc[row] = ci < p.N ? p.sched.doc[ci] : -1;
+          }
+          named_barrier_bwd();
         }
-        if (use_doc) sDoc[row] = ci < p.N ? p.sched.doc[ci] : -1;
-        named_barrier_128();
+        rm = RowMask{0, 0u};
+        group_bits = 0xffu;
+        my_doc = -2;
+        if (masked) {
+          // The bitmap is indexed (query sub-block, key sub-block).
+          if constexpr (KV_OWNED) {
+            rm = row_mask_for_key(p.sched, own_pos, other0, p.N);
+            group_bits = 0;
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              group_bits |= static_cast<uint32_t>((t.bitmap >> (g * 8 + (row >> 4))) & 1ull) << g;
+          } else {
+            rm = row_mask_for_query(p.sched, own_pos, other0, p.N);
+            group_bits = static_cast<uint32_t>(t.bitmap >> ((row >> 4) * 8)) & 0xffu;
+          }
+          if (use_doc && own_pos < p.N) my_doc = p.sched.doc[own_pos];
+        }
       }
-      if (!bounded_wait(&bars->sp_full, j & 1, abort, p.status, kStatusTimeoutTmemFull)) {
+      if (!bounded_wait(&bars->sp_full[hh], j & 1, abort, p.status, kStatusTimeoutTmemFull)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      RowMask rm{0, 0u};
-      uint32_t group_bits = 0xffu;
-      int my_doc = -2;
-      if (masked) {
-        // The bitmap is indexed (query sub-block, key sub-block).
-        if constexpr (KV_OWNED) {
-          rm = row_mask_for_key(p.sched, own_pos, other0, p.N);
-          group_bits = 0;
-#pragma unroll
-          for (int g = 0; g < 8; ++g)
-            group_bits |= static_cast<uint32_t>((t.bitmap >> (g * 8 + (row >> 4))) & 1ull) << g;
-        } else {
-          rm = row_mask_for_query(p.sched, own_pos, other0, p.N);
-          group_bits = static_cast<uint32_t>(t.bitmap >> ((row >> 4) * 8)) & 0xffu;
-        }
-        if (use_doc && own_pos < p.N) my_doc = p.sched.doc[own_pos];
-      }
-      // The P and dS tiles are free once the accumulation MMAs of tile j-1 are done;
-      // the tensor pipe runs in issue order, so that already holds when the scores
-      // of tile j have arrived and this wait returns at once.
-      if (j > 0 &&
-          !bounded_wait(&bars->acc_done, (j - 1) & 1, abort, p.status, kStatusTimeoutTmemFull)) {
+      // Half hh of the P and dS tiles is free once the accumulation MMAs of the
+      // previous tile's same half are done.
+      if (j > 0 && !bounded_wait(&bars->acc_done[hh], (j - 1) & 1, abort, p.status,
+                                 kStatusTimeoutTmemFull)) {
         ok = false;
         break;
       }
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      {
+        const int c = 2 * hh + part;
         float sv[32], dp[32];
         uint32_t pp[16], dd[16];
         tmem_ld_32x32f(tS + lane_base + c * 32, sv);
@@ -842,17 +885,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
       }
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(&bars->pds_ready);
+      mbar_arrive(&bars->pds_ready[hh]);
     }
-    if (ok && n_tiles > 0)
-      ok = bounded_wait(&bars->acc_done, (n_tiles - 1) & 1, abort, p.status, kStatusTimeoutTmemFull);
+    if (ok && n_tiles > 0)  // the tensor pipe is in order: the last half finishing ends them all
+      ok = bounded_wait(&bars->acc_done[1], (n_tiles - 1) & 1, abort, p.status,
+                        kStatusTimeoutTmemFull);
     if (ok) {
       tc_fence_after();
       const long goff = 2 * (b * p.g_sb + h * p.g_sh + static_cast<long>(own_pos) * p.g_st);
       auto write_acc = [&](uint32_t taddr, void* dst_base, float mul, bool rotate) {
         uint8_t* dst = static_cast<uint8_t*>(dst_base) + goff;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c0 = 0; c0 < D / 32; c0 += 2) {
+          const int c = c0 + part;
           float a[32];
           if (n_tiles > 0) {
             tmem_ld_32x32f(taddr + lane_base + c * 32, a);
@@ -1059,9 +1104,9 @@ extern "C" int sfl_attn_bwd(const SflAttnTensor* q, const SflAttnTensor* k, cons
     rc = set_smem(kkv, BwdSmem<D_>::kBytes);                                                  \
     if (rc) return rc;                                                                        \
     p.sched = to_sched(mask, false);                                                          \
-    kq<<<grid, kAttnThreads, BwdSmem<D_>::kBytes, stream>>>(tq, tdo, tk, tv, p);              \
+    kq<<<grid, kBwdThreads, BwdSmem<D_>::kBytes, stream>>>(tq, tdo, tk, tv, p);              \
     p.sched = to_sched(mask, true);                                                           \
-    kkv<<<grid, kAttnThreads, BwdSmem<D_>::kBytes, stream>>>(tk, tv, tq, tdo, p);             \
+    kkv<<<grid, kBwdThreads, BwdSmem<D_>::kBytes, stream>>>(tk, tv, tq, tdo, p);             \
   }
   if (D == 64) { if (is_fp16) SFL_BWD(64, true) else SFL_BWD(64, false) }
   else { if (is_fp16) SFL_BWD(128, true) else SFL_BWD(128, false) }
