@@ -1,0 +1,278 @@
+"""Kernel-level timings of this library at the shapes of the 324M training step.
+
+    python -m systems_for_llms_b200.ops.microbench gemm        # every GEMM of one layer
+    python -m systems_for_llms_b200.ops.microbench attention   # fwd / bwd at B4 H16 N1024 D64
+    python -m systems_for_llms_b200.ops.microbench elementwise # norms, loss, optimizer
+    python -m systems_for_llms_b200.ops.microbench step        # per-kernel table of one step
+    python -m systems_for_llms_b200.ops.microbench once NAME   # a few launches of one op
+
+Each timing is the median of CUDA-event measurements with a 256 MB buffer
+written between launches, so operands come from HBM rather than from a warm L2.
+Rates are printed next to their fraction of a roofline denominator: the measured
+cuBLAS bf16 throughput and copy bandwidth in ``MEASURED_PEAKS.json`` at the
+repository root when that file exists, otherwise 1590 TFLOP/s and 6650 GB/s.
+``once`` exists so that a profiler can capture a named kernel from a process that
+does little else; ``--json`` prints one machine-readable line instead of a table.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+from pathlib import Path
+
+import torch
+
+M_TOKENS, D_MODEL, D_FF, SEQ, HEADS, VOCAB = 4096, 1024, 2752, 1024, 16, 10000
+FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
+
+
+def peaks() -> tuple[dict, str]:
+    path = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if path.is_file():
+        data = json.loads(path.read_text())
+        if all(key in data for key in FALLBACK_PEAKS):
+            return {key: float(data[key]) for key in FALLBACK_PEAKS}, "of measured"
+    return dict(FALLBACK_PEAKS), "of fallback"
+
+
+def rnd(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
+
+
+def timeit(fn, iters: int = 30, warmup: int = 5) -> float:
+    """Median microseconds per call, L2 flushed between calls."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    flush = torch.empty(256 * 2 ** 20, dtype=torch.uint8, device="cuda")
+    samples = []
+    for _ in range(iters):
+        flush.zero_()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        fn()
+        end.record()
+        end.synchronize()
+        samples.append(begin.elapsed_time(end) * 1000)
+    return statistics.median(samples)
+
+
+def rope_tables(seq: int, dim: int):
+    inv = 1.0 / (10000.0 ** (torch.arange(0, dim, 2, device="cuda").float() / dim))
+    angles = torch.arange(seq, device="cuda").float()[:, None] * inv[None]
+    return tuple(f(angles).bfloat16().float().contiguous() for f in (torch.cos, torch.sin))
+
+
+def gemm_ops() -> dict:
+    """name -> (callable, flops, algorithmic bytes) for every GEMM of one block + the head."""
+    from . import gemm as G
+    M, C, F, dk = M_TOKENS, D_MODEL, D_FF, D_MODEL // HEADS
+    x, res = rnd(M, C), torch.randn(M, C, device="cuda")
+    wqkv, wo = rnd(3 * C, C, scale=0.03), rnd(C, C, scale=0.03)
+    w13, w2 = rnd(2 * F, C, scale=0.03), rnd(C, F, scale=0.03)
+    cos, sin = rope_tables(SEQ, dk)
+    qkv = torch.empty(M, 3 * C, dtype=torch.bfloat16, device="cuda")
+    ro = torch.empty(M, C, device="cuda")
+    g, a13 = G.swiglu_fwd(x, w13, F)
+    dy = rnd(M, C)
+    d13 = G.swiglu_bwd(dy, w2, a13)
+    dx = torch.empty(M, C, dtype=torch.bfloat16, device="cuda")
+    G.linear_fwd_rope(x, wqkv, cos, sin, SEQ, 2 * C, dk, qkv)
+    logits = torch.empty(M, VOCAB, dtype=torch.bfloat16, device="cuda")
+    whead = rnd(VOCAB, C, scale=0.03)
+    grads = {"qkv": torch.zeros(3 * C, C, device="cuda"), "wo": torch.zeros(C, C, device="cuda"),
+             "w13": torch.zeros(2 * F, C, device="cuda"), "w2": torch.zeros(C, F, device="cuda")}
+    group = [(dy, g, grads["w2"], True), (d13, x, grads["w13"], True),
+             (dy, x, grads["wo"], True), (qkv, x, grads["qkv"], True)]
+    b16, b32 = 2, 4
+
+    def flops(m, n, k):
+        return 2.0 * m * n * k
+
+    ops = {
+        "qkv_rope": (lambda: G.linear_fwd_rope(x, wqkv, cos, sin, SEQ, 2 * C, dk, qkv),
+                     flops(M, 3 * C, C), b16 * (M * C + 3 * C * C + M * 3 * C)),
+        "wo_resid": (lambda: G.linear_fwd_resid(x, wo, res, ro),
+                     flops(M, C, C), b16 * (M * C + C * C) + 2 * b32 * M * C),
+        "w13_swiglu": (lambda: G.swiglu_fwd(x, w13, F),
+                       flops(M, 2 * F, C), b16 * (M * C + 2 * F * C + 3 * M * F)),
+        "w2_resid": (lambda: G.linear_fwd_resid(g, w2, res, ro),
+                     flops(M, C, F), b16 * (M * F + C * F) + 2 * b32 * M * C),
+        "swiglu_bwd": (lambda: G.swiglu_bwd(dy, w2, a13),
+                       flops(M, F, C), b16 * (M * C + C * F + 4 * M * F)),
+        "dgrad_w13": (lambda: G.linear_dgrad(d13, w13, dx),
+                      flops(M, C, 2 * F), b16 * (2 * M * F + 2 * F * C + M * C)),
+        "dgrad_qkv": (lambda: G.linear_dgrad(qkv, wqkv, dx),
+                      flops(M, C, 3 * C), b16 * (3 * M * C + 3 * C * C + M * C)),
+        "dgrad_wo": (lambda: G.linear_dgrad(dy, wo, dx),
+                     flops(M, C, C), b16 * (2 * M * C + C * C)),
+        "wgrad_group": (lambda: G.wgrad_grouped(group),
+                        flops(M, C, F) + flops(M, 2 * F, C) + flops(M, C, C) + flops(M, 3 * C, C),
+                        b16 * M * (C + F + 2 * F + C + C + C + 3 * C + C)
+                        + 2 * b32 * (3 * C * C + C * C + 3 * F * C)),
+        "head": (lambda: G.linear_fwd(x, whead, logits),
+                 flops(M, VOCAB, C), b16 * (M * C + VOCAB * C + M * VOCAB)),
+    }
+    return ops
+
+
+def attention_ops(B=4, H=HEADS, N=SEQ, D=64) -> dict:
+    from ..attention import flash, masks
+    q, k, v, upstream = (torch.randn(B, H, N, D, device="cuda").bfloat16() for _ in range(4))
+    out = torch.empty_like(q)
+    lse = torch.empty(B, H, N, device="cuda")
+    mask = flash.prepare_mask(q, None, masks.MaskSpec(causal=True), None, "interval")
+    grads = [torch.empty_like(q) for _ in range(3)]
+    cos, sin = rope_tables(N, D)
+    scale = D ** -0.5
+    flash.flash_fwd(q, k, v, out, lse, mask, scale)
+    causal = 4.0 * B * H * N * N * D * 0.5
+    io = 2 * B * H * N * D
+    return {
+        "attn_fwd": (lambda: flash.flash_fwd(q, k, v, out, lse, mask, scale), causal, 4 * io),
+        "attn_bwd": (lambda: flash.flash_bwd(q, k, v, out, upstream, lse, *grads, mask, scale,
+                                             rope=(cos, sin)), 2.5 * causal, 8 * io),
+    }
+
+
+def elementwise_ops() -> dict:
+    from . import functional as K
+    M, C = M_TOKENS, D_MODEL
+    x = torch.randn(M, C, device="cuda")
+    w = torch.ones(C, device="cuda")
+    h, rstd = K.rmsnorm(x, w, 1e-5)
+    dy, dres = rnd(M, C), torch.randn(M, C, device="cuda")
+    dw = torch.zeros(C, device="cuda")
+    logits = rnd(M, VOCAB)
+    dlogits = torch.empty_like(logits)
+    targets = torch.randint(0, VOCAB, (M,), device="cuda")
+    return {
+        "rmsnorm_fwd": (lambda: K.rmsnorm(x, w, 1e-5), 0.0, M * C * (4 + 2)),
+        "rmsnorm_bwd": (lambda: K.rmsnorm_bwd(dy, x, w, rstd, dres, dw, True, want_bf16=True),
+                        0.0, M * C * (2 + 4 + 4 + 4 + 2)),
+        "cross_entropy": (lambda: K.cross_entropy_rows(logits, targets, VOCAB, dlogits, 1.0), 0.0,
+                          2 * M * VOCAB * 2),
+    }
+
+
+SUITES = {"gemm": gemm_ops, "attention": attention_ops, "elementwise": elementwise_ops}
+
+
+def run_suite(name: str) -> list[dict]:
+    from .gemm import check_status
+    reference, label = peaks()
+    rows = []
+    for op, (fn, flops, nbytes) in SUITES[name]().items():
+        micros = timeit(fn)
+        row = {"op": op, "us": micros, "denominator": label}
+        if flops:
+            row["tflops"] = flops / micros / 1e6
+            row["frac_bf16_burst"] = row["tflops"] / reference["bf16_tflops"]
+            row["frac_bf16_sustained"] = row["tflops"] / reference["bf16_tflops_sustained"]
+        row["gbs"] = nbytes / micros / 1e3
+        row["frac_hbm"] = row["gbs"] / reference["hbm_gbs"]
+        rows.append(row)
+    torch.cuda.synchronize()
+    check_status()
+    return rows
+
+
+def print_rows(rows: list[dict]) -> None:
+    print(f"{'op':14s} {'us':>9s} {'TFLOP/s':>9s} {'burst':>7s} {'sust.':>7s} {'GB/s':>8s} "
+          f"{'hbm':>6s}   ({rows[0]['denominator']})")
+    for row in rows:
+        tf = f"{row['tflops']:9.1f} {row['frac_bf16_burst']:7.2f} {row['frac_bf16_sustained']:7.2f}" \
+            if "tflops" in row else f"{'':9s} {'':7s} {'':7s}"
+        print(f"{row['op']:14s} {row['us']:9.1f} {tf} {row['gbs']:8.0f} {row['frac_hbm']:6.2f}")
+    print(f"{'total':14s} {sum(r['us'] for r in rows):9.1f}")
+
+
+def step_table(steps: int = 3) -> dict:
+    """Wall time of the flagship training step and its per-kernel device time."""
+    import time
+
+    from ..models.transformer import TransformerLM
+    from ..optim import FusedAdamW
+    from .gemm import check_status
+    torch.manual_seed(0)
+    model = TransformerLM(vocab_size=VOCAB, context_length=SEQ, d_model=D_MODEL, num_layers=24,
+                          num_heads=HEADS, d_ff=D_FF, rope_theta=10000.0, attention_backend="sdpa",
+                          device="cuda", dtype=torch.float32)
+    optimizer = FusedAdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
+    x = torch.randint(0, VOCAB, (4, SEQ), device="cuda")
+    y = torch.randint(0, VOCAB, (4, SEQ), device="cuda")
+
+    def step(accumulation=8):
+        optimizer.zero_grad(set_to_none=True)
+        for _ in range(accumulation):
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                loss = model.loss(x, y, 1.0 / accumulation)
+            loss.backward()
+        optimizer.engine = model._fused
+        return optimizer.clip_and_step(1.0)
+
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    check_status()
+    begin = time.perf_counter()
+    for _ in range(steps):
+        step()
+    torch.cuda.synchronize()
+    seconds = (time.perf_counter() - begin) / steps
+    from torch.profiler import ProfilerActivity, profile
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        step()
+        torch.cuda.synchronize()
+    events = sorted(prof.key_averages(), key=lambda e: -e.device_time_total)[:24]
+    return {"step_ms": seconds * 1e3, "tokens_per_s": 32 * SEQ / seconds,
+            "peak_gib": torch.cuda.max_memory_allocated() / 2 ** 30,
+            "note": "kernel times come from a profiled step; the wall time does not",
+            "kernels": [{"name": e.key[:90], "ms": e.device_time_total / 1e3, "launches": e.count}
+                        for e in events]}
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__,
+                                     formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("what", choices=[*SUITES, "step", "once"])
+    parser.add_argument("name", nargs="?", help="operation for 'once' (e.g. w13_swiglu, attn_bwd)")
+    parser.add_argument("--repeat", type=int, default=3)
+    parser.add_argument("--json", action="store_true")
+    args = parser.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("a CUDA GPU is required")
+    if args.what == "once":
+        from .gemm import check_status
+        for suite in SUITES.values():
+            ops = suite()
+            if args.name in ops:
+                for _ in range(args.repeat):
+                    ops[args.name][0]()
+                torch.cuda.synchronize()
+                check_status()
+                print(f"ran {args.name} x{args.repeat}")
+                return
+        raise SystemExit(f"unknown operation {args.name!r}")
+    if args.what == "step":
+        table = step_table()
+        if args.json:
+            print(json.dumps(table))
+            return
+        print(f"step {table['step_ms']:.1f} ms  {table['tokens_per_s']:.0f} tokens/s  "
+              f"peak {table['peak_gib']:.2f} GiB")
+        for row in table["kernels"]:
+            print(f"{row['ms']:8.2f} ms {row['launches']:6d}  "
+                  f"{row['ms'] / row['launches'] * 1000:8.1f} us  {row['name']}")
+        return
+    rows = run_suite(args.what)
+    if args.json:
+        print(json.dumps(rows))
+    else:
+        print_rows(rows)
+
+
+if __name__ == "__main__":
+    main()
