@@ -266,6 +266,50 @@ int sfl_embedding_fwd(const float* weight, const int64_t* ids, float* out, int r
 /* Library build tag, for diagnostics. */
 const char* sfl_version(void);
 
+/* ------------------------------------------------------ transformer block -- */
+/* One pre-norm block (RMSNorm -> fused QKV + RoPE -> causal attention -> output
+ * projection + residual -> RMSNorm -> SwiGLU -> down projection + residual) run
+ * forward or backward by one call.  Weights are the bf16 copies, [out, in]
+ * row-major, with q|k|v and w1|w3 stacked; norms, the residual stream, statistics
+ * and parameter gradients are fp32.  `saved` (sfl_block_saved_bytes) carries the
+ * activations from forward to backward; `scratch` (sfl_block_scratch_bytes) is
+ * only used during backward.  Buffers need 256-byte alignment. */
+typedef struct SflBlockArgs {
+  int batch, seq_len, d_model, heads, head_dim, d_ff;
+  float eps1, eps2, attn_scale;
+  const void* wqkv;  /* [3 * heads * head_dim, d_model] */
+  const void* wo;    /* [d_model, heads * head_dim]     */
+  const void* w13;   /* [2 * d_ff, d_model]             */
+  const void* w2;    /* [d_model, d_ff]                 */
+  const float* norm1;
+  const float* norm2;
+  const float* rope_cos; /* [>= seq_len, head_dim / 2] */
+  const float* rope_sin;
+  const SflAttnMask* mask;
+  const float* x; /* [batch * seq_len, d_model] */
+  float* x_out;   /* forward only */
+  void* saved;
+  /* backward only */
+  const float* d_out;
+  const void* d_out_bf16; /* optional bf16 copy of d_out */
+  float* dx;
+  void* dx_bf16;
+  void* scratch;
+  float* g_wqkv;
+  float* g_wo;
+  float* g_w13;
+  float* g_w2;
+  float* g_norm1;
+  float* g_norm2;
+  int acc_wqkv, acc_wo, acc_w13, acc_w2, acc_norm1, acc_norm2; /* 1: add to the gradient */
+  int* status;
+} SflBlockArgs;
+
+long sfl_block_saved_bytes(const SflBlockArgs* args);
+long sfl_block_scratch_bytes(const SflBlockArgs* args);
+int sfl_block_forward(const SflBlockArgs* args, void* stream);
+int sfl_block_backward(const SflBlockArgs* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -21,7 +21,9 @@ eager PyTorch call: src/llmlab/model/transformer.py:121-139):
 
 from __future__ import annotations
 
+import ctypes
 import math
+import os
 
 import torch
 
@@ -77,6 +79,14 @@ class FusedEngine:
         self._layout()
         self._flatten()
         self.flat_grad: torch.Tensor | None = None
+        self._shadow_views: dict = {}
+        self._grad_views: dict = {}
+        # Run whole blocks through one library call (csrc/block.cu) instead of one
+        # Python-driven launch per kernel; tensor-parallel engines keep the latter.
+        self.native_blocks = os.environ.get("SFL_PYTHON_BLOCKS", "0") != "1"
+        self._native_args: dict = {}
+        self._native_sizes: dict = {}
+        self._native_keep: list = []
         self._versions = None
         self._bf16_alias: tuple[int, torch.Tensor] | None = None
         # hook(offset): every gradient at flat offset >= offset is final for this backward
@@ -128,10 +138,22 @@ class FusedEngine:
         return flat[begin:begin + p.numel()].view(p.shape)
 
     def shadow(self, p: torch.Tensor, rows: int | None = None) -> torch.Tensor:
-        """bf16 view of ``p``; ``rows`` extends it over adjacent matrices (q|k|v, w1|w3)."""
+        """bf16 view of ``p``; ``rows`` extends it over adjacent matrices (q|k|v, w1|w3).
+
+        Views are cached per (parameter, rows) and rebuilt when the flat buffer is
+        replaced: building a slice + view costs microseconds and every kernel
+        launch of the block needs one.
+        """
+        flat = self.flat_shadow
+        key = (id(p), rows)
+        hit = self._shadow_views.get(key)
+        if hit is not None and hit[0] is flat:
+            return hit[1]
         begin = self.offsets[id(p)]
-        rows = p.shape[0] if rows is None else rows
-        return self.flat_shadow[begin:begin + rows * p.shape[1]].view(rows, p.shape[1])
+        count = p.shape[0] if rows is None else rows
+        view = flat[begin:begin + count * p.shape[1]].view(count, p.shape[1])
+        self._shadow_views[key] = (flat, view)
+        return view
 
     def relocate(self, flat_param: torch.Tensor | None = None,
                  flat_grad: torch.Tensor | None = None) -> None:
@@ -161,10 +183,18 @@ class FusedEngine:
         return self.flat_grad
 
     def grad_view(self, p: torch.Tensor, rows: int | None = None) -> torch.Tensor:
+        flat = self.grad_buffer()
+        key = (id(p), rows)
+        hit = self._grad_views.get(key)
+        if hit is not None and hit[0] is flat:
+            return hit[1]
         begin = self.offsets[id(p)]
         if rows is None:
-            return self.grad_buffer()[begin:begin + p.numel()].view(p.shape)
-        return self.grad_buffer()[begin:begin + rows * p.shape[1]].view(rows, p.shape[1])
+            view = flat[begin:begin + p.numel()].view(p.shape)
+        else:
+            view = flat[begin:begin + rows * p.shape[1]].view(rows, p.shape[1])
+        self._grad_views[key] = (flat, view)
+        return view
 
     def claim(self, *params: torch.Tensor) -> bool:
         """Attach the flat views as ``.grad`` and say whether to accumulate.
@@ -248,9 +278,113 @@ class FusedEngine:
         return rows.sum() * (scale / rows.numel())
 
 
+# ----------------------------------------------------- native block runner --
+def _native_args(engine: FusedEngine, index: int, B: int, T: int) -> "_lib.BlockArgs":
+    """The constant part of a block's argument record; pointers that change per call
+    (activations, weights of sharded engines) are filled in by the callers."""
+    cache = engine._native_args
+    key = (index, B, T)
+    args = cache.get(key)
+    if args is None:
+        layer = engine.model.layers[index]
+        args = _lib.BlockArgs()
+        args.batch, args.seq_len, args.d_model = B, T, engine.d_model
+        args.heads, args.head_dim, args.d_ff = engine.num_heads, engine.d_k, engine.d_ff
+        args.eps1, args.eps2 = layer.attn_norm.eps, layer.ffn_norm.eps
+        args.attn_scale = engine.d_k ** -0.5
+        args.rope_cos, args.rope_sin = engine.cos.data_ptr(), engine.sin.data_ptr()
+        mask = flash.causal_mask(engine.device, T)
+        args.mask = ctypes.addressof(mask.struct)
+        args.status = G.status_word(engine.device).data_ptr()
+        handle = _lib.lib()
+        sizes = (handle.sfl_block_saved_bytes(ctypes.byref(args)),
+                 handle.sfl_block_scratch_bytes(ctypes.byref(args)))
+        if min(sizes) <= 0:
+            raise RuntimeError("block shape not supported by the native runner")
+        cache[key] = args
+        engine._native_sizes[key] = sizes
+        engine._native_keep.append(mask)      # the record points into the mask
+    return args
+
+
+def _native_weights(engine: FusedEngine, args, layer) -> None:
+    aw, dff = engine.attn_width, engine.d_ff
+    args.wqkv = engine.shadow(layer.attn.q_proj.weight, 3 * aw).data_ptr()
+    args.wo = engine.shadow(layer.attn.output_proj.weight).data_ptr()
+    args.w13 = engine.shadow(layer.ffn.w1.weight, 2 * dff).data_ptr()
+    args.w2 = engine.shadow(layer.ffn.w2.weight).data_ptr()
+    args.norm1 = layer.attn_norm.weight.data_ptr()
+    args.norm2 = layer.ffn_norm.weight.data_ptr()
+
+
+def native_block_forward(engine: FusedEngine, index: int, x: torch.Tensor, B: int, T: int):
+    """``block_forward`` through one library call (csrc/block.cu)."""
+    layer = engine.model.layers[index]
+    engine.prepare_block(index, False)
+    args = _native_args(engine, index, B, T)
+    x2 = x.reshape(B * T, engine.d_model)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    saved = torch.empty(engine._native_sizes[(index, B, T)][0], dtype=torch.uint8, device=x.device)
+    out = torch.empty_like(x2)
+    _native_weights(engine, args, layer)
+    args.x, args.x_out, args.saved = x2.data_ptr(), out.data_ptr(), saved.data_ptr()
+    code = _lib.lib().sfl_block_forward(ctypes.byref(args), _lib.stream_ptr())
+    _lib.check(code, "sfl_block_forward")
+    return out.view(B, T, engine.d_model), (x2, saved)
+
+
+def native_block_backward(engine: FusedEngine, index: int, saved, d_out: torch.Tensor, B: int,
+                          T: int):
+    layer = engine.model.layers[index]
+    attn_p, ffn = layer.attn, layer.ffn
+    d, aw, dff = engine.d_model, engine.attn_width, engine.d_ff
+    x2, buffer = saved
+    args = _native_args(engine, index, B, T)
+    dres = d_out.reshape(B * T, d)
+    if not dres.is_contiguous():
+        dres = dres.contiguous()
+    alias = engine._bf16_alias
+    engine._bf16_alias = None
+    scratch = torch.empty(engine._native_sizes[(index, B, T)][1], dtype=torch.uint8,
+                          device=dres.device)
+    dx = torch.empty_like(dres)
+    dx_bf16 = torch.empty(B * T, d, dtype=torch.bfloat16, device=dres.device)
+    _native_weights(engine, args, layer)
+    args.x, args.saved, args.scratch = x2.data_ptr(), buffer.data_ptr(), scratch.data_ptr()
+    args.d_out = dres.data_ptr()
+    args.d_out_bf16 = (alias[1].data_ptr()
+                       if alias is not None and alias[0] == dres.data_ptr() else None)
+    args.dx, args.dx_bf16 = dx.data_ptr(), dx_bf16.data_ptr()
+    args.acc_w2 = engine.claim(ffn.w2.weight)
+    args.acc_w13 = engine.claim(ffn.w1.weight, ffn.w3.weight)
+    args.acc_norm2 = engine.claim(layer.ffn_norm.weight)
+    args.acc_wo = engine.claim(attn_p.output_proj.weight)
+    args.acc_wqkv = engine.claim(attn_p.q_proj.weight, attn_p.k_proj.weight, attn_p.v_proj.weight)
+    args.acc_norm1 = engine.claim(layer.attn_norm.weight)
+    args.g_w2 = engine.grad_view(ffn.w2.weight).data_ptr()
+    args.g_w13 = engine.grad_view(ffn.w1.weight, 2 * dff).data_ptr()
+    args.g_norm2 = engine.grad_view(layer.ffn_norm.weight).data_ptr()
+    args.g_wo = engine.grad_view(attn_p.output_proj.weight).data_ptr()
+    args.g_wqkv = engine.grad_view(attn_p.q_proj.weight, 3 * aw).data_ptr()
+    args.g_norm1 = engine.grad_view(layer.attn_norm.weight).data_ptr()
+    code = _lib.lib().sfl_block_backward(ctypes.byref(args), _lib.stream_ptr())
+    _lib.check(code, "sfl_block_backward")
+    engine._bf16_alias = (dx.data_ptr(), dx_bf16)
+    if engine.on_block_backward is not None:
+        engine.on_block_backward(engine.layer_ranges[index][0])
+    return dx.view(B, T, d)
+
+
+def _use_native(engine: FusedEngine) -> bool:
+    return engine.tp is None and engine.native_blocks
+
+
 # ------------------------------------------------------------ block kernels --
 def block_forward(engine: FusedEngine, index: int, x: torch.Tensor, B: int, T: int):
     """Returns ``(x_out, saved)`` where ``saved`` holds what backward needs."""
+    if _use_native(engine):
+        return native_block_forward(engine, index, x, B, T)
     layer = engine.model.layers[index]
     d, dk, H, dff, aw = engine.d_model, engine.d_k, engine.num_heads, engine.d_ff, engine.attn_width
     tp = engine.tp
@@ -283,6 +417,8 @@ def block_forward(engine: FusedEngine, index: int, x: torch.Tensor, B: int, T: i
 
 
 def block_backward(engine: FusedEngine, index: int, saved, d_out: torch.Tensor, B: int, T: int):
+    if _use_native(engine):
+        return native_block_backward(engine, index, saved, d_out, B, T)
     layer = engine.model.layers[index]
     d, dk, H, dff, aw = engine.d_model, engine.d_k, engine.num_heads, engine.d_ff, engine.attn_width
     tp = engine.tp

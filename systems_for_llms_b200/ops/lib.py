@@ -42,6 +42,26 @@ class WgradProblem(Structure):
     ]
 
 
+class BlockArgs(Structure):
+    """Mirror of ``SflBlockArgs`` in csrc/sfl.h."""
+
+    _fields_ = [
+        ("batch", c_int), ("seq_len", c_int), ("d_model", c_int), ("heads", c_int),
+        ("head_dim", c_int), ("d_ff", c_int),
+        ("eps1", c_float), ("eps2", c_float), ("attn_scale", c_float),
+        ("wqkv", c_void_p), ("wo", c_void_p), ("w13", c_void_p), ("w2", c_void_p),
+        ("norm1", c_void_p), ("norm2", c_void_p), ("rope_cos", c_void_p), ("rope_sin", c_void_p),
+        ("mask", c_void_p), ("x", c_void_p), ("x_out", c_void_p), ("saved", c_void_p),
+        ("d_out", c_void_p), ("d_out_bf16", c_void_p), ("dx", c_void_p), ("dx_bf16", c_void_p),
+        ("scratch", c_void_p),
+        ("g_wqkv", c_void_p), ("g_wo", c_void_p), ("g_w13", c_void_p), ("g_w2", c_void_p),
+        ("g_norm1", c_void_p), ("g_norm2", c_void_p),
+        ("acc_wqkv", c_int), ("acc_wo", c_int), ("acc_w13", c_int), ("acc_w2", c_int),
+        ("acc_norm1", c_int), ("acc_norm2", c_int),
+        ("status", c_void_p),
+    ]
+
+
 EPI_BF16, EPI_F32, EPI_RESID, EPI_ROPE, EPI_SWIGLU, EPI_SWIGLU_BWD = range(6)
 
 _P = c_void_p
@@ -49,6 +69,10 @@ _SIGNATURES = {
     "sfl_gemm_bf16": [_P, c_long, c_int, _P, c_long, c_int, c_int, c_int, c_int,
                       POINTER(GemmEpilogue), c_int, c_int, _P],
     "sfl_gemm_wgrad_grouped": [POINTER(WgradProblem), c_int, _P, _P],
+    "sfl_block_forward": [POINTER(BlockArgs), _P],
+    "sfl_block_backward": [POINTER(BlockArgs), _P],
+    "sfl_block_saved_bytes": [POINTER(BlockArgs)],
+    "sfl_block_scratch_bytes": [POINTER(BlockArgs)],
     "sfl_rmsnorm_fwd": [_P, _P, _P, _P, c_int, c_int, c_float, _P],
     "sfl_rmsnorm_bwd_blocks": [c_int],
     "sfl_rmsnorm_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, _P],
@@ -73,7 +97,8 @@ def register_signature(name: str, argtypes: list) -> None:
 
 
 # Kernels launched per call of each entry point (default 1, 0 for host-only calls).
-_KERNELS_PER_CALL = {"sfl_attn_bwd": 2, "sfl_rmsnorm_bwd_blocks": 0, "sfl_sqnorm_blocks": 0,
+_KERNELS_PER_CALL = {"sfl_attn_bwd": 2, "sfl_block_forward": 7, "sfl_block_backward": 12,
+                     "sfl_block_saved_bytes": 0, "sfl_block_scratch_bytes": 0, "sfl_rmsnorm_bwd_blocks": 0, "sfl_sqnorm_blocks": 0,
                      "sfl_ipc_alloc": 0, "sfl_ipc_free": 0, "sfl_ipc_get_handle": 0,
                      "sfl_ipc_open_handle": 0, "sfl_ipc_close_handle": 0,
                      "sfl_comm_set_spin_limit": 0, "sfl_comm_flag_bytes": 0, "sfl_comm_slots": 0,
@@ -95,7 +120,7 @@ class _Library:
     def _bind(self, name: str, argtypes: list):
         function = getattr(self._handle, name)
         function.argtypes = argtypes
-        function.restype = c_int
+        function.restype = c_long if name.endswith("_bytes") else c_int
         weight = _KERNELS_PER_CALL.get(name, 1)
         counter = _launches
 
@@ -123,6 +148,13 @@ def lib() -> "_Library":
     return library
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_current_device = torch.cuda.current_device
+if _raw_stream is None:     # very old builds: fall back to the object API
+    def _raw_stream(index):  # noqa: F811
+        return torch.cuda.current_stream(index).cuda_stream
+
+
 def available() -> bool:
     """True when kernels can run: a CUDA device of compute capability 10.x."""
     if not torch.cuda.is_available():
@@ -132,7 +164,13 @@ def available() -> bool:
 
 
 def stream_ptr() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """Raw handle of the calling thread's current CUDA stream.
+
+    ``torch.cuda.current_stream()`` builds a Python ``Stream`` object per call
+    (several microseconds, paid once per kernel launch); the raw query is the
+    same lookup without the object.
+    """
+    return _raw_stream(_current_device())
 
 
 def ptr(tensor: torch.Tensor | None) -> int | None:
