@@ -27,6 +27,7 @@
 #include <math.h>
 #include <stdint.h>
 
+#include "launch.cuh"
 #include "ptx.cuh"
 #include "sfl.h"
 #include "tensormap.cuh"
@@ -379,6 +380,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
+  pdl_launch_dependents();  // set-up done: the next kernel may start its own
+  pdl_wait();               // inputs of this kernel are complete from here on
   const uint32_t tS = tmem;        // two score buffers: columns [0,128) and [128,256)
   const uint32_t tO = tmem + 256;  // output accumulator: D columns
   volatile int* abort = &bars->abort;
@@ -655,6 +658,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
+  pdl_launch_dependents();
+  pdl_wait();
   const uint32_t tS = tmem;         // scores
   const uint32_t tDP = tmem + 128;  // dP
   const uint32_t tAcc0 = tmem + 256;      // dV (kv-owned) or dQ
@@ -1046,7 +1051,8 @@ extern "C" int sfl_attn_fwd(const SflAttnTensor* q, const SflAttnTensor* k, cons
     auto kern = attn_fwd_kernel<D_, F_>;                                                  \
     int rc = set_smem(kern, FwdSmem<D_>::kBytes);                                         \
     if (rc) return rc;                                                                    \
-    kern<<<grid, kAttnThreads, FwdSmem<D_>::kBytes, stream>>>(tq, tk, tv, p);             \
+    rc = launch_pdl(kern, grid, dim3(kAttnThreads), FwdSmem<D_>::kBytes, stream, tq, tk, tv, p); \
+    if (rc) return rc;                                                                    \
   }
   if (D == 64) { if (is_fp16) SFL_FWD(64, true) else SFL_FWD(64, false) }
   else { if (is_fp16) SFL_FWD(128, true) else SFL_FWD(128, false) }
@@ -1104,9 +1110,11 @@ extern "C" int sfl_attn_bwd(const SflAttnTensor* q, const SflAttnTensor* k, cons
     rc = set_smem(kkv, BwdSmem<D_>::kBytes);                                                  \
     if (rc) return rc;                                                                        \
     p.sched = to_sched(mask, false);                                                          \
-    kq<<<grid, kBwdThreads, BwdSmem<D_>::kBytes, stream>>>(tq, tdo, tk, tv, p);              \
+    rc = launch_pdl(kq, grid, dim3(kBwdThreads), BwdSmem<D_>::kBytes, stream, tq, tdo, tk, tv, p); \
+    if (rc) return rc;                                                                        \
     p.sched = to_sched(mask, true);                                                           \
-    kkv<<<grid, kBwdThreads, BwdSmem<D_>::kBytes, stream>>>(tk, tv, tq, tdo, p);             \
+    rc = launch_pdl(kkv, grid, dim3(kBwdThreads), BwdSmem<D_>::kBytes, stream, tk, tv, tq, tdo, p); \
+    if (rc) return rc;                                                                        \
   }
   if (D == 64) { if (is_fp16) SFL_BWD(64, true) else SFL_BWD(64, false) }
   else { if (is_fp16) SFL_BWD(128, true) else SFL_BWD(128, false) }

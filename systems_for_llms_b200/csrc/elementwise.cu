@@ -10,6 +10,7 @@
 #include <math.h>
 #include <stdint.h>
 
+#include "launch.cuh"
 #include "ptx.cuh"
 #include "sfl.h"
 
@@ -61,6 +62,8 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 __global__ void rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                    __nv_bfloat16* __restrict__ y, float* __restrict__ rstd,
                                    int rows, int dim, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -109,6 +112,8 @@ rmsnorm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const float* __rest
                        const float* __restrict__ dres_in, float* __restrict__ dx_out,
                        __nv_bfloat16* __restrict__ dx_bf16, float* __restrict__ dw_partial,
                        int rows) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int dim = NCH * 128;
   extern __shared__ float dw_smem[];  // [warps, dim]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -183,6 +188,8 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const float* __restrict
                    const float* __restrict__ dres_in, float* __restrict__ dx_out,
                    __nv_bfloat16* __restrict__ dx_bf16, float* __restrict__ dw_partial, int rows,
                    int dim) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float dw_smem[];  // [warps, dim]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int warps = blockDim.x >> 5;
@@ -223,6 +230,8 @@ constexpr int kDwReduceWarps = 8;
 __global__ void __launch_bounds__(32 * kDwReduceWarps)
 rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, int blocks, float* __restrict__ dw,
                          int dim, int accumulate) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float part[kDwReduceWarps][32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int i = blockIdx.x * 32 + lane;
@@ -254,6 +263,8 @@ __global__ void __launch_bounds__(256)
 cross_entropy_kernel(const __nv_bfloat16* __restrict__ logits, long ld,
                      const int64_t* __restrict__ targets, float* __restrict__ row_loss,
                      __nv_bfloat16* __restrict__ dlogits, float grad_scale, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[33];
   const int row = blockIdx.x;
   const __nv_bfloat16* lr = logits + static_cast<long>(row) * ld;
@@ -358,6 +369,8 @@ adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restri
 // ------------------------------------------------------------------- misc ---
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y,
                                      long n) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long stride = static_cast<long>(gridDim.x) * blockDim.x;
   const long i0 = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const bool aligned = ((reinterpret_cast<uintptr_t>(x) & 15) | (reinterpret_cast<uintptr_t>(y) & 7)) == 0;
@@ -417,9 +430,8 @@ extern "C" int sfl_rmsnorm_fwd(const float* x, const float* w, void* y, float* r
                                int dim, float eps, void* stream) {
   if (rows <= 0 || dim <= 0) return -2;
   const int warps = 8;
-  rmsnorm_fwd_kernel<<<(rows + warps - 1) / warps, warps * 32, 0, SFL_STREAM(stream)>>>(
-      x, w, static_cast<__nv_bfloat16*>(y), rstd, rows, dim, eps);
-  SFL_RET();
+  return launch_pdl(rmsnorm_fwd_kernel, dim3((rows + warps - 1) / warps), dim3(warps * 32), 0,
+                    SFL_STREAM(stream), x, w, static_cast<__nv_bfloat16*>(y), rstd, rows, dim, eps);
 }
 
 extern "C" int sfl_rmsnorm_bwd_blocks(int rows) {
@@ -446,17 +458,16 @@ extern "C" int sfl_rmsnorm_bwd(const void* dy, const float* x, const float* w, c
   cudaStream_t st = SFL_STREAM(stream);
 #define SFL_NORM_BWD(NCH)                                                                     \
   case NCH:                                                                                   \
-    rmsnorm_bwd_vec_kernel<NCH><<<blocks, kNormBwdThreads, smem, st>>>(                       \
-        dyp, x, w, rstd, dres_in, dx_out, dxb, dw_partial, rows);                             \
-    break;
+    return launch_pdl(rmsnorm_bwd_vec_kernel<NCH>, dim3(blocks), dim3(kNormBwdThreads), smem, \
+                      st, dyp, x, w, rstd, dres_in, dx_out, dxb, dw_partial, rows);
   if (dim % 128 == 0 && dim <= 1024) {
     switch (dim / 128) {
       SFL_NORM_BWD(1) SFL_NORM_BWD(2) SFL_NORM_BWD(3) SFL_NORM_BWD(4)
       SFL_NORM_BWD(5) SFL_NORM_BWD(6) SFL_NORM_BWD(7) SFL_NORM_BWD(8)
     }
   } else {
-    rmsnorm_bwd_kernel<<<blocks, kNormBwdThreads, smem, st>>>(dyp, x, w, rstd, dres_in, dx_out,
-                                                              dxb, dw_partial, rows, dim);
+    return launch_pdl(rmsnorm_bwd_kernel, dim3(blocks), dim3(kNormBwdThreads), smem, st, dyp, x, w,
+                      rstd, dres_in, dx_out, dxb, dw_partial, rows, dim);
   }
 #undef SFL_NORM_BWD
   SFL_RET();
@@ -464,19 +475,17 @@ extern "C" int sfl_rmsnorm_bwd(const void* dy, const float* x, const float* w, c
 
 extern "C" int sfl_rmsnorm_dw_reduce(const float* partial, int blocks, float* dw, int dim,
                                      int accumulate, void* stream) {
-  rmsnorm_dw_reduce_kernel<<<(dim + 31) / 32, 32 * kDwReduceWarps, 0, SFL_STREAM(stream)>>>(
-      partial, blocks, dw, dim, accumulate);
-  SFL_RET();
+  return launch_pdl(rmsnorm_dw_reduce_kernel, dim3((dim + 31) / 32), dim3(32 * kDwReduceWarps), 0,
+                    SFL_STREAM(stream), partial, blocks, dw, dim, accumulate);
 }
 
 extern "C" int sfl_cross_entropy(const void* logits, long ld, const int64_t* targets,
                                  float* row_loss, void* dlogits, float grad_scale, int rows,
                                  int vocab, void* stream) {
   if (rows <= 0 || vocab <= 0) return -2;
-  cross_entropy_kernel<<<rows, 256, 0, SFL_STREAM(stream)>>>(
-      static_cast<const __nv_bfloat16*>(logits), ld, targets, row_loss,
-      static_cast<__nv_bfloat16*>(dlogits), grad_scale, vocab);
-  SFL_RET();
+  return launch_pdl(cross_entropy_kernel, dim3(rows), dim3(256), 0, SFL_STREAM(stream),
+                    static_cast<const __nv_bfloat16*>(logits), ld, targets, row_loss,
+                    static_cast<__nv_bfloat16*>(dlogits), grad_scale, vocab);
 }
 
 extern "C" int sfl_sqnorm_blocks(long n) {
@@ -509,9 +518,8 @@ extern "C" int sfl_adamw(float* p, const float* g, float* m, float* v, void* sha
 
 extern "C" int sfl_cast_f32_to_bf16(const float* x, void* y, long n, void* stream) {
   if (n <= 0) return 0;
-  cast_f32_bf16_kernel<<<grid_for((n + 3) / 4, 256), 256, 0, SFL_STREAM(stream)>>>(
-      x, static_cast<__nv_bfloat16*>(y), n);
-  SFL_RET();
+  return launch_pdl(cast_f32_bf16_kernel, dim3(grid_for((n + 3) / 4, 256)), dim3(256), 0,
+                    SFL_STREAM(stream), x, static_cast<__nv_bfloat16*>(y), n);
 }
 
 extern "C" int sfl_scale_f32(float* x, long n, const float* coef, float scale, void* stream) {

@@ -45,6 +45,7 @@
 #include <mutex>
 #include <tuple>
 
+#include "launch.cuh"
 #include "ptx.cuh"
 #include "sfl.h"
 #include "tensormap.cuh"
@@ -714,6 +715,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
   volatile int* abort = &bars->abort;
+  // Set-up is done without touching global data: let the next kernel in the stream
+  // begin its own set-up, then wait for the previous kernel's results.
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------ TMA producer ----
@@ -946,6 +951,10 @@ wgrad_grouped_kernel(const __grid_constant__ GroupedMaps maps,
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
   volatile int* abort = &bars->abort;
+  // Set-up is done without touching global data: let the next kernel in the stream
+  // begin its own set-up, then wait for the previous kernel's results.
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -1144,8 +1153,7 @@ int launch_one(const CUtensorMap& tmA, const CUtensorMap& tmB, const EpiMaps& em
   const int tiles = p.num_m_tiles * p.num_n_tiles;
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  kernel<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, em, p);
-  return static_cast<int>(cudaGetLastError());
+  return launch_pdl(kernel, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, tmA, tmB, em, p);
 }
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
@@ -1366,6 +1374,5 @@ extern "C" int sfl_gemm_wgrad_grouped(const SflWgradProblem* problems, int count
     configured = true;
   }
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  wgrad_grouped_kernel<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(maps, p);
-  return static_cast<int>(cudaGetLastError());
+  return launch_pdl(wgrad_grouped_kernel, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, maps, p);
 }

@@ -88,6 +88,21 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   return false;
 }
 
+// ------------------------------------------- programmatic dependent launch ----
+// A kernel launched with the programmatic-stream-serialization attribute may start
+// while its predecessor in the stream is still running: everything before
+// pdl_wait() (barrier set-up, TMEM allocation, descriptor prefetch) then overlaps
+// the predecessor's tail; pdl_wait() returns once the predecessor has completed and
+// its writes are visible.  pdl_launch_dependents() lets the successor be scheduled
+// as soon as every CTA of this grid has called it.  Both are no-ops for a kernel
+// launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ------------------------------------------------------------------- TMA ----
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
