@@ -297,10 +297,12 @@ def train_step(strategy: Strategy, data, config, sampler, device, *, global_batc
     report = torch.stack([loss_sum.float(), torch.isfinite(loss_sum).float(),
                           norm.float().to(device)])
     if world > 1:
+        # one collective: the loss sums, and so do the finiteness votes (all ranks
+        # finite <=> the votes add up to the world size)
         votes = report[:2].clone()
-        dist.all_reduce(votes[0:1])
-        dist.all_reduce(votes[1:2], op=dist.ReduceOp.MIN)
+        dist.all_reduce(votes)
         report[:2] = votes
+        report[1] = (votes[1] >= world - 0.5).float()
     mean_loss, finite, norm_value = report.tolist()
     if not finite:
         raise FloatingPointError("Non-finite training loss on a rank")
