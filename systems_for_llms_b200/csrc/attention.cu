@@ -321,11 +321,12 @@ struct FwdSmem {
   static constexpr int kPBytes = kTile * kTile * 2;
   static constexpr int kPBufs = (D == 64) ? 2 : 1;
   static constexpr int kStages = 2;
-  static constexpr int kBytes = kTileBytes * (1 + 2 * kStages) + kPBytes * kPBufs + 1024 + 1024;
+  // two query tiles (the next work item's is prefetched), K and V rings, P tiles
+  static constexpr int kBytes = kTileBytes * (2 + 2 * kStages) + kPBytes * kPBufs + 1024 + 1024;
 };
 
 struct FwdBarriers {
-  uint64_t q_full;
+  uint64_t q_full[2], q_empty[2];
   uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
   uint64_t s_full[2];
   uint64_t p_ready[2];
@@ -335,6 +336,16 @@ struct FwdBarriers {
   int col_doc[kTile];  // document labels of the current key tile
 };
 
+// Persistent forward kernel.  A work item is one 128-row query tile of one
+// (batch, head); items are numbered heaviest first (last query tiles of every
+// head before earlier ones) and dealt to the CTAs in rounds of alternating
+// direction (CTA c takes item c, then 2 grid - 1 - c, then 2 grid + c, ...), which
+// evens out the causal imbalance: 8+4+4 and 6+6+2+2 key tiles rather than
+// 8+6+4+2 and 6+4+2.
+// Barriers, tensor memory and the operand rings are set up once per CTA; every
+// role keeps running counters, so stage indices and barrier phases continue
+// across items and the next item's query tile and first scores are already in
+// flight while the current item's last P V products and its epilogue finish.
 template <int D, bool FP16>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -343,24 +354,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* sQ = smem;
-  uint8_t* sK = sQ + L::kTileBytes;
+  uint8_t* sQ = smem;  // two tiles
+  uint8_t* sK = sQ + 2 * L::kTileBytes;
   uint8_t* sV = sK + L::kStages * L::kTileBytes;
   uint8_t* sP = sV + L::kStages * L::kTileBytes;
   FwdBarriers* bars = reinterpret_cast<FwdBarriers*>(sP + L::kPBufs * L::kPBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // Heaviest (last) query tiles first so causal work is balanced across waves.
   const int num_q_tiles = (p.N + kTile - 1) / kTile;
-  const int q_tile = num_q_tiles - 1 - blockIdx.x;
-  const int bh = blockIdx.y;
-  const int b = bh / p.H, h = bh % p.H;
-  const TileRange range = tile_range(p.sched, q_tile, p.N, false);
-  const int n_tiles = range.end - range.begin;
+  const int BH = p.B * p.H;
+  const int num_items = num_q_tiles * BH;
+  const int rounds = (num_items + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  auto item_tile = [&](int w) { return num_q_tiles - 1 - w / BH; };
+  // item of this CTA in round r, or -1 when the last round has none for it
+  auto item_at = [&](int r) {
+    const int G = gridDim.x, c = blockIdx.x;
+    const int w = r * G + ((r & 1) ? G - 1 - c : c);
+    return w < num_items ? w : -1;
+  };
 
   if (threadIdx.x == 0) {
-    mbar_init(&bars->q_full, 1);
     for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->q_full[s], 1);
+      mbar_init(&bars->q_empty[s], 1);
       mbar_init(&bars->k_full[s], 1);
       mbar_init(&bars->k_empty[s], 1);
       mbar_init(&bars->v_full[s], 1);
@@ -388,31 +404,78 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   constexpr int PB = L::kPBufs;
 
   if (warp == 0) {
-    if (lane == 0 && n_tiles > 0) {
-      mbar_expect_tx(&bars->q_full, L::kTileBytes);
-      load_rows<D>(sQ, &tmQ, &bars->q_full, q_tile * kTile, h, b);
-      for (int j = 0; j < n_tiles; ++j) {
-        const TileInfo t = tile_info(p.sched, range, j);
-        const int s = j & 1;
-        const uint32_t ph = ((j >> 1) & 1) ^ 1;
-        if (!bounded_wait(&bars->k_empty[s], ph, abort, p.status, kStatusTimeoutEmpty)) break;
-        mbar_expect_tx(&bars->k_full[s], L::kTileBytes);
-        load_rows<D>(sK + s * L::kTileBytes, &tmK, &bars->k_full[s], t.other * kTile, h, b);
-        if (!bounded_wait(&bars->v_empty[s], ph, abort, p.status, kStatusTimeoutEmpty)) break;
-        mbar_expect_tx(&bars->v_full[s], L::kTileBytes);
-        load_rows<D>(sV + s * L::kTileBytes, &tmV, &bars->v_full[s], t.other * kTile, h, b);
+    // ------------------------------------------------------ TMA producer ----
+    if (lane == 0) {
+      uint32_t it = 0;  // key tiles loaded so far (all items)
+      uint32_t qi = 0;  // query tiles loaded so far
+      bool ok = true;
+      for (int r = 0; r < rounds && ok; ++r) {
+        const int w = item_at(r);
+        if (w < 0) continue;
+        const int q_tile = item_tile(w), bh = w % BH;
+        const int b = bh / p.H, h = bh % p.H;
+        const TileRange range = tile_range(p.sched, q_tile, p.N, false);
+        const int n_tiles = range.end - range.begin;
+        if (n_tiles <= 0) continue;
+        const int qb = qi & 1;
+        if (!bounded_wait(&bars->q_empty[qb], ((qi >> 1) & 1) ^ 1, abort, p.status,
+                          kStatusTimeoutEmpty))
+          break;
+        mbar_expect_tx(&bars->q_full[qb], L::kTileBytes);
+        load_rows<D>(sQ + qb * L::kTileBytes, &tmQ, &bars->q_full[qb], q_tile * kTile, h, b);
+        ++qi;
+        for (int j = 0; j < n_tiles; ++j, ++it) {
+          const TileInfo t = tile_info(p.sched, range, j);
+          const int s = it & 1;
+          const uint32_t ph = ((it >> 1) & 1) ^ 1;
+          if (!bounded_wait(&bars->k_empty[s], ph, abort, p.status, kStatusTimeoutEmpty) ) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&bars->k_full[s], L::kTileBytes);
+          load_rows<D>(sK + s * L::kTileBytes, &tmK, &bars->k_full[s], t.other * kTile, h, b);
+          if (!bounded_wait(&bars->v_empty[s], ph, abort, p.status, kStatusTimeoutEmpty)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&bars->v_full[s], L::kTileBytes);
+          load_rows<D>(sV + s * L::kTileBytes, &tmV, &bars->v_full[s], t.other * kTile, h, b);
+        }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && n_tiles > 0) {
+    // -------------------------------------------------------- MMA issuer ----
+    if (lane == 0) {
       constexpr uint32_t idesc_qk = idesc_16bit(FP16, kTile, kTile, false, false);
       constexpr uint32_t idesc_pv = idesc_16bit(FP16, kTile, D, false, true);
-      const uint32_t q_addr = smem_u32(sQ);
-      auto issue_qk = [&](int j) -> bool {
-        const int s = j & 1;
-        if (!bounded_wait(&bars->k_full[s], (j >> 1) & 1, abort, p.status, kStatusTimeoutFull))
+      // Cursor of the score products, which run two key tiles ahead of P V and
+      // therefore cross into the next work item before the current one is done.
+      int qr = 0, qj = 0, qn = 0;  // round, tile within the item, tiles of the item
+      uint32_t q_it = 0, q_qi = 0;
+      auto seek = [&]() {  // first round at or after qr whose item has key tiles
+        qj = 0;
+        qn = 0;
+        for (; qr < rounds; ++qr) {
+          const int w = item_at(qr);
+          if (w < 0) continue;
+          const TileRange t = tile_range(p.sched, item_tile(w), p.N, false);
+          if (t.end - t.begin > 0) {
+            qn = t.end - t.begin;
+            return;
+          }
+        }
+      };
+      auto issue_qk = [&]() -> bool {
+        if (qn == 0) return true;  // no work item left
+        const int qb = q_qi & 1;
+        if (qj == 0 &&
+            !bounded_wait(&bars->q_full[qb], (q_qi >> 1) & 1, abort, p.status, kStatusTimeoutFull))
+          return false;
+        const int s = q_it & 1;
+        if (!bounded_wait(&bars->k_full[s], (q_it >> 1) & 1, abort, p.status, kStatusTimeoutFull))
           return false;
         tc_fence_after();
+        const uint32_t q_addr = smem_u32(sQ + qb * L::kTileBytes);
         const uint32_t k_addr = smem_u32(sK + s * L::kTileBytes);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)
@@ -420,124 +483,156 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                        idesc_qk, k != 0);
         umma_commit(&bars->k_empty[s]);
         umma_commit(&bars->s_full[s]);
+        ++q_it;
+        if (++qj == qn) {  // last score product of the item: its query tile is free
+          umma_commit(&bars->q_empty[qb]);
+          ++q_qi;
+          ++qr;
+          seek();
+        }
         return true;
       };
-      bool ok = bounded_wait(&bars->q_full, 0, abort, p.status, kStatusTimeoutFull);
-      if (ok) ok = issue_qk(0);
-      if (ok && n_tiles > 1) ok = issue_qk(1);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int pb = j % PB;
-        const int s = j & 1;
-        if (!bounded_wait(&bars->p_ready[pb], (j / PB) & 1, abort, p.status,
-                          kStatusTimeoutTmemFull) ||
-            !bounded_wait(&bars->v_full[s], (j >> 1) & 1, abort, p.status, kStatusTimeoutFull))
-          break;
-        tc_fence_after();
-        const uint32_t p_addr = smem_u32(sP + pb * L::kPBytes);
-        const uint32_t v_addr = smem_u32(sV + s * L::kTileBytes);
+      seek();
+      bool ok = issue_qk();
+      if (ok) ok = issue_qk();
+      uint32_t it = 0;
+      for (int r = 0; r < rounds && ok; ++r) {
+        const int w = item_at(r);
+        if (w < 0) continue;
+        const TileRange range = tile_range(p.sched, item_tile(w), p.N, false);
+        const int n_tiles = range.end - range.begin;
+        for (int j = 0; j < n_tiles && ok; ++j, ++it) {
+          const int pb = it % PB;
+          const int s = it & 1;
+          if (!bounded_wait(&bars->p_ready[pb], (it / PB) & 1, abort, p.status,
+                            kStatusTimeoutTmemFull) ||
+              !bounded_wait(&bars->v_full[s], (it >> 1) & 1, abort, p.status,
+                            kStatusTimeoutFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t p_addr = smem_u32(sP + pb * L::kPBytes);
+          const uint32_t v_addr = smem_u32(sV + s * L::kTileBytes);
 #pragma unroll
-        for (int k = 0; k < kTile / 16; ++k)
-          umma_bf16_ss(tO, desc_kmajor(p_addr, kTile, k), desc_mnmajor(v_addr, k), idesc_pv,
-                       (j | k) != 0);
-        umma_commit(&bars->v_empty[s]);
-        umma_commit(&bars->pv_done[pb]);
-        if (j + 2 < n_tiles) ok = issue_qk(j + 2);
+          for (int k = 0; k < kTile / 16; ++k)
+            umma_bf16_ss(tO, desc_kmajor(p_addr, kTile, k), desc_mnmajor(v_addr, k), idesc_pv,
+                         (j | k) != 0);
+          umma_commit(&bars->v_empty[s]);
+          umma_commit(&bars->pv_done[pb]);
+          // the score buffer of tile it + 2 is the one tile `it` just released
+          ok = issue_qk();
+        }
       }
     }
   } else {
     // ------------------------------------------------ softmax + epilogue ----
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
-    const int q = q_tile * kTile + row;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const float scale_log2 = p.scale * kLog2e;
-    float m_used = -INFINITY;
-    float l = 0.f;
+    uint32_t it = 0;
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const TileInfo t = tile_info(p.sched, range, j);
-      const int s = j & 1;
-      const int pb = j % PB;
-      if (!bounded_wait(&bars->s_full[s], (j >> 1) & 1, abort, p.status, kStatusTimeoutTmemFull)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      float x[kTile];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32f(tS + lane_base + s * kTile + c * 32, x + c * 32);
-      tmem_ld_wait();
-      const int k0 = t.other * kTile;
-      const bool ragged = (k0 + kTile > p.N) || (q_tile * kTile + kTile > p.N);
-      if (!t.full || ragged) {
-        const RowMask rm = row_mask_for_query(p.sched, q, k0, p.N);
-        apply_mask(x, rm, static_cast<uint32_t>(t.bitmap >> ((row >> 4) * 8)) & 0xffu);
-        if (p.sched.doc != nullptr) {
-          named_barrier_128();  // previous readers of the label tile are done
-          bars->col_doc[row] = k0 + row < p.N ? p.sched.doc[k0 + row] : -1;
-          named_barrier_128();
-          apply_doc_mask(x, bars->col_doc, q < p.N ? p.sched.doc[q] : -2);
-        }
-      }
-      // Row maximum of the raw scores; the positive scale preserves the order.
-      float mx = x[0];
-#pragma unroll
-      for (int c = 1; c < kTile; ++c) mx = fmaxf(mx, x[c]);
-      mx *= scale_log2;
-      // Lazy rescale: keep a stale maximum until it is off by more than 2^8.
-      const bool grow = mx > m_used + 8.0f;
-      if (__any_sync(0xffffffffu, grow)) {
-        if (j > 0) {
-          if (!bounded_wait(&bars->pv_done[(j - 1) % PB], ((j - 1) / PB) & 1, abort, p.status,
-                            kStatusTimeoutTmemFull)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const float alpha = grow ? fast_exp2(m_used - mx) : 1.0f;
-#pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            float o[32];
-            tmem_ld_32x32f(tO + lane_base + c * 32, o);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] *= alpha;
-            tmem_st_32x32(tO + lane_base + c * 32, o);
-          }
-          tmem_st_wait();
-          l *= alpha;
-        }
-        if (grow) m_used = mx;
-      }
-      uint32_t packed[64];
-      float sum = 0.f;
-      // A row that has seen no key yet keeps m_used = -inf; subtract 0 instead so
-      // masked scores (-inf) still map to probability 0 rather than NaN.
-      const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
-#pragma unroll
-      for (int c = 0; c < kTile; c += 2) {
-        const float p0 = fast_exp2(fmaf(x[c], scale_log2, neg_m));
-        const float p1 = fast_exp2(fmaf(x[c + 1], scale_log2, neg_m));
-        sum += p0 + p1;
-        packed[c >> 1] = pack2<FP16>(p0, p1);
-      }
-      l += sum;
-      if (j >= PB) {
-        if (!bounded_wait(&bars->pv_done[pb], ((j - PB) / PB) & 1, abort, p.status,
+    for (int r = 0; r < rounds && ok; ++r) {
+      const int w = item_at(r);
+      if (w < 0) continue;
+      const int q_tile = item_tile(w), bh = w % BH;
+      const int b = bh / p.H, h = bh % p.H;
+      const TileRange range = tile_range(p.sched, q_tile, p.N, false);
+      const int n_tiles = range.end - range.begin;
+      const int q = q_tile * kTile + row;
+      float m_used = -INFINITY;
+      float l = 0.f;
+      for (int j = 0; j < n_tiles && ok; ++j, ++it) {
+        const TileInfo t = tile_info(p.sched, range, j);
+        const int s = it & 1;
+        const int pb = it % PB;
+        if (!bounded_wait(&bars->s_full[s], (it >> 1) & 1, abort, p.status,
                           kStatusTimeoutTmemFull)) {
           ok = false;
           break;
         }
+        tc_fence_after();
+        float x[kTile];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld_32x32f(tS + lane_base + s * kTile + c * 32, x + c * 32);
+        tmem_ld_wait();
+        const int k0 = t.other * kTile;
+        const bool ragged = (k0 + kTile > p.N) || (q_tile * kTile + kTile > p.N);
+        if (!t.full || ragged) {
+          const RowMask rm = row_mask_for_query(p.sched, q, k0, p.N);
+          apply_mask(x, rm, static_cast<uint32_t>(t.bitmap >> ((row >> 4) * 8)) & 0xffu);
+          if (p.sched.doc != nullptr) {
+            named_barrier_128();  // previous readers of the label tile are done
+            bars->col_doc[row] = k0 + row < p.N ? p.sched.doc[k0 + row] : -1;
+            named_barrier_128();
+            apply_doc_mask(x, bars->col_doc, q < p.N ? p.sched.doc[q] : -2);
+          }
+        }
+        // Row maximum of the raw scores; the positive scale preserves the order.
+        // (eight independent chains: one 127-long dependent chain of max operations
+        // would cost its full latency on a warp that has its scheduler to itself)
+        float mx8[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) mx8[c] = x[c];
+#pragma unroll
+        for (int c = 8; c < kTile; ++c) mx8[c & 7] = fmaxf(mx8[c & 7], x[c]);
+        float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                         fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+        mx *= scale_log2;
+        // Lazy rescale: keep a stale maximum until it is off by more than 2^8.
+        const bool grow = mx > m_used + 8.0f;
+        if (__any_sync(0xffffffffu, grow)) {
+          if (j > 0) {
+            if (!bounded_wait(&bars->pv_done[(it - 1) % PB], ((it - 1) / PB) & 1, abort, p.status,
+                              kStatusTimeoutTmemFull)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const float alpha = grow ? fast_exp2(m_used - mx) : 1.0f;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              float o[32];
+              tmem_ld_32x32f(tO + lane_base + c * 32, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] *= alpha;
+              tmem_st_32x32(tO + lane_base + c * 32, o);
+            }
+            tmem_st_wait();
+            l *= alpha;
+          }
+          if (grow) m_used = mx;
+        }
+        uint32_t packed[64];
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};  // independent partial sums, same reason
+        // A row that has seen no key yet keeps m_used = -inf; subtract 0 instead so
+        // masked scores (-inf) still map to probability 0 rather than NaN.
+        const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
+#pragma unroll
+        for (int c = 0; c < kTile; c += 2) {
+          const float p0 = fast_exp2(fmaf(x[c], scale_log2, neg_m));
+          const float p1 = fast_exp2(fmaf(x[c + 1], scale_log2, neg_m));
+          sum4[(c >> 1) & 3] += p0 + p1;
+          packed[c >> 1] = pack2<FP16>(p0, p1);
+        }
+        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        // the P tile is free once the product that read it PB tiles ago is done
+        if (it >= PB && !bounded_wait(&bars->pv_done[pb], ((it - PB) / PB) & 1, abort, p.status,
+                                      kStatusTimeoutTmemFull)) {
+          ok = false;
+          break;
+        }
+        store_row_swizzled(sP + pb * L::kPBytes, row, packed);
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(&bars->p_ready[pb]);
       }
-      store_row_swizzled(sP + pb * L::kPBytes, row, packed);
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(&bars->p_ready[pb]);
-    }
-    if (ok && n_tiles > 0)
-      ok = bounded_wait(&bars->pv_done[(n_tiles - 1) % PB], ((n_tiles - 1) / PB) & 1, abort,
-                        p.status, kStatusTimeoutTmemFull);
-    if (ok) {
+      if (ok && n_tiles > 0)
+        ok = bounded_wait(&bars->pv_done[(it - 1) % PB], ((it - 1) / PB) & 1, abort, p.status,
+                          kStatusTimeoutTmemFull);
+      if (!ok) break;
       tc_fence_after();
       const float inv = l > 0.f ? 1.0f / l : 0.f;
       uint8_t* orow = static_cast<uint8_t*>(p.o) +
@@ -567,6 +662,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (q < p.N && p.lse != nullptr)
         p.lse[(static_cast<long>(b) * p.H + h) * p.N + q] =
             l > 0.f ? (m_used + log2f(l)) * kLn2 : -INFINITY;
+      // The accumulator is overwritten by the next item's first P V product, which
+      // waits for this warp's next p_ready arrival - i.e. after the reads above.
+      tc_fence_before();
     }
   }
   tc_fence_before();
@@ -587,7 +685,7 @@ struct BwdSmem {
   static constexpr int kPBytes = kTile * kTile * 2;
   static constexpr int kStages = (D == 64) ? 2 : 1;
   static constexpr int kBytes =
-      2 * kTileBytes + kStages * 2 * kTileBytes + 2 * kPBytes + 1024 + 2048 + 256;
+      2 * kTileBytes + kStages * 2 * kTileBytes + 2 * kPBytes + 1024 + 3072 + 256;
 };
 
 struct BwdBarriers {
@@ -623,9 +721,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
   uint8_t* sIn = sOwnB + L::kTileBytes;  // stages x (A, B)
   uint8_t* sP = sIn + L::kStages * 2 * L::kTileBytes;
   uint8_t* sDS = sP + L::kPBytes;
-  float* sStats = reinterpret_cast<float*>(sDS + L::kPBytes);  // -lse[128], delta[128]
-  int* sDoc = reinterpret_cast<int*>(sStats + 2 * kTile);       // labels of the streamed tile
-  BwdBarriers* bars = reinterpret_cast<BwdBarriers*>(reinterpret_cast<uint8_t*>(sStats) + 2048);
+  float* sStats = reinterpret_cast<float*>(sDS + L::kPBytes);  // 2 x (-lse[128], delta[128])
+  int* sDoc = reinterpret_cast<int*>(sStats + 4 * kTile);       // 2 x labels of a streamed tile
+  BwdBarriers* bars = reinterpret_cast<BwdBarriers*>(reinterpret_cast<uint8_t*>(sStats) + 3072);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_tiles = (p.N + kTile - 1) / kTile;
@@ -691,25 +789,38 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
       // shared P / dS tiles are already stored as two 64-column halves.
       constexpr uint32_t idesc_s = idesc_16bit(FP16, kTile, 64, false, false);
       constexpr uint32_t idesc_acc = idesc_16bit(FP16, kTile, D, false, true);
-      const uint32_t ownA = smem_u32(sOwnA), ownB = smem_u32(sOwnB);
-      const uint32_t p_addr = smem_u32(sP), ds_addr = smem_u32(sDS);
       const int halves = 2 * n_tiles;
+      // Descriptors are built once and stepped by constant offsets (see
+      // umma_desc_advance): per MMA the issuing thread then only adds and issues.
+      uint64_t own_a[D / 16], own_b[D / 16];
+#pragma unroll
+      for (int k = 0; k < D / 16; ++k) {
+        own_a[k] = desc_kmajor(smem_u32(sOwnA), kTile, k);
+        own_b[k] = desc_kmajor(smem_u32(sOwnB), kTile, k);
+      }
+      const uint64_t in_k0 = desc_kmajor(smem_u32(sIn), kTile, 0);   // streamed tile, K-major view
+      const uint64_t in_mn0 = desc_mnmajor(smem_u32(sIn), 0);        // same tile, MN-major view
+      const uint64_t p_k0 = desc_kmajor(smem_u32(sP), kTile, 0);
+      const uint64_t ds_k0 = desc_kmajor(smem_u32(sDS), kTile, 0);
       auto issue_scores = [&](int h) -> bool {
         const int j = h >> 1, hh = h & 1, s = j % ST;
         if (hh == 0 &&
             !bounded_wait(&bars->in_full[s], (j / ST) & 1, abort, p.status, kStatusTimeoutFull))
           return false;
         tc_fence_after();
-        const uint32_t inA = smem_u32(sIn + s * 2 * L::kTileBytes) + hh * 64 * 128;
-        const uint32_t inB = inA + L::kTileBytes;
+        // rows [64 hh, 64 hh + 64) of the streamed pair (A then B, kTileBytes apart)
+        const uint64_t in_a = umma_desc_advance(in_k0, s * 2 * L::kTileBytes + hh * 64 * 128);
+        const uint64_t in_b = umma_desc_advance(in_a, L::kTileBytes);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)  // S^T = K Q^T   or   S = Q K^T
-          umma_bf16_ss(tS + hh * 64, desc_kmajor(ownA, kTile, k), desc_kmajor(inA, kTile, k),
-                       idesc_s, k != 0);
+          umma_bf16_ss(tS + hh * 64, own_a[k],
+                       umma_desc_advance(in_a, (k >> 2) * (kTile * 128) + (k & 3) * 32), idesc_s,
+                       k != 0);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)  // dP^T = V dO^T  or  dP = dO V^T
-          umma_bf16_ss(tDP + hh * 64, desc_kmajor(ownB, kTile, k), desc_kmajor(inB, kTile, k),
-                       idesc_s, k != 0);
+          umma_bf16_ss(tDP + hh * 64, own_b[k],
+                       umma_desc_advance(in_b, (k >> 2) * (kTile * 128) + (k & 3) * 32), idesc_s,
+                       k != 0);
         umma_commit(&bars->sp_full[hh]);
         return true;
       };
@@ -727,24 +838,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
         if (!bounded_wait(&bars->pds_ready[hh], j & 1, abort, p.status, kStatusTimeoutTmemFull))
           break;
         tc_fence_after();
-        const uint32_t inA = smem_u32(sIn + s * 2 * L::kTileBytes);
-        const uint32_t inB = inA + L::kTileBytes;
-        const uint32_t p_half = p_addr + hh * (kTile * 128);
-        const uint32_t ds_half = ds_addr + hh * (kTile * 128);
+        // MN-major views of the streamed pair: 16 reduction rows per step, 2048 B apart
+        const uint64_t mn_a = umma_desc_advance(in_mn0, s * 2 * L::kTileBytes + hh * 4 * 2048);
+        const uint64_t mn_b = umma_desc_advance(mn_a, L::kTileBytes);
+        const uint64_t p_half = umma_desc_advance(p_k0, hh * (kTile * 128));
+        const uint64_t ds_half = umma_desc_advance(ds_k0, hh * (kTile * 128));
         if constexpr (KV_OWNED) {
 #pragma unroll
           for (int k = 0; k < 4; ++k)  // dV += P^T dO
-            umma_bf16_ss(tAcc0, desc_kmajor(p_half, kTile, k), desc_mnmajor(inB, hh * 4 + k),
-                         idesc_acc, (h | k) != 0);
+            umma_bf16_ss(tAcc0, umma_desc_advance(p_half, k * 32),
+                         umma_desc_advance(mn_b, k * 2048), idesc_acc, (h | k) != 0);
 #pragma unroll
           for (int k = 0; k < 4; ++k)  // dK += dS^T Q
-            umma_bf16_ss(tAcc1, desc_kmajor(ds_half, kTile, k), desc_mnmajor(inA, hh * 4 + k),
-                         idesc_acc, (h | k) != 0);
+            umma_bf16_ss(tAcc1, umma_desc_advance(ds_half, k * 32),
+                         umma_desc_advance(mn_a, k * 2048), idesc_acc, (h | k) != 0);
         } else {
 #pragma unroll
           for (int k = 0; k < 4; ++k)  // dQ += dS K
-            umma_bf16_ss(tAcc0, desc_kmajor(ds_half, kTile, k), desc_mnmajor(inA, hh * 4 + k),
-                         idesc_acc, (h | k) != 0);
+            umma_bf16_ss(tAcc0, umma_desc_advance(ds_half, k * 32),
+                         umma_desc_advance(mn_a, k * 2048), idesc_acc, (h | k) != 0);
         }
         if (hh == 1) umma_commit(&bars->in_empty[s]);
         umma_commit(&bars->acc_done[hh]);
@@ -790,6 +902,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
       }
     }
     bool ok = true;
+    float next_ls = 0.f, next_dl = 0.f;
+    if constexpr (KV_OWNED) {
+      if (part == 0 && n_tiles > 0) {
+        const int c0 = tile_info(p.sched, range, 0).other * kTile + row;
+        float ls = c0 < p.N ? p.lse[stat_base + c0] * kLog2e : INFINITY;
+        if (ls == -INFINITY) ls = INFINITY;
+        next_ls = -ls;
+        next_dl = c0 < p.N ? p.delta[stat_base + c0] : 0.f;
+      }
+    }
     // state of the current streamed tile, set up when its first half starts
     bool masked = false, use_doc = false;
     RowMask rm{0, 0u};
@@ -805,19 +927,31 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
         use_doc = masked && p.sched.doc != nullptr;
         if (KV_OWNED || use_doc) {
           // Per-column data of this tile: (negated) log-sum-exp and delta of the
-          // query columns for the key-owned kernel, document labels for both.
-          if (j > 0) named_barrier_bwd();  // previous tile's readers are done
+          // query columns for the key-owned kernel, document labels for both.  The
+          // key-owned statistics were fetched from global memory one tile ahead
+          // (next_ls / next_dl), so only the shared-memory hand-over is paid here;
+          // the table is double buffered by tile parity, which makes one barrier
+          // per tile enough (a buffer is rewritten two tiles after it was read, and
+          // every thread passes the barrier in between).
+          float* stats = sStats + (j & 1) * (2 * kTile);
           const int ci = other0 + row;
           if (part == 0) {
             if constexpr (KV_OWNED) {
-              float ls = ci < p.N ? p.lse[stat_base + ci] * kLog2e : INFINITY;
-              if (ls == -INFINITY) ls = INFINITY;
-              sStats[row] = -ls;
-              sStats[kTile + row] = ci < p.N ? p.delta[stat_base + ci] : 0.f;
+              stats[row] = next_ls;
+              stats[kTile + row] = next_dl;
             }
-            if (use_doc) sDoc[row] = ci < p.N ? p.sched.doc[ci] : -1;
+            if (use_doc) sDoc[(j & 1) * kTile + row] = ci < p.N ? p.sched.doc[ci] : -1;
           }
           named_barrier_bwd();
+          if constexpr (KV_OWNED) {
+            if (part == 0 && j + 1 < n_tiles) {  // statistics of the next streamed tile
+              const int cn = tile_info(p.sched, range, j + 1).other * kTile + row;
+              float ls = cn < p.N ? p.lse[stat_base + cn] * kLog2e : INFINITY;
+              if (ls == -INFINITY) ls = INFINITY;
+              next_ls = -ls;
+              next_dl = cn < p.N ? p.delta[stat_base + cn] : 0.f;
+            }
+          }
         }
         rm = RowMask{0, 0u};
         group_bits = 0xffu;
@@ -866,24 +1000,41 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
           }
           if (use_doc) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) sv[i] = sDoc[c * 32 + i] == my_doc ? sv[i] : -INFINITY;
+            for (int i = 0; i < 32; ++i)
+              sv[i] = sDoc[(j & 1) * kTile + c * 32 + i] == my_doc ? sv[i] : -INFINITY;
           }
         }
+        // Statistics of the 32 columns: the key-owned kernel reads them from the
+        // shared table (the same address for every lane, so 16-byte loads), the
+        // query-owned kernel has them in registers.
+        const float* col_ls = sStats + (j & 1) * (2 * kTile) + c * 32;
+        const float* col_dl = col_ls + kTile;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float pr[2], ds[2];
+        for (int i = 0; i < 32; i += 4) {
+          float nl[4], dl[4];
+          if constexpr (KV_OWNED) {
+            const float4 a = *reinterpret_cast<const float4*>(col_ls + i);
+            const float4 b = *reinterpret_cast<const float4*>(col_dl + i);
+            nl[0] = a.x; nl[1] = a.y; nl[2] = a.z; nl[3] = a.w;
+            dl[0] = b.x; dl[1] = b.y; dl[2] = b.z; dl[3] = b.w;
+          } else {
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int col = c * 32 + i + e;
-            const float neg_ls = KV_OWNED ? sStats[col] : -my_lse;
-            const float dl = KV_OWNED ? sStats[kTile + col] : my_delta;
+            for (int e = 0; e < 4; ++e) {
+              nl[e] = -my_lse;
+              dl[e] = my_delta;
+            }
+          }
+          float pr[4], ds[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
             // exp2(-inf) = 0 covers both masked scores and rows without keys.
-            const float prob = fast_exp2(fmaf(sv[i + e], scale_log2, neg_ls));
-            pr[e] = prob;
-            ds[e] = prob * (dp[i + e] - dl);
+            pr[e] = fast_exp2(fmaf(sv[i + e], scale_log2, nl[e]));
+            ds[e] = pr[e] * (dp[i + e] - dl[e]);
           }
           pp[i >> 1] = pack2<FP16>(pr[0], pr[1]);
+          pp[(i >> 1) + 1] = pack2<FP16>(pr[2], pr[3]);
           dd[i >> 1] = pack2<FP16>(ds[0], ds[1]);
+          dd[(i >> 1) + 1] = pack2<FP16>(ds[2], ds[3]);
         }
         if constexpr (KV_OWNED) store_chunk_swizzled(sP, row, c, pp);
         store_chunk_swizzled(sDS, row, c, dd);
@@ -999,6 +1150,17 @@ int make_map(CUtensorMap* map, const void* base, const SflAttnTensor& t, int B, 
   return make_tensormap_nd_b16(map, base, 4, dims, strides, box, 3);
 }
 
+int attn_sm_count() {
+  static int count = 0;
+  if (count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
+    if (count <= 0) count = 148;
+  }
+  return count;
+}
+
 bool strides_ok(const SflAttnTensor& t) {
   return t.ptr != nullptr && (reinterpret_cast<uintptr_t>(t.ptr) & 15) == 0 &&
          t.stride_t % 8 == 0 && t.stride_h % 8 == 0 && t.stride_b % 8 == 0;
@@ -1045,7 +1207,8 @@ extern "C" int sfl_attn_fwd(const SflAttnTensor* q, const SflAttnTensor* k, cons
   p.sched = to_sched(mask, false);
   p.o = o->ptr; p.o_sb = o->stride_b; p.o_sh = o->stride_h; p.o_st = o->stride_t;
   p.lse = lse; p.is_fp16 = is_fp16; p.status = status;
-  dim3 grid((N + kTile - 1) / kTile, B * H);
+  const int items = ((N + kTile - 1) / kTile) * B * H;
+  dim3 grid(items < attn_sm_count() ? items : attn_sm_count());
 #define SFL_FWD(D_, F_)                                                                   \
   {                                                                                       \
     auto kern = attn_fwd_kernel<D_, F_>;                                                  \

@@ -286,6 +286,15 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr, uint32_t 
   return d;
 }
 
+// The start address is the low 14-bit field of the descriptor (in 16-byte units), so a
+// tile that lies `bytes` further on in shared memory has descriptor + (bytes >> 4);
+// nothing carries out of the field while addresses stay below 256 KB.  Building one
+// descriptor per tile and stepping it keeps the single MMA-issuing thread - whose
+// instruction rate bounds small-tile kernels - off the 64-bit assembly work.
+__device__ __forceinline__ uint64_t umma_desc_advance(uint64_t desc, uint32_t bytes) {
+  return desc + (bytes >> 4);
+}
+
 // Instruction descriptor: bf16 x bf16 -> fp32, dense.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n, bool a_mn_major,
                                                        bool b_mn_major) {
