@@ -63,9 +63,12 @@ def train_config_dict(steps: int, checkpointing: str) -> dict:
 class ClockSampler:
     """Samples SM clock and throttle reasons while the timed region runs (reads only).
 
-    NVML is polled from a thread every 10 ms, so even a timed region of a few
-    tens of milliseconds gets samples; ``nvidia-smi -lms`` is the fallback when
-    the NVML binding cannot be loaded.
+    NVML is polled from a thread every 25 ms, so even a timed region of a tenth of
+    a second gets samples; ``nvidia-smi -lms`` is the fallback when the NVML
+    binding cannot be loaded.  Only rank 0 samples (``enabled``): management
+    queries from eight processes at once take driver locks that kernel launches
+    also need, which slowed the launch-heavy sharded modes inside the timed
+    region.
     """
 
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
@@ -73,8 +76,8 @@ class ClockSampler:
              "clocks_event_reasons.sw_power_cap")
     NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
-    def __init__(self, index: int, uuid: str | None = None):
-        self.index, self.uuid = index, uuid
+    def __init__(self, index: int, uuid: str | None = None, enabled: bool = True):
+        self.index, self.uuid, self.enabled = index, uuid, enabled
         self.samples, self.process, self.thread = [], None, None
         self.stop = threading.Event()
 
@@ -102,9 +105,11 @@ class ClockSampler:
                                     + ["Active" if mask & bit else "Not Active" for bit in bits])
             except nvml.NVMLError:
                 pass
-            self.stop.wait(0.01)
+            self.stop.wait(0.025)
 
     def __enter__(self):
+        if not self.enabled:
+            return self
         try:
             nvml, handle = self._nvml_handle()
             self.thread = threading.Thread(target=self._poll_nvml, args=(nvml, handle), daemon=True)
@@ -235,7 +240,7 @@ def run_ours(args) -> None:
     check_status(device)
     launches_before = kernel_lib.launch_count()
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank, device_uuid(local_rank)) as clocks:
+    with ClockSampler(local_rank, device_uuid(local_rank), enabled=rank == 0) as clocks:
         begin.record()
         for step in range(args.steps):
             set_lr(args.warmup + step)
@@ -327,7 +332,7 @@ def run_reference(args) -> None:
                     break
                 time.sleep(0.1)
             workdir = Path(marker.read_text())
-    with ClockSampler(env_ranks()[2], device_uuid(env_ranks()[2])) as clocks:
+    with ClockSampler(env_ranks()[2], device_uuid(env_ranks()[2]), enabled=rank == 0) as clocks:
         summary = ref_runner.run(config, workdir, mode=mode, global_batch_size=GLOBAL_BATCH,
                                  microbatch_size=MICROBATCH, warmup_steps=args.warmup,
                                  sync_policy="last", bucket_cap_mb=25.0)
