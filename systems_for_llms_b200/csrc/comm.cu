@@ -335,12 +335,10 @@ struct ShardedAdamParams {
   const float* ok;     // skip update when 0
 };
 
-__global__ void __launch_bounds__(256)
-adamw_allgather_kernel(const CommView params, const CommView shadows, ShardedAdamParams a,
-                       int slot, uint32_t epoch, int* status) {
-  // Peers must have finished reading the old parameters (their forward/backward
-  // is complete when they reach this kernel), hence the ready barrier.
-  if (!ready_barrier(params, slot, epoch, status)) return;
+// AdamW on this rank's slice of one range, results stored into every peer.
+__device__ __forceinline__ void adamw_allgather_range(const CommView& params,
+                                                      const CommView& shadows,
+                                                      const ShardedAdamParams& a) {
   long begin, end;
   slice_of(a.count, params.world, params.rank, &begin, &end);
   const bool apply = a.ok == nullptr || *a.ok != 0.0f;
@@ -381,6 +379,40 @@ adamw_allgather_kernel(const CommView params, const CommView shadows, ShardedAda
       st_peer_f4(reinterpret_cast<float*>(params.data[p]) + elem, p4);
       st_peer_u2(reinterpret_cast<__nv_bfloat16*>(shadows.data[p]) + elem, sh);
     }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+adamw_allgather_kernel(const CommView params, const CommView shadows, ShardedAdamParams a,
+                       int slot, uint32_t epoch, int* status) {
+  // Peers must have finished reading the old parameters (their forward/backward
+  // is complete when they reach this kernel), hence the ready barrier.
+  if (!ready_barrier(params, slot, epoch, status)) return;
+  adamw_allgather_range(params, shadows, a);
+  done_barrier(params, slot, epoch, status);
+}
+
+// The same update over a table of ranges (one per gradient bucket) between a single
+// pair of barriers: launching and synchronising once per bucket costs more than the
+// update itself when eight GPUs each own an eighth of a 25 MB bucket.
+// ranges[3 r .. 3 r + 2] = {element offset, element count, offset of this rank's
+// slice inside grad / m / v}.
+__global__ void __launch_bounds__(256)
+adamw_allgather_ranges_kernel(const CommView params, const CommView shadows,
+                              ShardedAdamParams a, const long* __restrict__ ranges, int num_ranges,
+                              int slot, uint32_t epoch, int* status) {
+  if (!ready_barrier(params, slot, epoch, status)) return;
+  const float* grad = a.grad;
+  float* m = a.m;
+  float* v = a.v;
+  for (int r = 0; r < num_ranges; ++r) {
+    a.offset = ranges[3 * r];
+    a.count = ranges[3 * r + 1];
+    const long shard = ranges[3 * r + 2];
+    a.grad = grad + shard;
+    a.m = m + shard;
+    a.v = v + shard;
+    adamw_allgather_range(params, shadows, a);
   }
   done_barrier(params, slot, epoch, status);
 }
@@ -635,6 +667,21 @@ extern "C" int sfl_adamw_allgather(const SflComm* comm, long offset, long count,
   ctas = clamp_ctas(ctas);
   adamw_allgather_kernel<<<ctas, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       to_view(comm, 0), to_view(comm, 1), a, slot, epoch, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int sfl_adamw_allgather_ranges(const SflComm* comm, const long* ranges, int num_ranges,
+                                          const float* grad, float* m, float* v, float lr,
+                                          float beta1, float beta2, float eps, float wd,
+                                          float bias1, float bias2, const float* coef,
+                                          const float* ok, int slot, unsigned epoch, int ctas,
+                                          int* status, void* stream) {
+  if (comm == nullptr || comm->world < 1 || comm->world > kMaxPeers) return -2;
+  if (ranges == nullptr || num_ranges <= 0 || slot < 0 || slot >= kSlots) return -2;
+  ShardedAdamParams a{0, 0, grad, m, v, lr, beta1, beta2, eps, wd, bias1, sqrtf(bias2), coef, ok};
+  ctas = clamp_ctas(ctas);
+  adamw_allgather_ranges_kernel<<<ctas, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      to_view(comm, 0), to_view(comm, 1), a, ranges, num_ranges, slot, epoch, status);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -239,6 +239,15 @@ int sfl_adamw_allgather(const SflComm* comm, long offset, long count, const floa
                         float* v, float lr, float beta1, float beta2, float eps, float wd,
                         float bias1, float bias2, const float* coef, const float* ok, int slot,
                         unsigned epoch, int ctas, int* status, void* stream);
+/* The same update for a table of ranges in one launch (one barrier pair):
+ * ranges (device memory) holds {element offset, element count, offset of this
+ * rank's slice inside grad / m / v} per range; counts and offsets are multiples
+ * of four elements. */
+int sfl_adamw_allgather_ranges(const SflComm* comm, const long* ranges, int num_ranges,
+                               const float* grad, float* m, float* v, float lr, float beta1,
+                               float beta2, float eps, float wd, float bias1, float bias2,
+                               const float* coef, const float* ok, int slot, unsigned epoch,
+                               int ctas, int* status, void* stream);
 /* Pull chunk r (chunk_bytes at offset_bytes + r*chunk_bytes) from every peer r. */
 int sfl_allgather_bytes(const SflComm* comm, long offset_bytes, long chunk_bytes, int slot,
                         unsigned epoch, int ctas, int* status, void* stream);

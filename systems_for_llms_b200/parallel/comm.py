@@ -47,6 +47,8 @@ for _name, _args in {
     "sfl_comm_norm_finalize": [_C, _P, c_int, c_int, c_float, _P, _P, _P],
     "sfl_adamw_allgather": [_C, c_long, c_long, _P, _P, _P, c_float, c_float, c_float, c_float,
                             c_float, c_float, c_float, _P, _P, c_int, c_uint, c_int, _P, _P],
+    "sfl_adamw_allgather_ranges": [_C, _P, c_int, _P, _P, _P, c_float, c_float, c_float, c_float,
+                                   c_float, c_float, c_float, _P, _P, c_int, c_uint, c_int, _P, _P],
     "sfl_allgather_bytes": [_C, c_long, c_long, c_int, c_uint, c_int, _P, _P],
     "sfl_allgather_into": [_C, c_long, c_long, _P, c_int, c_uint, c_int, _P, _P],
     "sfl_reduce_rows_resid": [_C, c_long, c_long, _P, c_long, c_int, c_int, c_uint, c_int, _P, _P],
@@ -203,6 +205,28 @@ class PeerComm:
             1.0 - beta1 ** step, 1.0 - beta2 ** step, _lib.ptr(coef), _lib.ptr(ok), slot,
             self.next_epoch(slot), self.ctas, self.status.data_ptr(), _lib.stream_ptr())
         _lib.check(code, "sfl_adamw_allgather")
+
+    def adamw_allgather_ranges(self, params: SymmetricBuffer, shadows: SymmetricBuffer,
+                               ranges: torch.Tensor, grad: torch.Tensor, exp_avg: torch.Tensor,
+                               exp_avg_sq: torch.Tensor, *, step: int, lr: float, beta1: float,
+                               beta2: float, eps: float, weight_decay: float,
+                               coef: torch.Tensor | None, ok: torch.Tensor | None,
+                               slot: int) -> None:
+        """Sharded AdamW + parameter all-gather for every bucket range in one launch.
+
+        ``ranges`` is an int64 device tensor ``[n, 3]`` of (element offset, element
+        count, offset of this rank's slice inside ``grad`` / ``exp_avg`` /
+        ``exp_avg_sq``).
+        """
+        if ranges.dtype != torch.int64 or ranges.dim() != 2 or ranges.shape[1] != 3 \
+                or not ranges.is_contiguous():
+            raise ValueError("ranges must be a contiguous int64 [n, 3] tensor")
+        code = _lib.lib().sfl_adamw_allgather_ranges(
+            ctypes.byref(self.struct(params, shadows)), ranges.data_ptr(), ranges.shape[0],
+            grad.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr(), lr, beta1, beta2, eps,
+            weight_decay, 1.0 - beta1 ** step, 1.0 - beta2 ** step, _lib.ptr(coef), _lib.ptr(ok),
+            slot, self.next_epoch(slot), self.ctas, self.status.data_ptr(), _lib.stream_ptr())
+        _lib.check(code, "sfl_adamw_allgather_ranges")
 
     def allgather_bytes(self, buffer: SymmetricBuffer, offset_bytes: int, chunk_bytes: int,
                         slot: int) -> None:

@@ -233,17 +233,21 @@ class ShardedAdamW:
         beta1, beta2 = group["betas"]
         engine.sync_shadow()
         ranges = state["ranges"]
-        # One launch per bucket range keeps slices aligned with the reduce-scatter.
-        for index, (begin, end) in enumerate(ranges):
-            offset = state["shard_offsets"][index]
-            length = ddp._slice_len(begin, end)
-            comm.adamw_allgather(
-                flat["params"], flat["shadows"], begin, end - begin,
-                state["shard"][offset:offset + length], flat["exp_avg"][offset:offset + length],
-                flat["exp_avg_sq"][offset:offset + length], step=flat["step"], lr=group["lr"],
-                beta1=beta1, beta2=beta2, eps=group.get("eps", 1e-8),
-                weight_decay=group["weight_decay"], coef=stats[1:2], ok=stats[2:3],
-                slot=comm.slots - 1 - (index % 4))
+        # Every bucket range in one launch; the table keeps each range's slice
+        # aligned with what the reduce-scatter left in the shard buffer.
+        table = flat.get("range_table")
+        if table is None:
+            rows = [(begin, end - begin, state["shard_offsets"][index])
+                    for index, (begin, end) in enumerate(ranges)]
+            if any(value % 4 for row in rows for value in row):
+                raise ValueError("bucket ranges must be multiples of four elements")
+            table = torch.tensor(rows, dtype=torch.int64, device=state["shard"].device)
+            flat["range_table"] = table
+        comm.adamw_allgather_ranges(
+            flat["params"], flat["shadows"], table, state["shard"], flat["exp_avg"],
+            flat["exp_avg_sq"], step=flat["step"], lr=group["lr"], beta1=beta1, beta2=beta2,
+            eps=group.get("eps", 1e-8), weight_decay=group["weight_decay"], coef=stats[1:2],
+            ok=stats[2:3], slot=comm.slots - 1)
         engine.mark_shadow_current()
 
     def close(self) -> None:
