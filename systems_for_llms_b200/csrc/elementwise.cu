@@ -536,3 +536,14 @@ extern "C" int sfl_embedding_fwd(const float* weight, const int64_t* ids, float*
 }
 
 extern "C" const char* sfl_version(void) { return "sfl_b200 sm_100a"; }
+
+// sizeof of every structure that crosses the C interface, in the order of the
+// enum below, so a binding can verify its mirrors field for field.
+extern "C" int sfl_struct_sizes(int* sizes, int capacity) {
+  const int values[] = {static_cast<int>(sizeof(SflGemmEpilogue)), static_cast<int>(sizeof(SflWgradProblem)),
+                        static_cast<int>(sizeof(SflAttnTensor)), static_cast<int>(sizeof(SflAttnMask)),
+                        static_cast<int>(sizeof(SflComm)), static_cast<int>(sizeof(SflBlockArgs))};
+  const int count = static_cast<int>(sizeof(values) / sizeof(values[0]));
+  for (int i = 0; i < count && i < capacity; ++i) sizes[i] = values[i];
+  return count;
+}

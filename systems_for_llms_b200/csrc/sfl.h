@@ -274,6 +274,10 @@ int sfl_embedding_fwd(const float* weight, const int64_t* ids, float* out, int r
                       int vocab, void* stream);
 /* Library build tag, for diagnostics. */
 const char* sfl_version(void);
+/* Writes sizeof(SflGemmEpilogue), sizeof(SflWgradProblem), sizeof(SflAttnTensor),
+ * sizeof(SflAttnMask), sizeof(SflComm), sizeof(SflBlockArgs) and returns how many
+ * there are; bindings compare them with their own mirrors. */
+int sfl_struct_sizes(int* sizes, int capacity);
 
 /* ------------------------------------------------------ transformer block -- */
 /* One pre-norm block (RMSNorm -> fused QKV + RoPE -> causal attention -> output

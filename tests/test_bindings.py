@@ -1,0 +1,49 @@
+"""The ctypes mirrors of the library's C structures must match the compiled layout."""
+
+import ctypes
+
+import pytest
+
+from systems_for_llms_b200.ops import build as builder
+
+
+@pytest.fixture(scope="module")
+def library():
+    from systems_for_llms_b200.ops import lib
+    try:
+        builder.build()
+        return lib.lib()
+    except Exception as error:      # no CUDA toolkit on this machine
+        pytest.skip(f"kernel library unavailable: {error}")
+
+
+def test_struct_sizes_match_the_compiled_library(library):
+    from systems_for_llms_b200.attention.flash import AttnMask, AttnTensor
+    from systems_for_llms_b200.ops.lib import BlockArgs, GemmEpilogue, WgradProblem
+    from systems_for_llms_b200.parallel.comm import CommStruct
+    handle = library._handle
+    handle.sfl_struct_sizes.argtypes = [ctypes.POINTER(ctypes.c_int), ctypes.c_int]
+    handle.sfl_struct_sizes.restype = ctypes.c_int
+    sizes = (ctypes.c_int * 8)()
+    count = handle.sfl_struct_sizes(sizes, 8)
+    mirrors = [GemmEpilogue, WgradProblem, AttnTensor, AttnMask, CommStruct, BlockArgs]
+    assert count == len(mirrors)
+    assert [ctypes.sizeof(m) for m in mirrors] == list(sizes)[:count]
+
+
+def test_block_runner_rejects_bad_shapes_without_a_gpu(library):
+    from systems_for_llms_b200.ops.lib import BlockArgs
+    args = BlockArgs()
+    assert library.sfl_block_saved_bytes(ctypes.byref(args)) == -1       # all zero
+    args.batch, args.seq_len, args.d_model, args.heads, args.head_dim, args.d_ff = 4, 1024, 1024, 16, 64, 2752
+    saved = library.sfl_block_saved_bytes(ctypes.byref(args))
+    scratch = library.sfl_block_scratch_bytes(ctypes.byref(args))
+    tokens = 4 * 1024
+    # h1, qkv, attn, h2, a13, g in bf16; x_mid in fp32; statistics
+    expected = tokens * 2 * (1024 + 3072 + 1024 + 1024 + 2 * 2752 + 2752) + tokens * 1024 * 4
+    statistics = 4 * 16 * 1024 * 4 + 2 * tokens * 4        # log-sum-exp, two 1/rms vectors
+    assert expected + statistics <= saved <= expected + statistics + 16 * 256
+    assert scratch > tokens * 2 * (2 * 2752 + 3 * 1024)
+    args.head_dim = 48                                                     # unsupported width
+    assert library.sfl_block_saved_bytes(ctypes.byref(args)) == -1
+    assert library.sfl_block_forward(ctypes.byref(args), None) == -2     # refused before any launch
