@@ -5,6 +5,7 @@
     python -m systems_for_llms_b200.ops.microbench elementwise # norms, loss, optimizer
     python -m systems_for_llms_b200.ops.microbench step        # per-kernel table of one step
     python -m systems_for_llms_b200.ops.microbench once NAME   # a few launches of one op
+    python -m systems_for_llms_b200.ops.microbench mma         # tcgen05.mma issue-rate test
 
 Each timing is the median of CUDA-event measurements with a 256 MB buffer
 written between launches, so operands come from HBM rather than from a warm L2.
@@ -234,16 +235,35 @@ def step_table(steps: int = 3) -> dict:
                         for e in events]}
 
 
+def mma_issue_rate() -> str:
+    """Compile ops/mma_issue_rate.cu for sm_100a into a temporary directory and run it."""
+    import subprocess
+    import tempfile
+
+    from . import build as builder
+    source = Path(__file__).with_name("mma_issue_rate.cu")
+    with tempfile.TemporaryDirectory() as scratch:
+        binary = Path(scratch) / "mma_issue_rate"
+        subprocess.run(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17",
+                        "--expt-relaxed-constexpr", "-I", str(builder.CSRC), "-o", str(binary),
+                        str(source)], check=True)
+        return subprocess.run([str(binary)], check=True, capture_output=True, text=True,
+                              timeout=120).stdout
+
+
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__,
                                      formatter_class=argparse.RawDescriptionHelpFormatter)
-    parser.add_argument("what", choices=[*SUITES, "step", "once"])
+    parser.add_argument("what", choices=[*SUITES, "step", "once", "mma"])
     parser.add_argument("name", nargs="?", help="operation for 'once' (e.g. w13_swiglu, attn_bwd)")
     parser.add_argument("--repeat", type=int, default=3)
     parser.add_argument("--json", action="store_true")
     args = parser.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("a CUDA GPU is required")
+    if args.what == "mma":
+        print(mma_issue_rate(), end="")
+        return
     if args.what == "once":
         from .gemm import check_status
         for suite in SUITES.values():
