@@ -11,7 +11,9 @@
 // The arithmetic is that of the reference block (src/llmlab/model/transformer.py:
 // 33-47: x + attn(norm(x)), then x + ffn(norm(x))) with the epilogue fusions of
 // gemm.cu; gradients follow models/fused.py:block_backward, which remains the
-// implementation for tensor-parallel engines.
+// implementation for engines the runner does not cover.  Under tensor
+// parallelism (SflBlockArgs::tp_pool) the four products whose reduction dimension
+// is sharded are issued as GEMM + all-reduce in one kernel (sfl_gemm_tp_reduce).
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -144,12 +146,30 @@ extern "C" long sfl_block_scratch_bytes(const SflBlockArgs* a) {
   return carve_scratch(dims_of(*a), nullptr).bytes;
 }
 
+namespace {
+
+// Local base of a fused product's result buffer.
+uint8_t* tp_local(const SflTpFuse* t) {
+  return t == nullptr || t->rank < 0 || t->rank >= 8 ? nullptr
+                                                     : static_cast<uint8_t*>(t->out[t->rank]);
+}
+
+}  // namespace
+
 extern "C" int sfl_block_forward(const SflBlockArgs* a, void* stream) {
-  if (a == nullptr || !shape_ok(*a) || a->x == nullptr || a->x_out == nullptr ||
-      a->saved == nullptr || a->mask == nullptr)
+  if (a == nullptr || !shape_ok(*a) || a->x == nullptr || a->saved == nullptr ||
+      a->mask == nullptr)
     return -2;
+  const bool tp = a->tp_pool != nullptr;
+  if (!tp && a->x_out == nullptr) return -2;
+  if (tp && tp_local(a->tp_pool) == nullptr) return -2;
   const Dims s = dims_of(*a);
-  const Saved v = carve_saved(s, a->saved);
+  Saved v = carve_saved(s, a->saved);
+  float* x_out = a->x_out;
+  if (tp) {
+    v.x_mid = tp_local(a->tp_pool) + a->tp_off_mid;
+    x_out = reinterpret_cast<float*>(tp_local(a->tp_pool) + a->tp_off_out);
+  }
   const int M = static_cast<int>(s.M);
   const int d = static_cast<int>(s.d), aw = static_cast<int>(s.aw), dff = static_cast<int>(s.dff);
 
@@ -169,10 +189,16 @@ extern "C" int sfl_block_forward(const SflBlockArgs* a, void* stream) {
   const SflAttnTensor o = head_view(v.attn, 0, s.aw, s);
   SFL_TRY(sfl_attn_fwd(&q, &k, &vv, &o, reinterpret_cast<float*>(v.lse), s.B, s.H, s.T, s.dk,
                        a->attn_scale, a->mask, 0, a->status, stream));
-  SflGemmEpilogue resid = epilogue(kResid, v.x_mid, s.d, a->status);
-  resid.aux = a->x;
-  resid.ldaux = s.d;
-  SFL_TRY(sfl_gemm_bf16(v.attn, s.aw, 0, a->wo, s.aw, 0, M, d, aw, &resid, 0, 0, stream));
+  if (tp) {
+    SFL_TRY(sfl_gemm_tp_reduce(v.attn, s.aw, a->wo, s.aw, 0, M, d, aw, a->tp_pool, a->tp_off_mid, 0,
+                               a->x, s.d, a->tp_slot[0], a->tp_epoch[0], a->tp_tile_epoch[0],
+                               a->status, stream));
+  } else {
+    SflGemmEpilogue resid = epilogue(kResid, v.x_mid, s.d, a->status);
+    resid.aux = a->x;
+    resid.ldaux = s.d;
+    SFL_TRY(sfl_gemm_bf16(v.attn, s.aw, 0, a->wo, s.aw, 0, M, d, aw, &resid, 0, 0, stream));
+  }
 
   // feed-forward half: x_out = x_mid + W2 (silu(W1 h) * W3 h), h = norm(x_mid)
   SFL_TRY(sfl_rmsnorm_fwd(reinterpret_cast<const float*>(v.x_mid), a->norm2, v.h2,
@@ -183,10 +209,16 @@ extern "C" int sfl_block_forward(const SflBlockArgs* a, void* stream) {
   gate.dual_offset = dff;
   gate.dual_rows = 2 * dff;
   SFL_TRY(sfl_gemm_bf16(v.h2, s.d, 0, a->w13, s.d, 0, M, dff, d, &gate, 0, 0, stream));
-  SflGemmEpilogue out = epilogue(kResid, a->x_out, s.d, a->status);
-  out.aux = v.x_mid;
-  out.ldaux = s.d;
-  SFL_TRY(sfl_gemm_bf16(v.g, s.dff, 0, a->w2, s.dff, 0, M, d, dff, &out, 0, 0, stream));
+  if (tp) {
+    SFL_TRY(sfl_gemm_tp_reduce(v.g, s.dff, a->w2, s.dff, 0, M, d, dff, a->tp_pool, a->tp_off_out, 0,
+                               reinterpret_cast<const float*>(v.x_mid), s.d, a->tp_slot[1],
+                               a->tp_epoch[1], a->tp_tile_epoch[1], a->status, stream));
+  } else {
+    SflGemmEpilogue out = epilogue(kResid, x_out, s.d, a->status);
+    out.aux = v.x_mid;
+    out.ldaux = s.d;
+    SFL_TRY(sfl_gemm_bf16(v.g, s.dff, 0, a->w2, s.dff, 0, M, d, dff, &out, 0, 0, stream));
+  }
   return 0;
 }
 
@@ -197,9 +229,15 @@ extern "C" int sfl_block_backward(const SflBlockArgs* a, void* stream) {
       a->g_w13 == nullptr || a->g_w2 == nullptr || a->g_norm1 == nullptr ||
       a->g_norm2 == nullptr)
     return -2;
+  const bool tp = a->tp_pool != nullptr;
+  if (tp && (tp_local(a->tp_pool) == nullptr || tp_local(a->tp_small) == nullptr)) return -2;
   const Dims s = dims_of(*a);
-  const Saved v = carve_saved(s, a->saved);
-  const Scratch t = carve_scratch(s, a->scratch);
+  Saved v = carve_saved(s, a->saved);
+  Scratch t = carve_scratch(s, a->scratch);
+  if (tp) {
+    v.x_mid = tp_local(a->tp_pool) + a->tp_off_mid;
+    t.dh2 = t.dh1 = tp_local(a->tp_small);  // used one after the other
+  }
   const int M = static_cast<int>(s.M);
   const int d = static_cast<int>(s.d), aw = static_cast<int>(s.aw), dff = static_cast<int>(s.dff);
   const int blocks = sfl_rmsnorm_bwd_blocks(M);
@@ -217,7 +255,14 @@ extern "C" int sfl_block_backward(const SflBlockArgs* a, void* stream) {
   act.ldaux = 2 * s.dff;
   SFL_TRY(sfl_gemm_bf16(dres_bf16, s.d, 0, a->w2, s.dff, 1, M, dff, d, &act, 0, 0, stream));
   SflGemmEpilogue plain = epilogue(kBf16, t.dh2, s.d, a->status);
-  SFL_TRY(sfl_gemm_bf16(t.d13, 2 * s.dff, 0, a->w13, s.d, 1, M, d, 2 * dff, &plain, 0, 0, stream));
+  if (tp) {
+    SFL_TRY(sfl_gemm_tp_reduce(t.d13, 2 * s.dff, a->w13, s.d, 1, M, d, 2 * dff, a->tp_small, 0, 1,
+                               nullptr, 0, a->tp_slot[0], a->tp_epoch[0], a->tp_tile_epoch[0],
+                               a->status, stream));
+  } else {
+    SFL_TRY(sfl_gemm_bf16(t.d13, 2 * s.dff, 0, a->w13, s.d, 1, M, d, 2 * dff, &plain, 0, 0,
+                          stream));
+  }
   SFL_TRY(sfl_rmsnorm_bwd(t.dh2, reinterpret_cast<const float*>(v.x_mid), a->norm2,
                           reinterpret_cast<const float*>(v.rstd2), a->d_out,
                           reinterpret_cast<float*>(t.dres2), t.dres2_bf16, partial, M, d, stream));
@@ -237,8 +282,15 @@ extern "C" int sfl_block_backward(const SflBlockArgs* a, void* stream) {
   SFL_TRY(sfl_attn_bwd(&q, &k, &vv, &o, &d_o, reinterpret_cast<const float*>(v.lse),
                        reinterpret_cast<float*>(t.delta), &dq, &dk, &dv, s.B, s.H, s.T, s.dk,
                        a->attn_scale, a->mask, 0, a->status, a->rope_cos, a->rope_sin, stream));
-  plain = epilogue(kBf16, t.dh1, s.d, a->status);
-  SFL_TRY(sfl_gemm_bf16(t.dqkv, 3 * s.aw, 0, a->wqkv, s.d, 1, M, d, 3 * aw, &plain, 0, 0, stream));
+  if (tp) {
+    SFL_TRY(sfl_gemm_tp_reduce(t.dqkv, 3 * s.aw, a->wqkv, s.d, 1, M, d, 3 * aw, a->tp_small, 0, 1,
+                               nullptr, 0, a->tp_slot[1], a->tp_epoch[1], a->tp_tile_epoch[1],
+                               a->status, stream));
+  } else {
+    plain = epilogue(kBf16, t.dh1, s.d, a->status);
+    SFL_TRY(sfl_gemm_bf16(t.dqkv, 3 * s.aw, 0, a->wqkv, s.d, 1, M, d, 3 * aw, &plain, 0, 0,
+                          stream));
+  }
 
   // ---- the four weight gradients as one grouped launch
   SflWgradProblem w[4] = {

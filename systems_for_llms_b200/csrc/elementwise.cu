@@ -542,7 +542,8 @@ extern "C" const char* sfl_version(void) { return "sfl_b200 sm_100a"; }
 extern "C" int sfl_struct_sizes(int* sizes, int capacity) {
   const int values[] = {static_cast<int>(sizeof(SflGemmEpilogue)), static_cast<int>(sizeof(SflWgradProblem)),
                         static_cast<int>(sizeof(SflAttnTensor)), static_cast<int>(sizeof(SflAttnMask)),
-                        static_cast<int>(sizeof(SflComm)), static_cast<int>(sizeof(SflBlockArgs))};
+                        static_cast<int>(sizeof(SflComm)), static_cast<int>(sizeof(SflBlockArgs)),
+                        static_cast<int>(sizeof(SflTpFuse))};
   const int count = static_cast<int>(sizeof(values) / sizeof(values[0]));
   for (int i = 0; i < count && i < capacity; ++i) sizes[i] = values[i];
   return count;

@@ -45,6 +45,7 @@
 #include <mutex>
 #include <tuple>
 
+#include "comm.cuh"
 #include "launch.cuh"
 #include "ptx.cuh"
 #include "sfl.h"
@@ -1093,6 +1094,402 @@ wgrad_grouped_kernel(const __grid_constant__ GroupedMaps maps,
 }
 
 // ------------------------------------------------------------------ host ----
+// --------------------------------- GEMM fused with its all-reduce (tensor parallel) ----
+// Under tensor parallelism the output projection and the down projection (forward)
+// and the input gradients of the column-parallel layers (backward) are products
+// whose reduction dimension is split over the ranks: every rank holds a partial
+// [M, N] result and all of them need the sum (the reference all-reduces after
+// F.linear, distributed/llmdist/tensor_parallel.py).  This kernel is the GEMM and
+// that all-reduce in one launch, tile by tile over NVLink peer memory:
+//
+//   * the 128-row tile strips are owned round-robin by the ranks;
+//   * a CTA that finishes a tile owned by a peer converts the accumulator to bf16
+//     and stores it straight into that peer's staging buffer, then publishes one
+//     flag word per epilogue warp (system-scope release);
+//   * a CTA that finishes a tile it owns waits for the other ranks' strips of the
+//     same tile, adds them to its own accumulator in rank order (so the sum is the
+//     same on every run), applies the epilogue (fp32 residual add, or a plain bf16
+//     result) and stores the finished rows into the result buffer of every rank.
+//
+// With two ranks (ONE_SHOT) ownership is dropped: each rank sends every strip to the
+// other, waits for the other's strip of the same tile and finishes all rows
+// itself, so the matrix crosses the link once as bf16 in a single phase and no
+// rank's result depends on a peer's stores.
+//
+// A peer may only write here once this rank has entered the kernel (ready flags,
+// polled while the first main loop runs), and with owned tiles the kernel ends only
+// after every rank has reported that all its stores are done.  Owned and foreign tiles are
+// the same function of the tile index on every rank and CTAs walk tiles in the
+// same order, so a wait is always for a tile that its producer reaches without
+// waiting for this rank; every wait is bounded and reports through the status
+// word.  Stores to peers go through the swizzled staging tile of each epilogue
+// warp and leave as full 128-byte rows.
+struct TpFuse {
+  int rank, world;
+  char* stage[kMaxPeers];           // [source rank][tile][128][256] bf16 on each rank
+  char* out[kMaxPeers];             // result buffers
+  uint32_t* tile_flags[kMaxPeers];  // [tile][source rank][epilogue warp]
+  uint32_t* flags[kMaxPeers];       // barrier flags of the communicator
+  long out_off;                     // byte offset of the result inside `out`
+  const float* resid;               // local fp32 residual (fp32 output only)
+  long ldresid;
+  int slot;
+  uint32_t epoch, tile_epoch;
+  unsigned long long* trace;        // optional: phase times of CTA 0 (nanoseconds, summed)
+};
+
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+constexpr int kTpBN = 256;
+constexpr uint32_t kTpSpinLimit = 1u << 22;  // about a second of polling
+
+__device__ __forceinline__ bool tp_wait_flag(const uint32_t* flag, uint32_t epoch) {
+  for (uint32_t spin = 0; spin < kTpSpinLimit; ++spin) {
+    if (reached(ld_acquire_sys(flag), epoch)) return true;
+    if (spin > 64) __nanosleep(200);
+  }
+  return false;
+}
+
+// The warp's 32-row x 128-byte staging tile goes to `dst` (row pitch in bytes),
+// four complete rows per store instruction.
+__device__ __forceinline__ void tile_to_global(char* dst, long pitch, uint8_t* tile, int lane,
+                                               int rows_valid) {
+  const int ch = lane & 7;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = i * 4 + (lane >> 3);
+    const uint4 q = *reinterpret_cast<const uint4*>(staged_chunk(tile, r, ch));
+    if (r < rows_valid) st_peer_u4(dst + r * pitch + ch * 16, q);
+  }
+}
+
+template <bool B_MN, bool OUT_BF16, bool ONE_SHOT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const GemmParams p, const TpFuse f) {
+  using Cfg = GemmConfig<kTpBN, EPI_F32, true>;  // one 4 KB staging tile per epilogue warp
+  constexpr int BN = kTpBN;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* epi_smem = smem + Cfg::kStages * Cfg::kStageBytes;
+  GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(epi_smem + Cfg::kEpiBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->tmem_full[s], 1);
+      mbar_init(&bars->tmem_empty[s], 32 * kEpiWarps);
+    }
+    bars->abort = 0;
+    mbar_fence_init();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+  volatile int* abort = &bars->abort;
+  pdl_launch_dependents();
+  pdl_wait();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % p.num_m_tiles) * BM;
+        const int n0 = (tile / p.num_m_tiles) * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!wait_or_abort(&bars->empty[stage], phase ^ 1, abort)) {
+            report_status(p.status, kStatusTimeoutEmpty);
+            *abort = 1;
+            ok = false;
+            break;
+          }
+          uint8_t* sA = smem + stage * Cfg::kStageBytes;
+          uint8_t* sB = sA + kTileABytes;
+          mbar_expect_tx(&bars->full[stage], Cfg::kStageBytes);
+          const int k0 = kb * BK;
+          tma_load_2d(sA, &tmA, &bars->full[stage], k0, m0);
+          if constexpr (B_MN) {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i)
+              tma_load_2d(sB + i * (BK * 128), &tmB, &bars->full[stage], n0 + i * 64, k0);
+          } else {
+            tma_load_2d(sB, &tmB, &bars->full[stage], k0, n0);
+          }
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, false, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!wait_or_abort(&bars->tmem_empty[acc], acc_phase ^ 1, abort)) {
+          report_status(p.status, kStatusTimeoutTmemEmpty);
+          *abort = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!wait_or_abort(&bars->full[stage], phase, abort)) {
+            report_status(p.status, kStatusTimeoutFull);
+            *abort = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint32_t b_addr = a_addr + kTileABytes;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t a_desc = umma_smem_desc(a_addr + k * 32, 16, 1024);
+            const uint64_t b_desc = B_MN ? umma_smem_desc(b_addr + k * 2048, BK * 128, 1024)
+                                         : umma_smem_desc(b_addr + k * 32, 16, 1024);
+            umma_bf16_ss(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0);
+          }
+          umma_commit(&bars->empty[stage]);
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&bars->tmem_full[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------- epilogue + collective ----
+    const int quarter = warp & 3;
+    const int part = (warp - 2) >> 2;
+    const int wslot = warp - 2;
+    uint8_t* tile_smem = epi_smem + wslot * Cfg::kEpiWarpBytes;
+    // "This rank has entered": everything that used the buffers before is done.
+    if (blockIdx.x == 0 && wslot == 0 && lane < f.world) {
+      __threadfence_system();
+      st_release_sys(flag_ptr(f.flags[lane], f.slot, 0, f.rank), f.epoch);
+    }
+    bool peers_ready = false;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    // Phase times of the first tile of CTA 0's first epilogue warp, when asked for:
+    // start -> accumulator ready -> peers ready -> strip sent -> peers' strips here -> done.
+    const bool tracing = f.trace != nullptr && blockIdx.x == 0 && wslot == 0 && lane == 0;
+    unsigned long long stamp = tracing ? global_ns() : 0;
+    int trace_at = 0;
+    auto mark = [&]() {
+      if (tracing && trace_at < 5) {
+        const unsigned long long now = global_ns();
+        atomicAdd(f.trace + trace_at, now - stamp);
+        stamp = now;
+        ++trace_at;
+      }
+    };
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      const int m_tile = tile % p.num_m_tiles;
+      const int m0 = m_tile * BM;
+      const int n0 = (tile / p.num_m_tiles) * BN;
+      if (!wait_or_abort(&bars->tmem_full[acc], acc_phase, abort)) {
+        report_status(p.status, kStatusTimeoutTmemFull);
+        *abort = 1;
+        break;
+      }
+      tc_fence_after();
+      mark();
+      if (!peers_ready) {
+        const bool ok = lane >= f.world ||
+                        tp_wait_flag(flag_ptr(f.flags[f.rank], f.slot, 0, lane), f.epoch);
+        if (!__all_sync(0xffffffffu, ok) && lane == 0) report_status(p.status, kStatusTimeoutPeer);
+        peers_ready = true;
+      }
+      mark();
+      const int owner = ONE_SHOT ? f.rank : m_tile % f.world;
+      const int strip = quarter * 32;            // first row of this warp inside the tile
+      const int rows_valid = p.M - (m0 + strip);  // rows of the strip that exist (may exceed 32)
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(strip) << 16) + acc * BN;
+      const long tile_elems = static_cast<long>(BM) * BN;
+      const long my_strip = ((static_cast<long>(f.rank) * num_tiles + tile) * tile_elems +
+                             static_cast<long>(strip) * BN) * 2;  // inside a staging buffer
+      const long flag_word = (static_cast<long>(tile) * kMaxPeers + f.rank) * kEpiWarps + wslot;
+      if (ONE_SHOT || owner != f.rank) {
+        // ---- bf16 strip into the staging buffer of the owner (or of every peer) ----
+        for (int c = part; c < BN / 64; c += 2) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            float v[32];
+            load_acc32(t_row + c * 64 + h * 32, v);
+            stage_bf16_half(tile_smem, lane, h, v);
+          }
+          __syncwarp();
+          if constexpr (ONE_SHOT) {
+            for (int peer = 0; peer < f.world; ++peer)
+              if (peer != f.rank)
+                tile_to_global(f.stage[peer] + my_strip + c * 128, BN * 2, tile_smem, lane, 32);
+          } else {
+            tile_to_global(f.stage[owner] + my_strip + c * 128, BN * 2, tile_smem, lane, 32);
+          }
+          __syncwarp();
+        }
+        __threadfence_system();
+        __syncwarp();
+        if constexpr (ONE_SHOT) {
+          if (lane < f.world && lane != f.rank)
+            st_release_sys(f.tile_flags[lane] + flag_word, f.tile_epoch);
+        } else {
+          tc_fence_before();
+          mbar_arrive(&bars->tmem_empty[acc]);
+          if (lane == 0) st_release_sys(f.tile_flags[owner] + flag_word, f.tile_epoch);
+        }
+      }
+      mark();
+      if (owner == f.rank) {
+        // ---- add the peers' strips in rank order, finish the rows, store them ----
+        bool ok = true;
+        if (lane < f.world && lane != f.rank)
+          ok = tp_wait_flag(f.tile_flags[f.rank] +
+                                (static_cast<long>(tile) * kMaxPeers + lane) * kEpiWarps + wslot,
+                            f.tile_epoch);
+        if (!__all_sync(0xffffffffu, ok) && lane == 0) report_status(p.status, kStatusTimeoutPeer);
+        mark();
+        const int row = m0 + strip + lane;
+        const bool row_ok = row < p.M;
+        const char* mine = f.stage[f.rank] +
+                           (static_cast<long>(tile) * tile_elems +
+                            static_cast<long>(strip + lane) * BN) * 2;
+        constexpr int CW = OUT_BF16 ? 64 : 32;
+        for (int c = part; c < BN / CW; c += 2) {
+          const int col0 = n0 + c * CW;
+#pragma unroll
+          for (int h = 0; h < CW / 32; ++h) {
+            float v[32], sum[32];
+            load_acc32(t_row + c * CW + h * 32, v);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) sum[j] = 0.f;
+            for (int src = 0; src < f.world; ++src) {
+              if (src == f.rank) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) sum[j] += bf16_round(v[j]);
+              } else {
+                const char* from = mine + static_cast<long>(src) * num_tiles * tile_elems * 2 +
+                                   (c * CW + h * 32) * 2;
+                uint4 q[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) q[j] = ld_peer_u4(from + j * 16);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  float u[8];
+                  unpack_bf16x8(q[j], u);
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) sum[8 * j + i] += u[i];
+                }
+              }
+            }
+            if constexpr (OUT_BF16) {
+              stage_bf16_half(tile_smem, lane, h, sum);
+            } else {
+              float res[32];
+              const float* rp = f.resid + static_cast<long>(row_ok ? row : 0) * f.ldresid + col0;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 r4 = *reinterpret_cast<const float4*>(rp + 4 * j);
+                res[4 * j] = r4.x + bf16_round(sum[4 * j]);
+                res[4 * j + 1] = r4.y + bf16_round(sum[4 * j + 1]);
+                res[4 * j + 2] = r4.z + bf16_round(sum[4 * j + 2]);
+                res[4 * j + 3] = r4.w + bf16_round(sum[4 * j + 3]);
+              }
+              stage_f32(tile_smem, lane, res);
+            }
+          }
+          __syncwarp();
+          const long pitch = static_cast<long>(p.N) * (OUT_BF16 ? 2 : 4);
+          const long at = f.out_off + static_cast<long>(m0 + strip) * pitch +
+                          static_cast<long>(col0) * (OUT_BF16 ? 2 : 4);
+          if constexpr (ONE_SHOT) {
+            tile_to_global(f.out[f.rank] + at, pitch, tile_smem, lane, rows_valid);
+          } else {
+            for (int peer = 0; peer < f.world; ++peer)
+              tile_to_global(f.out[peer] + at, pitch, tile_smem, lane, rows_valid);
+          }
+          __syncwarp();
+        }
+        tc_fence_before();
+        mbar_arrive(&bars->tmem_empty[acc]);
+      }
+      mark();
+      if (tracing && trace_at == 5) {
+        atomicAdd(f.trace + 5, 1ull);
+        trace_at = 6;
+      }
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+    // ---- all stores of this warp are out; the last warp of the grid trades "done" ----
+    // (Not needed when every rank finishes its own copy: nothing of this rank's
+    // result is written by a peer, and staging is protected by the ready flags.)
+    __threadfence_system();
+    __syncwarp();
+    int last = 0;
+    if (!ONE_SHOT && lane == 0) {
+      const uint32_t arrived = atomicAdd(counter_ptr(f.flags[f.rank], f.slot), 1u);
+      last = arrived == gridDim.x * kEpiWarps - 1;
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last) {
+      if (lane == 0) *counter_ptr(f.flags[f.rank], f.slot) = 0;
+      if (lane < f.world) {
+        st_release_sys(flag_ptr(f.flags[lane], f.slot, 1, f.rank), f.epoch);
+        if (!tp_wait_flag(flag_ptr(f.flags[f.rank], f.slot, 1, lane), f.epoch))
+          report_status(p.status, kStatusTimeoutPeer);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+
 namespace {
 
 struct MapKey {
@@ -1375,4 +1772,109 @@ extern "C" int sfl_gemm_wgrad_grouped(const SflWgradProblem* problems, int count
   }
   const int grid = tiles < sm_count() ? tiles : sm_count();
   return launch_pdl(wgrad_grouped_kernel, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, maps, p);
+}
+
+// ---- GEMM + all-reduce over peer memory (see gemm_tp_kernel) ----
+namespace {
+unsigned long long* g_tp_trace = nullptr;
+
+long tp_tiles(int M, int N) {
+  return static_cast<long>((M + BM - 1) / BM) * ((N + kTpBN - 1) / kTpBN);
+}
+}  // namespace
+
+// Six 64-bit counters in device memory (or NULL to stop): summed nanoseconds of the
+// five phases of CTA 0's first tile in every later sfl_gemm_tp_reduce, and a count.
+extern "C" int sfl_gemm_tp_set_trace(void* counters) {
+  g_tp_trace = static_cast<unsigned long long*>(counters);
+  return 0;
+}
+
+extern "C" long sfl_gemm_tp_stage_bytes(int M, int N, int world) {
+  if (M <= 0 || N <= 0 || world <= 0) return 0;
+  return static_cast<long>(world) * tp_tiles(M, N) * BM * kTpBN * 2;
+}
+
+extern "C" long sfl_gemm_tp_tile_flag_bytes(int M, int N) {
+  if (M <= 0 || N <= 0) return 0;
+  return tp_tiles(M, N) * kMaxPeers * kEpiWarps * static_cast<long>(sizeof(uint32_t));
+}
+
+extern "C" int sfl_gemm_tp_reduce(const void* a, long lda, const void* b, long ldb, int b_mn, int M,
+                                  int N, int K, const SflTpFuse* tp, long out_off_bytes,
+                                  int out_bf16, const float* resid, long ldresid, int slot,
+                                  unsigned epoch, unsigned tile_epoch, int* status,
+                                  void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (tp == nullptr || M <= 0 || N <= 0 || K <= 0) return -2;
+  if (tp->world < 2 || tp->world > kMaxPeers || tp->rank < 0 || tp->rank >= tp->world) return -2;
+  if (N % kTpBN != 0 || (lda & 7) || (ldb & 7) || (out_off_bytes & 15)) return -2;
+  if (slot < 0 || slot >= kSlots) return -2;
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return -2;
+  if (!out_bf16 &&
+      (resid == nullptr || (reinterpret_cast<uintptr_t>(resid) & 15) || (ldresid & 3)))
+    return -2;
+
+  GemmParams p{};
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.num_m_tiles = (M + BM - 1) / BM;
+  p.num_n_tiles = N / kTpBN;
+  p.status = status;
+  TpFuse f{};
+  f.rank = tp->rank;
+  f.world = tp->world;
+  for (int i = 0; i < tp->world; ++i) {
+    if (tp->stage[i] == nullptr || tp->out[i] == nullptr || tp->tile_flags[i] == nullptr ||
+        tp->flags[i] == nullptr)
+      return -2;
+    f.stage[i] = static_cast<char*>(tp->stage[i]);
+    f.out[i] = static_cast<char*>(tp->out[i]);
+    f.tile_flags[i] = static_cast<uint32_t*>(tp->tile_flags[i]);
+    f.flags[i] = static_cast<uint32_t*>(tp->flags[i]);
+  }
+  f.out_off = out_off_bytes;
+  f.resid = resid;
+  f.ldresid = ldresid;
+  f.slot = slot;
+  f.epoch = epoch;
+  f.tile_epoch = tile_epoch;
+  f.trace = g_tp_trace;
+
+  CUtensorMap tmA, tmB;
+  int rc = cached_map(&tmA, a, K, M, lda, BK, BM);
+  if (rc) return 1000 + rc;
+  if (b_mn)
+    rc = cached_map(&tmB, b, N, K, ldb, 64, BK);
+  else
+    rc = cached_map(&tmB, b, K, N, ldb, BK, kTpBN);
+  if (rc) return 1000 + rc;
+
+  using Cfg = GemmConfig<kTpBN, EPI_F32, true>;
+  const long tiles = tp_tiles(M, N);
+  const int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
+  auto go = [&](auto kernel) -> int {
+    cudaError_t e =
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    return launch_pdl(kernel, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, tmA, tmB, p, f);
+  };
+  // Two ranks: each sends its whole bf16 partial to the other and both finish every
+  // row themselves (one transfer phase, 2 bytes per element).  More ranks: tiles are
+  // owned round-robin, partials go to the owner and finished rows to everyone
+  // (2 (W-1)/W transfers of the matrix instead of W-1).  SFL_TP_ONE_SHOT=0|1 overrides.
+  static const int forced = [] {
+    const char* v = getenv("SFL_TP_ONE_SHOT");
+    return v == nullptr ? -1 : atoi(v);
+  }();
+  const bool one_shot = forced < 0 ? tp->world == 2 : forced != 0;
+  if (one_shot) {
+    if (b_mn)
+      return out_bf16 ? go(gemm_tp_kernel<true, true, true>) : go(gemm_tp_kernel<true, false, true>);
+    return out_bf16 ? go(gemm_tp_kernel<false, true, true>) : go(gemm_tp_kernel<false, false, true>);
+  }
+  if (b_mn)
+    return out_bf16 ? go(gemm_tp_kernel<true, true, false>) : go(gemm_tp_kernel<true, false, false>);
+  return out_bf16 ? go(gemm_tp_kernel<false, true, false>) : go(gemm_tp_kernel<false, false, false>);
 }

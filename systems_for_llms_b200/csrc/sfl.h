@@ -266,6 +266,35 @@ int sfl_reduce_rows_bf16(const SflComm* comm, long in_off_bytes, long out_off_by
 int sfl_allreduce_rows_f32(const SflComm* comm, long in_off_bytes, long out_off_bytes, long count,
                            int slot, unsigned epoch, int ctas, int* status, void* stream);
 
+/* ------------------------------------ GEMM fused with its all-reduce (TP) -- */
+/* Pointer tables of one tensor-parallel group; entry r belongs to rank r and is
+ * a peer mapping (CUDA IPC) unless r == rank. */
+typedef struct SflTpFuse {
+  int rank, world;      /* 2 <= world <= 8                                            */
+  void* stage[8];       /* staging for partial tiles: sfl_gemm_tp_stage_bytes each    */
+  void* out[8];         /* result buffers                                             */
+  void* tile_flags[8];  /* tile arrival words: sfl_gemm_tp_tile_flag_bytes, zeroed    */
+  void* flags[8];       /* barrier flag buffers (sfl_comm_flag_bytes)                 */
+} SflTpFuse;
+long sfl_gemm_tp_stage_bytes(int M, int N, int world);
+/* Diagnostics: six uint64 counters in device memory (NULL stops): nanoseconds, summed
+ * over later calls, that CTA 0 spent until its first accumulator was ready, waiting
+ * for the peers to enter, sending its strip, waiting for the peers' strips, and
+ * finishing the rows; the sixth word counts the calls. */
+int sfl_gemm_tp_set_trace(void* counters);
+long sfl_gemm_tp_tile_flag_bytes(int M, int N);
+/* Every rank of the group calls this with its own K-slice of the operands:
+ *   partial[M, N] = a[M, K] (K-major, bf16) x b  (b: [N, K] K-major, or [K, N] when b_mn)
+ * and, in the same kernel, out[*][out_off] <- resid + bf16(sum over ranks of
+ * bf16(partial)) as fp32 [M, N] (out_bf16 = 0; resid is this rank's fp32 [M, N]
+ * with pitch ldresid), or the bf16 sum without a residual (out_bf16 = 1).  N must
+ * be a multiple of 256.  `slot`/`epoch` follow the communicator's barrier rules;
+ * `tile_epoch` must grow by one with every call on every rank. */
+int sfl_gemm_tp_reduce(const void* a, long lda, const void* b, long ldb, int b_mn, int M, int N,
+                       int K, const SflTpFuse* tp, long out_off_bytes, int out_bf16,
+                       const float* resid, long ldresid, int slot, unsigned epoch,
+                       unsigned tile_epoch, int* status, void* stream);
+
 /* ------------------------------------------------------------------ misc -- */
 int sfl_cast_f32_to_bf16(const float* x, void* y_bf16, long n, void* stream);
 int sfl_scale_f32(float* x, long n, const float* coef_dev, float scale, void* stream);
@@ -275,7 +304,7 @@ int sfl_embedding_fwd(const float* weight, const int64_t* ids, float* out, int r
 /* Library build tag, for diagnostics. */
 const char* sfl_version(void);
 /* Writes sizeof(SflGemmEpilogue), sizeof(SflWgradProblem), sizeof(SflAttnTensor),
- * sizeof(SflAttnMask), sizeof(SflComm), sizeof(SflBlockArgs) and returns how many
+ * sizeof(SflAttnMask), sizeof(SflComm), sizeof(SflBlockArgs), sizeof(SflTpFuse) and returns how many
  * there are; bindings compare them with their own mirrors. */
 int sfl_struct_sizes(int* sizes, int capacity);
 
@@ -316,6 +345,19 @@ typedef struct SflBlockArgs {
   float* g_norm2;
   int acc_wqkv, acc_wo, acc_w13, acc_w2, acc_norm1, acc_norm2; /* 1: add to the gradient */
   int* status;
+  /* Tensor parallelism (NULL tp_pool: none).  heads and d_ff above are this rank's
+   * share.  The output and down projections (forward) and the input gradients of
+   * the qkv and w1|w3 projections (backward) then run as sfl_gemm_tp_reduce: the
+   * forward results x_mid and x_out are written into every rank's fp32 pool
+   * (tp_pool->out) at the byte offsets below, x_out is ignored, and the backward
+   * sums land in every rank's bf16 buffer (tp_small->out).  Entry 0 / 1 of the
+   * slot and epoch arrays serve the first / second fused product of the call. */
+  const SflTpFuse* tp_pool;
+  const SflTpFuse* tp_small;
+  long tp_off_mid, tp_off_out;
+  int tp_slot[2];
+  unsigned tp_epoch[2];
+  unsigned tp_tile_epoch[2];
 } SflBlockArgs;
 
 long sfl_block_saved_bytes(const SflBlockArgs* args);

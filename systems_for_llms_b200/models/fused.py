@@ -326,9 +326,13 @@ def native_block_forward(engine: FusedEngine, index: int, x: torch.Tensor, B: in
     if not x2.is_contiguous():
         x2 = x2.contiguous()
     saved = torch.empty(engine._native_sizes[(index, B, T)][0], dtype=torch.uint8, device=x.device)
-    out = torch.empty_like(x2)
     _native_weights(engine, args, layer)
-    args.x, args.x_out, args.saved = x2.data_ptr(), out.data_ptr(), saved.data_ptr()
+    if engine.tp is None:
+        out = torch.empty_like(x2)
+        args.x_out = out.data_ptr()
+    else:   # results land in the symmetric pool on every rank
+        out = engine.tp.fill_block_args(args, index, B * T, engine.d_model)
+    args.x, args.saved = x2.data_ptr(), saved.data_ptr()
     code = _lib.lib().sfl_block_forward(ctypes.byref(args), _lib.stream_ptr())
     _lib.check(code, "sfl_block_forward")
     return out.view(B, T, engine.d_model), (x2, saved)
@@ -368,6 +372,8 @@ def native_block_backward(engine: FusedEngine, index: int, saved, d_out: torch.T
     args.g_wo = engine.grad_view(attn_p.output_proj.weight).data_ptr()
     args.g_wqkv = engine.grad_view(attn_p.q_proj.weight, 3 * aw).data_ptr()
     args.g_norm1 = engine.grad_view(layer.attn_norm.weight).data_ptr()
+    if engine.tp is not None:
+        engine.tp.fill_block_args(args, index, B * T, d)
     code = _lib.lib().sfl_block_backward(ctypes.byref(args), _lib.stream_ptr())
     _lib.check(code, "sfl_block_backward")
     engine._bf16_alias = (dx.data_ptr(), dx_bf16)
@@ -377,7 +383,11 @@ def native_block_backward(engine: FusedEngine, index: int, saved, d_out: torch.T
 
 
 def _use_native(engine: FusedEngine) -> bool:
-    return engine.tp is None and engine.native_blocks
+    """One library call per block; tensor-parallel engines qualify when their
+    reductions can run inside the GEMM kernels."""
+    if not engine.native_blocks:
+        return False
+    return engine.tp is None or engine.tp.can_fuse(engine.d_model)
 
 
 # ------------------------------------------------------------ block kernels --
@@ -403,13 +413,17 @@ def block_forward(engine: FusedEngine, index: int, x: torch.Tensor, B: int, T: i
     wo = engine.shadow(layer.attn.output_proj.weight)
     if tp is None:
         x_mid = G.linear_fwd_resid(attn, wo, x2)
-    else:   # row-parallel: bf16 partial sums -> one kernel sums peers, adds the residual
+    elif tp.can_fuse(d):   # row-parallel: GEMM, sum over ranks and residual add in one kernel
+        x_mid = tp.gemm_reduce_residual(attn, wo, x2, 2 * index)
+    else:   # bf16 partial sums -> a second kernel sums peers and adds the residual
         x_mid = tp.reduce_residual(G.linear_fwd(attn, wo, tp.partial(M, d)), x2, 2 * index)
     h2, rstd2 = K.rmsnorm(x_mid, layer.ffn_norm.weight, layer.ffn_norm.eps)
     g, a13 = G.swiglu_fwd(h2, engine.shadow(layer.ffn.w1.weight, 2 * dff), dff)
     w2 = engine.shadow(layer.ffn.w2.weight)
     if tp is None:
         x_out = G.linear_fwd_resid(g, w2, x_mid)
+    elif tp.can_fuse(d):
+        x_out = tp.gemm_reduce_residual(g, w2, x_mid, 2 * index + 1)
     else:
         x_out = tp.reduce_residual(G.linear_fwd(g, w2, tp.partial(M, d)), x_mid, 2 * index + 1)
     saved = (x2, rstd1, h1, qkv, attn, lse, x_mid, rstd2, h2, a13, g)
@@ -441,7 +455,9 @@ def block_backward(engine: FusedEngine, index: int, saved, d_out: torch.Tensor, 
     wgrads = [(dres_bf16, g, engine.grad_view(ffn.w2.weight), engine.claim(ffn.w2.weight))]
     if tp is None:
         dh2 = G.linear_dgrad(d13, engine.shadow(ffn.w1.weight, 2 * dff))
-    else:   # column-parallel input gradient: partial over ranks, summed by one kernel
+    elif tp.can_fuse(d):   # column-parallel input gradient: GEMM + sum over ranks, one kernel
+        dh2 = tp.gemm_reduce_bf16(d13, engine.shadow(ffn.w1.weight, 2 * dff))
+    else:
         dh2 = tp.reduce_bf16(G.linear_dgrad(d13, engine.shadow(ffn.w1.weight, 2 * dff),
                                             tp.partial(M, d)))
     wgrads.append((d13, h2, engine.grad_view(ffn.w1.weight, 2 * dff),
@@ -464,6 +480,8 @@ def block_backward(engine: FusedEngine, index: int, saved, d_out: torch.Tensor, 
                     rope=(engine.cos, engine.sin))   # dq, dk come back un-rotated
     if tp is None:
         dh1 = G.linear_dgrad(dqkv, engine.shadow(attn_p.q_proj.weight, 3 * aw))
+    elif tp.can_fuse(d):
+        dh1 = tp.gemm_reduce_bf16(dqkv, engine.shadow(attn_p.q_proj.weight, 3 * aw))
     else:
         dh1 = tp.reduce_bf16(G.linear_dgrad(dqkv, engine.shadow(attn_p.q_proj.weight, 3 * aw),
                                             tp.partial(M, d)))

@@ -9,7 +9,7 @@ can never pass on the wrong code path.
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_long, c_void_p
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_long, c_uint, c_void_p
 from functools import lru_cache
 
 import torch
@@ -59,6 +59,9 @@ class BlockArgs(Structure):
         ("acc_wqkv", c_int), ("acc_wo", c_int), ("acc_w13", c_int), ("acc_w2", c_int),
         ("acc_norm1", c_int), ("acc_norm2", c_int),
         ("status", c_void_p),
+        ("tp_pool", c_void_p), ("tp_small", c_void_p), ("tp_off_mid", c_long),
+        ("tp_off_out", c_long), ("tp_slot", c_int * 2), ("tp_epoch", c_uint * 2),
+        ("tp_tile_epoch", c_uint * 2),
     ]
 
 
@@ -102,7 +105,8 @@ _KERNELS_PER_CALL = {"sfl_attn_bwd": 2, "sfl_block_forward": 7, "sfl_block_backw
                      "sfl_ipc_alloc": 0, "sfl_ipc_free": 0, "sfl_ipc_get_handle": 0,
                      "sfl_ipc_open_handle": 0, "sfl_ipc_close_handle": 0,
                      "sfl_comm_set_spin_limit": 0, "sfl_comm_flag_bytes": 0, "sfl_comm_slots": 0,
-                     "sfl_comm_max_ctas": 0}
+                     "sfl_comm_max_ctas": 0, "sfl_gemm_tp_stage_bytes": 0,
+                     "sfl_gemm_tp_tile_flag_bytes": 0}
 _launches = [0]
 
 

@@ -6,6 +6,8 @@
     python -m systems_for_llms_b200.ops.microbench step        # per-kernel table of one step
     python -m systems_for_llms_b200.ops.microbench once NAME   # a few launches of one op
     python -m systems_for_llms_b200.ops.microbench mma         # tcgen05.mma issue-rate test
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
+        -m systems_for_llms_b200.ops.microbench tp             # GEMM + all-reduce, one kernel vs two
 
 Each timing is the median of CUDA-event measurements with a 256 MB buffer
 written between launches, so operands come from HBM rather than from a warm L2.
@@ -235,6 +237,87 @@ def step_table(steps: int = 3) -> dict:
                         for e in events]}
 
 
+def tensor_parallel_table(iters: int = 30) -> dict:
+    """The four sharded-reduction products of a tensor-parallel layer (one process per
+    GPU): the GEMM followed by the peer-memory reduction kernel against the single
+    kernel that does both, CUDA-event time per call as the max over ranks, and the
+    fused kernel's own phase times (CTA 0, first tile)."""
+    import ctypes
+    import os
+
+    import torch.distributed as dist
+
+    from ..parallel.tensor_parallel import TensorParallelComm
+    from . import gemm as G
+    from . import lib as L
+    from .gemm import check_status
+    rank, world, local = (int(os.environ[k]) for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=device)
+    tp = TensorParallelComm(device, None, num_layers=1)
+    M, d = M_TOKENS, D_MODEL
+    aw, dff = D_MODEL // world, D_FF // world
+    torch.manual_seed(rank)
+    resid = torch.randn(M, d, device=device)
+    cases = {   # name: (activations, weight, weight is [K, N])
+        "wo_resid": (rnd(M, aw), rnd(d, aw, scale=aw ** -0.5), False),
+        "w2_resid": (rnd(M, dff), rnd(d, dff, scale=dff ** -0.5), False),
+        "dgrad_w13": (rnd(M, 2 * dff), rnd(2 * dff, d, scale=d ** -0.5), True),
+        "dgrad_qkv": (rnd(M, 3 * aw), rnd(3 * aw, d, scale=d ** -0.5), True),
+    }
+
+    def two_kernels(a, w, b_mn):
+        if b_mn:
+            return tp.reduce_bf16(G.linear_dgrad(a, w, tp.partial(M, d)))
+        return tp.reduce_residual(G.linear_fwd(a, w, tp.partial(M, d)), resid, 0)
+
+    def one_kernel(a, w, b_mn):
+        return tp.gemm_reduce_bf16(a, w) if b_mn else tp.gemm_reduce_residual(a, w, resid, 1)
+
+    def timed(fn, args) -> float:
+        for _ in range(5):
+            fn(*args)
+        samples = []
+        for _ in range(iters):
+            dist.barrier()
+            torch.cuda.synchronize()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            for _ in range(4):          # back to back, as inside a layer
+                fn(*args)
+            end.record()
+            end.synchronize()
+            samples.append(begin.elapsed_time(end) * 250)
+        worst = torch.tensor(statistics.median(samples), device=device)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        return worst.item()
+
+    rows = []
+    for name, args in cases.items():
+        K = args[0].shape[1]
+        rows.append({"op": name, "k_per_rank": K, "two_kernels_us": timed(two_kernels, args),
+                     "one_kernel_us": timed(one_kernel, args),
+                     "link_mb_per_rank": M * d * 2 / 2 ** 20 if world == 2
+                     else M * d * (2 + (2 if args[2] else 4)) * (world - 1) / world / 2 ** 20})
+    counters = torch.zeros(6, dtype=torch.int64, device=device)
+    handle = L.lib()._handle
+    handle.sfl_gemm_tp_set_trace.argtypes = [ctypes.c_void_p]
+    handle.sfl_gemm_tp_set_trace(counters.data_ptr())
+    for _ in range(50):
+        one_kernel(*cases["w2_resid"])
+    torch.cuda.synchronize()
+    handle.sfl_gemm_tp_set_trace(None)
+    check_status()
+    values = counters.tolist()
+    phases = {name: values[i] / max(values[5], 1) / 1e3 for i, name in enumerate(
+        ("accumulator_ready", "peers_entered", "strip_sent", "peer_strips_arrived", "rows_finished"))}
+    dist.barrier()
+    tp.close()
+    dist.destroy_process_group()
+    return {"rank": rank, "world": world, "rows": rows, "w2_resid_phase_us": phases}
+
+
 def mma_issue_rate() -> str:
     """Compile ops/mma_issue_rate.cu for sm_100a into a temporary directory and run it."""
     import subprocess
@@ -254,7 +337,7 @@ def mma_issue_rate() -> str:
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__,
                                      formatter_class=argparse.RawDescriptionHelpFormatter)
-    parser.add_argument("what", choices=[*SUITES, "step", "once", "mma"])
+    parser.add_argument("what", choices=[*SUITES, "step", "once", "mma", "tp"])
     parser.add_argument("name", nargs="?", help="operation for 'once' (e.g. w13_swiglu, attn_bwd)")
     parser.add_argument("--repeat", type=int, default=3)
     parser.add_argument("--json", action="store_true")
@@ -263,6 +346,20 @@ def main() -> None:
         raise SystemExit("a CUDA GPU is required")
     if args.what == "mma":
         print(mma_issue_rate(), end="")
+        return
+    if args.what == "tp":
+        table = tensor_parallel_table()
+        if table["rank"] == 0:
+            if args.json:
+                print(json.dumps(table))
+                return
+            print(f"{table['world']} ranks, M {M_TOKENS}, N {D_MODEL}; microseconds per call, max over ranks")
+            for row in table["rows"]:
+                print(f"{row['op']:10s} K/rank {row['k_per_rank']:5d}  GEMM + reduce kernel "
+                      f"{row['two_kernels_us']:7.1f}   one kernel {row['one_kernel_us']:7.1f}   "
+                      f"({row['link_mb_per_rank']:.1f} MB per rank over NVLink)")
+            print("w2_resid, CTA 0, first tile, microseconds per phase: " + ", ".join(
+                f"{k} {v:.1f}" for k, v in table["w2_resid_phase_us"].items()))
         return
     if args.what == "once":
         from .gemm import check_status

@@ -33,6 +33,14 @@ class CommStruct(Structure):
                 ("data2", c_void_p * MAX_PEERS), ("flags", c_void_p * MAX_PEERS)]
 
 
+class TpFuseStruct(Structure):
+    """Mirror of ``SflTpFuse`` (csrc/sfl.h)."""
+
+    _fields_ = [("rank", c_int), ("world", c_int), ("stage", c_void_p * MAX_PEERS),
+                ("out", c_void_p * MAX_PEERS), ("tile_flags", c_void_p * MAX_PEERS),
+                ("flags", c_void_p * MAX_PEERS)]
+
+
 _C = POINTER(CommStruct)
 _P = c_void_p
 for _name, _args in {
@@ -54,6 +62,11 @@ for _name, _args in {
     "sfl_reduce_rows_resid": [_C, c_long, c_long, _P, c_long, c_int, c_int, c_uint, c_int, _P, _P],
     "sfl_reduce_rows_bf16": [_C, c_long, c_long, c_long, c_int, c_int, c_uint, c_int, _P, _P],
     "sfl_allreduce_rows_f32": [_C, c_long, c_long, c_long, c_int, c_uint, c_int, _P, _P],
+    "sfl_gemm_tp_stage_bytes": [c_int, c_int, c_int],
+    "sfl_gemm_tp_tile_flag_bytes": [c_int, c_int],
+    "sfl_gemm_tp_reduce": [_P, c_long, _P, c_long, c_int, c_int, c_int, c_int,
+                           POINTER(TpFuseStruct), c_long, c_int, _P, c_long, c_int, c_uint,
+                           c_uint, _P, _P],
 }.items():
     _lib.register_signature(_name, _args)
 
@@ -264,6 +277,37 @@ class PeerComm:
             ctypes.byref(self.struct(partial, out)), in_off, out_off, count, slot,
             self.next_epoch(slot), self.ctas, self.status.data_ptr(), _lib.stream_ptr())
         _lib.check(code, "sfl_allreduce_rows_f32")
+
+    def tp_struct(self, stage: SymmetricBuffer, out: SymmetricBuffer,
+                  tile_flags: SymmetricBuffer) -> TpFuseStruct:
+        key = ("tp", id(stage), id(out), id(tile_flags))
+        cached = self._structs.get(key)
+        if cached is None:
+            cached = TpFuseStruct()
+            cached.rank, cached.world = self.rank, self.world
+            for peer in range(self.world):
+                cached.stage[peer] = stage.peer_ptrs[peer]
+                cached.out[peer] = out.peer_ptrs[peer]
+                cached.tile_flags[peer] = tile_flags.peer_ptrs[peer]
+                cached.flags[peer] = self.flags.peer_ptrs[peer]
+            self._structs[key] = cached
+        return cached
+
+    def gemm_tp_reduce(self, a: torch.Tensor, b: torch.Tensor, b_mn: bool, n: int,
+                       stage: SymmetricBuffer, tile_flags: SymmetricBuffer, out: SymmetricBuffer,
+                       out_off: int, resid: torch.Tensor | None, slot: int,
+                       tile_epoch: int) -> None:
+        """One kernel: ``a @ b`` on this rank's K-slice, summed over ranks, finished
+        (``resid + sum`` in fp32, or the bf16 sum when ``resid`` is None) and written
+        into ``out`` at ``out_off`` bytes on every rank.  ``b`` is ``[n, K]``, or
+        ``[K, n]`` with ``b_mn``."""
+        m, k = a.shape
+        code = _lib.lib().sfl_gemm_tp_reduce(
+            a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), int(b_mn), m, n, k,
+            ctypes.byref(self.tp_struct(stage, out, tile_flags)), out_off, int(resid is None),
+            _lib.ptr(resid), resid.stride(0) if resid is not None else 0, slot,
+            self.next_epoch(slot), tile_epoch, self.status.data_ptr(), _lib.stream_ptr())
+        _lib.check(code, "sfl_gemm_tp_reduce")
 
     def close(self) -> None:
         self.flags.close()

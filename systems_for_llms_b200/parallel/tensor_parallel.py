@@ -21,7 +21,9 @@ Data paths:
 
 from __future__ import annotations
 
+import ctypes
 import math
+import os
 
 import torch
 import torch.distributed as dist
@@ -242,17 +244,28 @@ class TensorParallelComm:
         self.device, self.group, self.num_layers = device, group, num_layers
         self.comm = pm.PeerComm(device, group, ctas=96)
         self.rows = self.cols = 0
-        self.partial_buf = self.pool = self.small = None
+        self.partial_buf = self.pool = self.small = self.stage = self.tile_flags = None
         self._calls = 0
+        self._tile_epoch = 0
+        # SFL_TP_UNFUSED=1 keeps the GEMM and its reduction as two kernels (A/B runs)
+        self.fuse_gemm = os.environ.get("SFL_TP_UNFUSED", "0") != "1"
 
     def _ensure(self, rows: int, cols: int) -> None:
         if rows <= self.rows and cols == self.cols:
             return
-        for buffer in (self.partial_buf, self.pool, self.small):
+        for buffer in (self.partial_buf, self.pool, self.small, self.stage, self.tile_flags):
             if buffer is not None:
                 buffer.close()
         pm = self.pm
+        self.comm._structs.clear()      # cached pointer tables name the old buffers
         self.rows, self.cols = rows, cols
+        from ..ops import lib as _kernel_lib
+        handle = _kernel_lib.lib()
+        world = self.comm.world
+        self.stage = pm.SymmetricBuffer(max(256, handle.sfl_gemm_tp_stage_bytes(rows, cols, world)),
+                                        self.device, self.group)
+        self.tile_flags = pm.SymmetricBuffer(
+            max(256, handle.sfl_gemm_tp_tile_flag_bytes(rows, cols)), self.device, self.group)
         self.partial_buf = pm.SymmetricBuffer(rows * cols * 2, self.device, self.group)
         self.pool = pm.SymmetricBuffer(2 * self.num_layers * rows * cols * 4, self.device,
                                        self.group)
@@ -273,13 +286,59 @@ class TensorParallelComm:
                                     self._slot())
         return self.pool.view(torch.float32, rows * cols, offset).view(rows, cols)
 
+    def can_fuse(self, cols: int) -> bool:
+        """The one-kernel GEMM + all-reduce needs whole 256-column tiles."""
+        return self.fuse_gemm and self.comm.world > 1 and cols % 256 == 0
+
+    def _next_tile_epoch(self) -> int:
+        self._tile_epoch += 1
+        return self._tile_epoch
+
+    def gemm_reduce_residual(self, a: torch.Tensor, weight: torch.Tensor, resid: torch.Tensor,
+                             position: int) -> torch.Tensor:
+        """``resid + sum over ranks of a @ weight.T`` (row-parallel forward) in one kernel:
+        tiles go to their owner rank as they finish and the finished rows come back
+        to every rank's pool slot while later tiles are still in the tensor cores."""
+        rows, cols = a.shape[0], weight.shape[0]
+        self._ensure(rows, cols)
+        offset = position * self.rows * self.cols * 4
+        self.comm.gemm_tp_reduce(a, weight, False, cols, self.stage, self.tile_flags, self.pool,
+                                 offset, resid, self._slot(), self._next_tile_epoch())
+        return self.pool.view(torch.float32, rows * cols, offset).view(rows, cols)
+
+    def gemm_reduce_bf16(self, dy: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+        """bf16 ``sum over ranks of dy @ weight`` (column-parallel input gradient)."""
+        rows, cols = dy.shape[0], weight.shape[1]
+        self._ensure(rows, cols)
+        self.comm.gemm_tp_reduce(dy, weight, True, cols, self.stage, self.tile_flags, self.small,
+                                 0, None, self._slot(), self._next_tile_epoch())
+        return self.small.view(torch.bfloat16, rows * cols).view(rows, cols)
+
+    def fill_block_args(self, args, index: int, rows: int, cols: int) -> torch.Tensor:
+        """Tensor-parallel part of a native block call (csrc/block.cu): pointer tables,
+        pool offsets of the layer's two results, and barrier slots / epochs for the
+        call's two fused products.  Returns the view where ``x_out`` will appear."""
+        self._ensure(rows, cols)
+        comm = self.comm
+        pool = comm.tp_struct(self.stage, self.pool, self.tile_flags)
+        small = comm.tp_struct(self.stage, self.small, self.tile_flags)
+        args.tp_pool, args.tp_small = ctypes.addressof(pool), ctypes.addressof(small)
+        slot_bytes = self.rows * self.cols * 4
+        args.tp_off_mid, args.tp_off_out = 2 * index * slot_bytes, (2 * index + 1) * slot_bytes
+        for i in range(2):
+            slot = self._slot()
+            args.tp_slot[i] = slot
+            args.tp_epoch[i] = comm.next_epoch(slot)
+            args.tp_tile_epoch[i] = self._next_tile_epoch()
+        return self.pool.view(torch.float32, rows * cols, args.tp_off_out).view(rows, cols)
+
     def reduce_bf16(self, partial: torch.Tensor) -> torch.Tensor:
         rows, cols = partial.shape
         self.comm.reduce_rows_bf16(self.partial_buf, self.small, 0, 0, rows, cols, self._slot())
         return self.small.view(torch.bfloat16, rows * cols).view(rows, cols)
 
     def close(self) -> None:
-        for buffer in (self.partial_buf, self.pool, self.small):
+        for buffer in (self.partial_buf, self.pool, self.small, self.stage, self.tile_flags):
             if buffer is not None:
                 buffer.close()
         self.comm.close()

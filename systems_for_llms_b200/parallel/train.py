@@ -436,6 +436,11 @@ def run(config: TrainConfig, output_dir, *, mode="single", global_batch_size=8,
                                    or (strategy.engine is not None and strategy.engine.tp is not None)
                                    or (mode == "fsdp" and strategy.engine is not None)
                                    else "torch.distributed collectives"),
+            "tensor_parallel_reduction": (
+                None if strategy.engine is None or strategy.engine.tp is None
+                else "inside the GEMM kernels (tile by tile over peer memory)"
+                if strategy.engine.tp.can_fuse(strategy.engine.d_model)
+                else "separate peer-memory kernel after each GEMM"),
             "checkpoint_scope": ("optional final model/optimizer state for correctness checks; "
                                  "resume unsupported"),
         }

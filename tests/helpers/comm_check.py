@@ -95,6 +95,42 @@ check_status()
 got = ob.view(torch.float32, rows * cols).view(rows, cols)
 out["tp_reduce_maxerr"] = (got - (resid + total.bfloat16().float())).abs().max().item()
 
+# GEMM fused with its all-reduce: must equal the two-kernel path bit for bit
+# (same bf16 partials, same rank-order sum), for both operand layouts, with a
+# ragged last row tile, several launches in a row (staging and flag reuse).
+from systems_for_llms_b200.ops import gemm as G  # noqa: E402
+from systems_for_llms_b200.parallel.tensor_parallel import TensorParallelComm  # noqa: E402
+
+tp = TensorParallelComm(dev, None, num_layers=2)
+M, N, KL = 1000, 512, 192
+fused_equal, fused_err = True, 0.0
+for trial in range(3):
+    torch.manual_seed(1000 * trial + rank)
+    a = torch.randn(M, KL, device=dev).bfloat16()
+    w = (torch.randn(N, KL, device=dev) / KL ** 0.5).bfloat16()
+    w_t = w.t().contiguous()                    # [KL, N]: the input-gradient layout
+    torch.manual_seed(5 + trial)
+    resid = torch.randn(M, N, device=dev)
+    two_step = tp.reduce_residual(G.linear_fwd(a, w, tp.partial(M, N)), resid, 0).clone()
+    two_step_bf16 = tp.reduce_bf16(G.linear_dgrad(a, w_t, tp.partial(M, N))).clone()
+    one_step = tp.gemm_reduce_residual(a, w, resid, 1).clone()
+    one_step_bf16 = tp.gemm_reduce_bf16(a, w_t).clone()
+    torch.cuda.synchronize()
+    check_status()
+    fused_equal &= bool(torch.equal(one_step, two_step)) and bool(
+        torch.equal(one_step_bf16, two_step_bf16))
+    exact = a.float() @ w.float().t()
+    dist.all_reduce(exact)
+    fused_err = max(fused_err, (one_step - resid - exact).abs().max().item(),
+                    (one_step_bf16.float() - exact).abs().max().item())
+out["tp_fused_equal"], out["tp_fused_maxerr"] = fused_equal, fused_err
+replicas = [None] * world
+dist.all_gather_object(replicas, (one_step.double().sum().item(), one_step_bf16.double().sum().item()))
+out["tp_fused_replicas_equal"] = len(set(replicas)) == 1
+dist.barrier()
+torch.cuda.synchronize()
+tp.close()
+
 # Failure detection without faulting anything: only rank 0 enters a collective on
 # a fresh slot with a ~1 ms polling budget; the flag it waits for is never set.
 dist.barrier()

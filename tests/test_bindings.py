@@ -20,13 +20,13 @@ def library():
 def test_struct_sizes_match_the_compiled_library(library):
     from systems_for_llms_b200.attention.flash import AttnMask, AttnTensor
     from systems_for_llms_b200.ops.lib import BlockArgs, GemmEpilogue, WgradProblem
-    from systems_for_llms_b200.parallel.comm import CommStruct
+    from systems_for_llms_b200.parallel.comm import CommStruct, TpFuseStruct
     handle = library._handle
     handle.sfl_struct_sizes.argtypes = [ctypes.POINTER(ctypes.c_int), ctypes.c_int]
     handle.sfl_struct_sizes.restype = ctypes.c_int
     sizes = (ctypes.c_int * 8)()
     count = handle.sfl_struct_sizes(sizes, 8)
-    mirrors = [GemmEpilogue, WgradProblem, AttnTensor, AttnMask, CommStruct, BlockArgs]
+    mirrors = [GemmEpilogue, WgradProblem, AttnTensor, AttnMask, CommStruct, BlockArgs, TpFuseStruct]
     assert count == len(mirrors)
     assert [ctypes.sizeof(m) for m in mirrors] == list(sizes)[:count]
 
@@ -47,3 +47,22 @@ def test_block_runner_rejects_bad_shapes_without_a_gpu(library):
     args.head_dim = 48                                                     # unsupported width
     assert library.sfl_block_saved_bytes(ctypes.byref(args)) == -1
     assert library.sfl_block_forward(ctypes.byref(args), None) == -2     # refused before any launch
+
+
+def test_fused_tensor_parallel_gemm_validates_before_launching(library):
+    from systems_for_llms_b200.parallel.comm import TpFuseStruct
+    assert library.sfl_gemm_tp_stage_bytes(4096, 1024, 2) == 2 * 32 * 4 * 128 * 256 * 2
+    assert library.sfl_gemm_tp_tile_flag_bytes(4096, 1024) == 32 * 4 * 8 * 8 * 4
+    assert library.sfl_gemm_tp_stage_bytes(1000, 512, 8) == 8 * 8 * 2 * 128 * 256 * 2   # ragged rows
+    table = TpFuseStruct()
+    call = library._handle.sfl_gemm_tp_reduce
+    call.restype = ctypes.c_int
+    call.argtypes = None
+    args = lambda n, world: (ctypes.c_void_p(256), ctypes.c_long(64), ctypes.c_void_p(512),
+                             ctypes.c_long(64), 0, 128, n, 64, ctypes.byref(table),
+                             ctypes.c_long(0), 1, None, ctypes.c_long(0), 0, 1, 1, None, None)
+    table.rank, table.world = 0, 1
+    assert call(*args(256, 1)) == -2          # a group of one has nothing to reduce
+    table.world = 2
+    assert call(*args(200, 2)) == -2          # N must be whole 256-column tiles
+    assert call(*args(256, 2)) == -2          # pointer tables not filled in

@@ -73,14 +73,34 @@ def test_two_gpu_mode_matches_single(tmp_path, single, mode, extra):
         assert summary["optimizer_state_bytes_max_rank"] * 2 <= summary["optimizer_state_bytes_sum"] + 64
 
 
-def test_comm_kernels_against_nccl(tmp_path):
+def test_two_gpu_tensor_parallel_fused_gemm_allreduce_matches_single(tmp_path, monkeypatch):
+    """d_model of 256 lets the row-parallel products and the column-parallel input
+    gradients run as one GEMM + all-reduce kernel each, issued by the native block
+    runner; the result must match a single GPU like every other mode."""
+    wide = dict(CONFIG, model=dict(CONFIG["model"], d_model=256, num_heads=4, d_ff=704))
+    monkeypatch.setitem(globals(), "CONFIG", wide)
+    ref_summary, _, ref_state = launch(tmp_path, "one", "single", 1, ["--microbatch-size", "4"])
+    for extra in ([], ["--checkpointing", "block"]):
+        summary, meta, state = launch(tmp_path, "tp" + str(len(extra)), "tp", 2,
+                                      ["--microbatch-size", "2", *extra])
+        assert meta["tensor_parallel_reduction"].startswith("inside the GEMM kernels")
+        assert summary["batch_stream_sha256"] == ref_summary["batch_stream_sha256"]
+        assert summary["valid_loss"] == pytest.approx(ref_summary["valid_loss"], rel=2e-2)
+        for name, value in ref_state["model"].items():
+            torch.testing.assert_close(state["model"][name], value, rtol=0, atol=5e-3, msg=name)
+
+
+@pytest.mark.parametrize("one_shot", ["1", "0"])
+def test_comm_kernels_against_nccl(tmp_path, one_shot):
+    """``one_shot`` picks the variant of the fused GEMM + all-reduce: both ranks finish
+    every row (the default for two ranks) or tiles owned round-robin (larger groups)."""
     script = ROOT / "tests" / "helpers" / "comm_check.py"
     global PORT
     PORT += 1
     command = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                "--master-addr", "127.0.0.1", "--master-port", str(PORT), str(script),
                str(tmp_path / "out.json")]
-    env = dict(os.environ, PYTHONPATH=str(ROOT), NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, PYTHONPATH=str(ROOT), NCCL_NVLS_ENABLE="0", SFL_TP_ONE_SHOT=one_shot)
     result = subprocess.run(command, cwd=ROOT, env=env, capture_output=True, text=True, timeout=300)
     assert result.returncode == 0, result.stderr[-3000:]
     out = json.loads((tmp_path / "out.json").read_text())
@@ -88,4 +108,6 @@ def test_comm_kernels_against_nccl(tmp_path):
     assert out["norm"] == pytest.approx(out["norm_ref"], rel=1e-5)
     assert out["zero_param_maxerr"] < 2e-6 and out["zero_shadow_ok"]
     assert out["allgather_ok"] and out["tp_reduce_maxerr"] < 1e-6
+    assert out["tp_fused_equal"] and out["tp_fused_replicas_equal"]
+    assert out["tp_fused_maxerr"] < 0.15      # bf16 partials of a K = 384 reduction, |x| ~ 1
     assert out["timeout_status"] == 5 and out["recovered_after_timeout"]
