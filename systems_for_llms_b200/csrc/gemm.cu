@@ -1126,7 +1126,7 @@ wgrad_grouped_kernel(const __grid_constant__ GroupedMaps maps,
 // warp and leave as full 128-byte rows.
 struct TpFuse {
   int rank, world;
-  char* stage[kMaxPeers];           // [source rank][tile][128][256] bf16 on each rank
+  char* stage[kMaxPeers];           // [source rank][tile][4 strips][4 chunks] 4 KB blocks
   char* out[kMaxPeers];             // result buffers
   uint32_t* tile_flags[kMaxPeers];  // [tile][source rank][epilogue warp]
   uint32_t* flags[kMaxPeers];       // barrier flags of the communicator
@@ -1166,6 +1166,16 @@ __device__ __forceinline__ void tile_to_global(char* dst, long pitch, uint8_t* t
     const uint4 q = *reinterpret_cast<const uint4*>(staged_chunk(tile, r, ch));
     if (r < rows_valid) st_peer_u4(dst + r * pitch + ch * 16, q);
   }
+}
+
+// The staging tile as it is (swizzle included) to 4 KB of contiguous memory: every
+// store instruction of the warp covers 512 consecutive bytes, which is what the
+// link moves best.  The reader undoes the swizzle (staged_chunk on the address).
+__device__ __forceinline__ void tile_to_block(char* dst, const uint8_t* tile, int lane) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    st_peer_u4(dst + i * 512 + lane * 16,
+               *reinterpret_cast<const uint4*>(tile + i * 512 + lane * 16));
 }
 
 template <bool B_MN, bool OUT_BF16, bool ONE_SHOT>
@@ -1343,8 +1353,10 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int rows_valid = p.M - (m0 + strip);  // rows of the strip that exist (may exceed 32)
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(strip) << 16) + acc * BN;
       const long tile_elems = static_cast<long>(BM) * BN;
+      // A strip in a staging buffer: four 4 KB blocks (32 rows x 64 columns of bf16),
+      // one per 64-column chunk, each an image of the sender's staging tile.
       const long my_strip = ((static_cast<long>(f.rank) * num_tiles + tile) * tile_elems +
-                             static_cast<long>(strip) * BN) * 2;  // inside a staging buffer
+                             static_cast<long>(strip) * BN) * 2;
       const long flag_word = (static_cast<long>(tile) * kMaxPeers + f.rank) * kEpiWarps + wslot;
       if (ONE_SHOT || owner != f.rank) {
         // ---- bf16 strip into the staging buffer of the owner (or of every peer) ----
@@ -1359,9 +1371,9 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if constexpr (ONE_SHOT) {
             for (int peer = 0; peer < f.world; ++peer)
               if (peer != f.rank)
-                tile_to_global(f.stage[peer] + my_strip + c * 128, BN * 2, tile_smem, lane, 32);
+                tile_to_block(f.stage[peer] + my_strip + c * kEpiTileBytes, tile_smem, lane);
           } else {
-            tile_to_global(f.stage[owner] + my_strip + c * 128, BN * 2, tile_smem, lane, 32);
+            tile_to_block(f.stage[owner] + my_strip + c * kEpiTileBytes, tile_smem, lane);
           }
           __syncwarp();
         }
@@ -1388,9 +1400,8 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         mark();
         const int row = m0 + strip + lane;
         const bool row_ok = row < p.M;
-        const char* mine = f.stage[f.rank] +
-                           (static_cast<long>(tile) * tile_elems +
-                            static_cast<long>(strip + lane) * BN) * 2;
+        const char* mine = f.stage[f.rank] + (static_cast<long>(tile) * tile_elems +
+                                              static_cast<long>(strip) * BN) * 2;
         constexpr int CW = OUT_BF16 ? 64 : 32;
         for (int c = part; c < BN / CW; c += 2) {
           const int col0 = n0 + c * CW;
@@ -1405,11 +1416,15 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
                 for (int j = 0; j < 32; ++j) sum[j] += bf16_round(v[j]);
               } else {
-                const char* from = mine + static_cast<long>(src) * num_tiles * tile_elems * 2 +
-                                   (c * CW + h * 32) * 2;
+                const int col = c * CW + h * 32;  // first of 32 columns inside the tile
+                const char* block = mine + static_cast<long>(src) * num_tiles * tile_elems * 2 +
+                                    (col >> 6) * kEpiTileBytes;
+                const int first = (col & 63) >> 3;  // 16-byte chunk of the row
                 uint4 q[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) q[j] = ld_peer_u4(from + j * 16);
+                for (int j = 0; j < 4; ++j)
+                  q[j] = ld_peer_u4(staged_chunk(
+                      reinterpret_cast<uint8_t*>(const_cast<char*>(block)), lane, first + j));
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                   float u[8];
