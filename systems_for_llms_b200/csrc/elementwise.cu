@@ -413,6 +413,74 @@ __global__ void embedding_fwd_kernel(const float* __restrict__ weight,
   }
 }
 
+// Embedding backward: dW[v] (+)= sum of dx[t] over the tokens t with ids[t] == v, added
+// in token order so the result does not depend on scheduling (the reference relies
+// on autograd's embedding backward, src/llmlab/model/layers.py:60-74).  Two kernels:
+// the first links the tokens of each id into a chain (next[t] = next later token with
+// the same id, head[v] = its first token), scanning the ids in shared memory; the
+// second walks one chain per vocabulary row.  No sort, no dense temporary.
+__global__ void __launch_bounds__(256)
+embedding_links_kernel(const int64_t* __restrict__ ids, int rows, int vocab,
+                       int* __restrict__ next, int* __restrict__ head) {
+  extern __shared__ int sid[];
+  for (int i = threadIdx.x; i < rows; i += blockDim.x) {
+    const int64_t v = ids[i];
+    sid[i] = (v < 0 || v >= vocab) ? 0 : static_cast<int>(v);  // same clamp as the forward
+  }
+  __syncthreads();
+  for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < rows; t += gridDim.x * blockDim.x) {
+    const int id = sid[t];
+    int nx = -1;
+    for (int u = t + 1; u < rows; ++u)
+      if (sid[u] == id) {
+        nx = u;
+        break;
+      }
+    next[t] = nx;
+    bool first = true;
+    for (int u = t - 1; u >= 0; --u)
+      if (sid[u] == id) {
+        first = false;
+        break;
+      }
+    if (first) head[id] = t;  // exactly one token per id gets here
+  }
+}
+
+__global__ void __launch_bounds__(128)
+embedding_bwd_kernel(const float* __restrict__ dx, const int* __restrict__ next,
+                     const int* __restrict__ head, float* __restrict__ dweight, int dim,
+                     int accumulate) {
+  const int v = blockIdx.x;
+  float* dst = dweight + static_cast<long>(v) * dim;
+  int t = head[v];
+  if (t < 0) {
+    if (!accumulate)
+      for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = 0.f;
+    return;
+  }
+  if ((dim & 3) == 0) {
+    for (int i = threadIdx.x * 4; i < dim; i += blockDim.x * 4) {
+      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int u = t; u >= 0; u = next[u]) {
+        const float4 g = *reinterpret_cast<const float4*>(dx + static_cast<long>(u) * dim + i);
+        sum.x += g.x; sum.y += g.y; sum.z += g.z; sum.w += g.w;
+      }
+      if (accumulate) {
+        const float4 o = *reinterpret_cast<const float4*>(dst + i);
+        sum.x += o.x; sum.y += o.y; sum.z += o.z; sum.w += o.w;
+      }
+      *reinterpret_cast<float4*>(dst + i) = sum;
+    }
+  } else {
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+      float sum = 0.f;
+      for (int u = t; u >= 0; u = next[u]) sum += dx[static_cast<long>(u) * dim + i];
+      dst[i] = accumulate ? dst[i] + sum : sum;
+    }
+  }
+}
+
 inline int grid_for(long n, int threads, int cap = 148 * 8) {
   long blocks = (n + threads - 1) / threads;
   if (blocks > cap) blocks = cap;
@@ -532,6 +600,32 @@ extern "C" int sfl_embedding_fwd(const float* weight, const int64_t* ids, float*
                                  int dim, int vocab, void* stream) {
   if (rows <= 0) return -2;
   embedding_fwd_kernel<<<rows, 128, 0, SFL_STREAM(stream)>>>(weight, ids, out, rows, dim, vocab);
+  SFL_RET();
+}
+
+extern "C" int sfl_embedding_bwd(const float* dx, const int64_t* ids, float* dweight, int rows,
+                                 int dim, int vocab, int accumulate, int* next_scratch,
+                                 int* head_scratch, void* stream) {
+  if (rows <= 0 || dim <= 0 || vocab <= 0 || dx == nullptr || ids == nullptr ||
+      dweight == nullptr || next_scratch == nullptr || head_scratch == nullptr)
+    return -2;
+  const size_t smem = static_cast<size_t>(rows) * sizeof(int);
+  if (smem > 200 * 1024) return -2;  // ids must fit in shared memory; callers fall back
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(embedding_links_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  cudaError_t e = cudaMemsetAsync(head_scratch, 0xFF, static_cast<size_t>(vocab) * sizeof(int),
+                                  SFL_STREAM(stream));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const int ctas = grid_for(rows, 256, 148);
+  embedding_links_kernel<<<ctas, 256, smem, SFL_STREAM(stream)>>>(ids, rows, vocab, next_scratch,
+                                                                  head_scratch);
+  embedding_bwd_kernel<<<vocab, 128, 0, SFL_STREAM(stream)>>>(dx, next_scratch, head_scratch,
+                                                              dweight, dim, accumulate);
   SFL_RET();
 }
 

@@ -301,6 +301,12 @@ int sfl_scale_f32(float* x, long n, const float* coef_dev, float scale, void* st
 /* out fp32 [rows, dim] = weight[ids[row]] */
 int sfl_embedding_fwd(const float* weight, const int64_t* ids, float* out, int rows, int dim,
                       int vocab, void* stream);
+/* dweight fp32 [vocab, dim] (+)= scatter-add of dx fp32 [rows, dim] by ids, added in row
+ * order (deterministic).  next_scratch: rows ints, head_scratch: vocab ints.  rows is
+ * limited by shared memory (51200); returns -2 beyond that. */
+int sfl_embedding_bwd(const float* dx, const int64_t* ids, float* dweight, int rows, int dim,
+                      int vocab, int accumulate, int* next_scratch, int* head_scratch,
+                      void* stream);
 /* Library build tag, for diagnostics. */
 const char* sfl_version(void);
 /* Writes sizeof(SflGemmEpilogue), sizeof(SflWgradProblem), sizeof(SflAttnTensor),

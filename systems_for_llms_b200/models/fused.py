@@ -543,14 +543,15 @@ class _Embed(torch.autograd.Function):
     def backward(ctx, grad):
         (ids,) = ctx.saved_tensors
         engine, weight = ctx.engine, ctx.weight
-        dense = torch.ops.aten.embedding_dense_backward(
-            grad.reshape(-1, grad.shape[-1]), ids.reshape(-1), weight.shape[0], -1, False)
         accumulate = engine.claim(weight)
         view = engine.grad_view(weight)
-        if accumulate:
-            view.add_(dense)
-        else:
-            view.copy_(dense)
+        if not K.embedding_bwd(grad, ids, view, accumulate):    # more tokens than the kernel takes
+            dense = torch.ops.aten.embedding_dense_backward(
+                grad.reshape(-1, grad.shape[-1]), ids.reshape(-1), weight.shape[0], -1, False)
+            if accumulate:
+                view.add_(dense)
+            else:
+                view.copy_(dense)
         if engine.on_block_backward is not None:
             engine.on_block_backward(0)
         return None, None, None

@@ -78,6 +78,34 @@ def embedding(weight: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
     return out.view(*ids.shape, weight.shape[1])
 
 
+EMBEDDING_BWD_MAX_ROWS = 51200     # the ids of one call must fit in shared memory
+
+
+def embedding_bwd(dx: torch.Tensor, ids: torch.Tensor, dweight: torch.Tensor,
+                  accumulate: bool) -> bool:
+    """``dweight[ids[t]] (+)= dx[t]`` summed in token order (deterministic, no sort, no
+    dense temporary).  Returns False, without touching ``dweight``, when the call
+    has more tokens than the kernel handles; the caller then uses another route."""
+    flat = ids.reshape(-1).contiguous()
+    if flat.dtype != torch.int64:
+        flat = flat.to(torch.int64)
+    rows, dim = flat.numel(), dweight.shape[1]
+    if rows > EMBEDDING_BWD_MAX_ROWS:
+        return False
+    dx2 = dx.reshape(rows, dim)
+    if dx2.dtype != torch.float32 or not dx2.is_contiguous():
+        dx2 = dx2.float().contiguous()
+    if dweight.dtype != torch.float32 or not dweight.is_contiguous():
+        raise ValueError("embedding gradients are fp32 and contiguous")
+    scratch = torch.empty(rows + dweight.shape[0], dtype=torch.int32, device=dx.device)
+    code = _lib.lib().sfl_embedding_bwd(dx2.data_ptr(), flat.data_ptr(), dweight.data_ptr(), rows,
+                                       dim, dweight.shape[0], int(accumulate),
+                                       scratch.data_ptr(), scratch[rows:].data_ptr(),
+                                       _lib.stream_ptr())
+    _lib.check(code, "sfl_embedding_bwd")
+    return True
+
+
 def cross_entropy_rows(logits: torch.Tensor, targets: torch.Tensor, vocab: int,
                        dlogits: torch.Tensor | None, grad_scale: float) -> torch.Tensor:
     """Per-row loss of bf16 ``logits[rows, ld]`` over the first ``vocab`` columns.

@@ -89,6 +89,7 @@ _SIGNATURES = {
     "sfl_cast_f32_to_bf16": [_P, _P, c_long, _P],
     "sfl_scale_f32": [_P, c_long, _P, c_float, _P],
     "sfl_embedding_fwd": [_P, _P, _P, c_int, c_int, c_int, _P],
+    "sfl_embedding_bwd": [_P, _P, _P, c_int, c_int, c_int, c_int, _P, _P, _P],
 }
 _OPTIONAL: dict[str, list] = {}
 
@@ -100,7 +101,7 @@ def register_signature(name: str, argtypes: list) -> None:
 
 
 # Kernels launched per call of each entry point (default 1, 0 for host-only calls).
-_KERNELS_PER_CALL = {"sfl_attn_bwd": 2, "sfl_block_forward": 7, "sfl_block_backward": 12,
+_KERNELS_PER_CALL = {"sfl_attn_bwd": 2, "sfl_embedding_bwd": 2, "sfl_block_forward": 7, "sfl_block_backward": 12,
                      "sfl_block_saved_bytes": 0, "sfl_block_scratch_bytes": 0, "sfl_rmsnorm_bwd_blocks": 0, "sfl_sqnorm_blocks": 0,
                      "sfl_ipc_alloc": 0, "sfl_ipc_free": 0, "sfl_ipc_get_handle": 0,
                      "sfl_ipc_open_handle": 0, "sfl_ipc_close_handle": 0,

@@ -194,3 +194,29 @@ def test_adamw_and_norm(dev):
                  weight_decay=0.1, coef=bad[1:2], ok_flag=bad[2:3])
     check(dev)
     assert torch.equal(p, before) and bad[2].item() == 0.0
+
+
+@pytest.mark.parametrize("rows,dim,vocab,skew", [(4096, 1024, 10000, False), (777, 96, 50, True),
+                                                 (2048, 130, 1000, True)])
+def test_embedding_backward_is_a_deterministic_scatter_add(dev, rows, dim, vocab, skew):
+    """Against an fp64 index_add; bitwise repeatable; accumulate and overwrite modes;
+    ``skew`` makes a few ids very frequent (long chains) and leaves many rows unused."""
+    from systems_for_llms_b200.ops import functional as K
+    torch.manual_seed(rows + dim)
+    ids = torch.randint(0, vocab, (rows,), device=dev)
+    if skew:
+        ids[torch.rand(rows, device=dev) < 0.5] = 3
+    dx = torch.randn(rows, dim, device=dev)
+    expected = torch.zeros(vocab, dim, device=dev, dtype=torch.float64).index_add_(0, ids, dx.double())
+    grad = torch.full((vocab, dim), 7.0, device=dev)          # overwrite must clear stale values
+    assert K.embedding_bwd(dx, ids, grad, False)
+    first = grad.clone()
+    torch.testing.assert_close(grad.double(), expected, rtol=1e-5, atol=1e-3)
+    grad.fill_(-1.0)
+    assert K.embedding_bwd(dx, ids, grad, False)
+    assert torch.equal(grad, first)                            # same order of additions every time
+    assert K.embedding_bwd(dx, ids.view(1, rows), grad, True)  # second microbatch accumulates
+    torch.testing.assert_close(grad.double(), 2 * expected, rtol=1e-5, atol=2e-3)
+    too_many = torch.zeros(K.EMBEDDING_BWD_MAX_ROWS + 1, dtype=torch.int64, device=dev)
+    assert not K.embedding_bwd(torch.zeros(too_many.numel(), 8, device=dev), too_many,
+                               torch.zeros(4, 8, device=dev), False)
