@@ -78,9 +78,12 @@ __device__ __forceinline__ bool ready_barrier(const CommView& c, int slot, uint3
 __device__ __forceinline__ void done_barrier(const CommView& c, int slot, uint32_t epoch,
                                              int* status) {
   __shared__ int last;
-  __threadfence_system();
+  // The block barrier orders every thread's stores before thread 0's fence, which
+  // is cumulative: one system fence per block instead of one per thread (each
+  // waits for the block's outstanding peer stores, and 256 of them queue up).
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     const uint32_t arrived = atomicAdd(counter_ptr(c.flags[c.rank], slot), 1u);
     last = arrived == gridDim.x - 1;
   }
