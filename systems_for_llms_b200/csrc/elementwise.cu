@@ -397,6 +397,17 @@ __global__ void scale_f32_kernel(float* __restrict__ x, long n, const float* __r
     x[i] *= c;
 }
 
+// x *= *coef for bf16 data, and nothing at all when *coef is exactly 1: the gradient
+// that arrives at a loss is almost always the constant one, known only on the device.
+__global__ void scale_bf16_unless_one_kernel(__nv_bfloat16* __restrict__ x, long n,
+                                             const float* __restrict__ coef) {
+  const float c = *coef;
+  if (c == 1.0f) return;
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+    x[i] = __float2bfloat16_rn(__bfloat162float(x[i]) * c);
+}
+
 __global__ void embedding_fwd_kernel(const float* __restrict__ weight,
                                      const int64_t* __restrict__ ids, float* __restrict__ out,
                                      int rows, int dim, int vocab) {
@@ -417,12 +428,15 @@ __global__ void embedding_fwd_kernel(const float* __restrict__ weight,
 // in token order so the result does not depend on scheduling (the reference relies
 // on autograd's embedding backward, src/llmlab/model/layers.py:60-74).  Two kernels:
 // the first links the tokens of each id into a chain (next[t] = next later token with
-// the same id, head[v] = its first token), scanning the ids in shared memory; the
-// second walks one chain per vocabulary row.  No sort, no dense temporary.
-__global__ void __launch_bounds__(256)
+// the same id, found by scanning the ids in shared memory; head[v] = its first token,
+// by atomicMin); the second walks one chain per vocabulary row.  No sort, no dense
+// temporary.
+constexpr int kNoToken = 0x7F7F7F7F;  // what a byte-wise memset of 0x7F leaves in head[]
+
+__global__ void __launch_bounds__(64)
 embedding_links_kernel(const int64_t* __restrict__ ids, int rows, int vocab,
                        int* __restrict__ next, int* __restrict__ head) {
-  extern __shared__ int sid[];
+  extern __shared__ __align__(16) int sid[];
   for (int i = threadIdx.x; i < rows; i += blockDim.x) {
     const int64_t v = ids[i];
     sid[i] = (v < 0 || v >= vocab) ? 0 : static_cast<int>(v);  // same clamp as the forward
@@ -430,20 +444,26 @@ embedding_links_kernel(const int64_t* __restrict__ ids, int rows, int vocab,
   __syncthreads();
   for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < rows; t += gridDim.x * blockDim.x) {
     const int id = sid[t];
+    atomicMin(head + id, t);  // the first token of the id, whatever the arrival order
+    // next later token with the same id: scalar up to a 16-byte boundary, then four
+    // ids per shared-memory load
     int nx = -1;
-    for (int u = t + 1; u < rows; ++u)
-      if (sid[u] == id) {
-        nx = u;
-        break;
+    int u = t + 1;
+    for (; u < rows && (u & 3) != 0 && nx < 0; ++u)
+      if (sid[u] == id) nx = u;
+    if (nx < 0) {
+      for (; u + 3 < rows; u += 4) {
+        const int4 q = *reinterpret_cast<const int4*>(sid + u);
+        if (q.x == id || q.y == id || q.z == id || q.w == id) {
+          nx = q.x == id ? u : q.y == id ? u + 1 : q.z == id ? u + 2 : u + 3;
+          break;
+        }
       }
+      if (nx < 0)
+        for (; u < rows && nx < 0; ++u)
+          if (sid[u] == id) nx = u;
+    }
     next[t] = nx;
-    bool first = true;
-    for (int u = t - 1; u >= 0; --u)
-      if (sid[u] == id) {
-        first = false;
-        break;
-      }
-    if (first) head[id] = t;  // exactly one token per id gets here
   }
 }
 
@@ -454,7 +474,7 @@ embedding_bwd_kernel(const float* __restrict__ dx, const int* __restrict__ next,
   const int v = blockIdx.x;
   float* dst = dweight + static_cast<long>(v) * dim;
   int t = head[v];
-  if (t < 0) {
+  if (t == kNoToken) {
     if (!accumulate)
       for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = 0.f;
     return;
@@ -596,6 +616,15 @@ extern "C" int sfl_scale_f32(float* x, long n, const float* coef, float scale, v
   SFL_RET();
 }
 
+extern "C" int sfl_scale_bf16_unless_one(void* x_bf16, long n, const float* coef_dev,
+                                         void* stream) {
+  if (x_bf16 == nullptr || coef_dev == nullptr || n < 0) return -2;
+  if (n == 0) return 0;
+  scale_bf16_unless_one_kernel<<<grid_for(n, 256), 256, 0, SFL_STREAM(stream)>>>(
+      static_cast<__nv_bfloat16*>(x_bf16), n, coef_dev);
+  SFL_RET();
+}
+
 extern "C" int sfl_embedding_fwd(const float* weight, const int64_t* ids, float* out, int rows,
                                  int dim, int vocab, void* stream) {
   if (rows <= 0) return -2;
@@ -618,12 +647,12 @@ extern "C" int sfl_embedding_bwd(const float* dx, const int64_t* ids, float* dwe
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  cudaError_t e = cudaMemsetAsync(head_scratch, 0xFF, static_cast<size_t>(vocab) * sizeof(int),
+  cudaError_t e = cudaMemsetAsync(head_scratch, 0x7F, static_cast<size_t>(vocab) * sizeof(int),
                                   SFL_STREAM(stream));
   if (e != cudaSuccess) return static_cast<int>(e);
-  const int ctas = grid_for(rows, 256, 148);
-  embedding_links_kernel<<<ctas, 256, smem, SFL_STREAM(stream)>>>(ids, rows, vocab, next_scratch,
-                                                                  head_scratch);
+  const int ctas = grid_for(rows, 64, 148 * 2);
+  embedding_links_kernel<<<ctas, 64, smem, SFL_STREAM(stream)>>>(ids, rows, vocab, next_scratch,
+                                                                 head_scratch);
   embedding_bwd_kernel<<<vocab, 128, 0, SFL_STREAM(stream)>>>(dx, next_scratch, head_scratch,
                                                               dweight, dim, accumulate);
   SFL_RET();

@@ -271,7 +271,8 @@ int sfl_allreduce_rows_f32(const SflComm* comm, long in_off_bytes, long out_off_
  * a peer mapping (CUDA IPC) unless r == rank. */
 typedef struct SflTpFuse {
   int rank, world;      /* 2 <= world <= 8                                            */
-  void* stage[8];       /* staging for partial tiles: sfl_gemm_tp_stage_bytes each    */
+  void* stage[8];       /* staging for partial tiles (opaque layout of 4 KB blocks):  *
+                         * sfl_gemm_tp_stage_bytes each                                */
   void* out[8];         /* result buffers                                             */
   void* tile_flags[8];  /* tile arrival words: sfl_gemm_tp_tile_flag_bytes, zeroed    */
   void* flags[8];       /* barrier flag buffers (sfl_comm_flag_bytes)                 */
@@ -298,6 +299,8 @@ int sfl_gemm_tp_reduce(const void* a, long lda, const void* b, long ldb, int b_m
 /* ------------------------------------------------------------------ misc -- */
 int sfl_cast_f32_to_bf16(const float* x, void* y_bf16, long n, void* stream);
 int sfl_scale_f32(float* x, long n, const float* coef_dev, float scale, void* stream);
+/* bf16 x *= *coef_dev; returns at once on the device when *coef_dev == 1. */
+int sfl_scale_bf16_unless_one(void* x_bf16, long n, const float* coef_dev, void* stream);
 /* out fp32 [rows, dim] = weight[ids[row]] */
 int sfl_embedding_fwd(const float* weight, const int64_t* ids, float* out, int rows, int dim,
                       int vocab, void* stream);

@@ -610,6 +610,6 @@ class _HeadLoss(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad):
         dlogits, *saved = ctx.saved_tensors
-        dlogits.mul_(grad.to(torch.bfloat16))
+        K.scale_bf16_unless_one(dlogits, grad)    # the incoming gradient is normally 1
         dx = head_backward(ctx.engine, saved, dlogits)
         return dx.view(ctx.shape), None, None, None

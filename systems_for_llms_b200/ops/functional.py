@@ -78,6 +78,18 @@ def embedding(weight: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
     return out.view(*ids.shape, weight.shape[1])
 
 
+def scale_bf16_unless_one(x: torch.Tensor, coef: torch.Tensor) -> None:
+    """In place ``x *= coef`` for contiguous bf16 ``x`` and a one-element fp32 device
+    tensor; the kernel returns immediately when the factor is exactly one."""
+    if x.dtype != torch.bfloat16 or not x.is_contiguous():
+        raise ValueError("expects a contiguous bf16 tensor")
+    if coef.dtype != torch.float32 or coef.numel() != 1 or coef.device != x.device:
+        coef = coef.reshape(-1)[:1].to(device=x.device, dtype=torch.float32)
+    code = _lib.lib().sfl_scale_bf16_unless_one(x.data_ptr(), x.numel(), coef.data_ptr(),
+                                               _lib.stream_ptr())
+    _lib.check(code, "sfl_scale_bf16_unless_one")
+
+
 EMBEDDING_BWD_MAX_ROWS = 51200     # the ids of one call must fit in shared memory
 
 

@@ -88,6 +88,7 @@ _SIGNATURES = {
                   c_float, c_float, _P, c_float, _P, _P],
     "sfl_cast_f32_to_bf16": [_P, _P, c_long, _P],
     "sfl_scale_f32": [_P, c_long, _P, c_float, _P],
+    "sfl_scale_bf16_unless_one": [_P, c_long, _P, _P],
     "sfl_embedding_fwd": [_P, _P, _P, c_int, c_int, c_int, _P],
     "sfl_embedding_bwd": [_P, _P, _P, c_int, c_int, c_int, c_int, _P, _P, _P],
 }

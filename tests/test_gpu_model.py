@@ -70,6 +70,23 @@ def test_fused_matches_portable(dev, ckpt):
     check_status()
 
 
+def test_gradient_arriving_at_the_loss_is_applied(dev):
+    """The head skips its scaling pass when the incoming gradient is exactly one; any
+    other factor (a caller scaling the loss) must still reach every parameter."""
+    model = build(dev)
+    x = torch.randint(0, 1000, (2, 256), device=dev)
+    y = torch.randint(0, 1000, (2, 256), device=dev)
+    grads = []
+    for factor in (1.0, -2.5):
+        model.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = model.loss(x, y, 1.0)
+        (loss * factor).backward()
+        grads.append([p.grad.clone() for p in model.parameters()])
+    for unit, scaled in zip(*grads):
+        assert relative(scaled, -2.5 * unit) < 0.02
+
+
 def test_shadow_follows_external_parameter_changes(dev):
     model = build(dev)
     x = torch.randint(0, 1000, (2, 128), device=dev)
