@@ -8,6 +8,8 @@
     python -m systems_for_llms_b200.ops.microbench mma         # tcgen05.mma issue-rate test
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
         -m systems_for_llms_b200.ops.microbench tp             # GEMM + all-reduce, one kernel vs two
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
+        -m systems_for_llms_b200.ops.microbench comm           # peer-memory collectives vs NCCL
 
 Each timing is the median of CUDA-event measurements with a 256 MB buffer
 written between launches, so operands come from HBM rather than from a warm L2.
@@ -318,6 +320,90 @@ def tensor_parallel_table(iters: int = 30) -> dict:
     return {"rank": rank, "world": world, "rows": rows, "w2_resid_phase_us": phases}
 
 
+LINK_GBS = 770.0      # measured peer copy, per direction per GPU, on this pool's NVLink 5
+
+
+def collective_table(iters: int = 10) -> dict:
+    """The data-parallel collectives at the size of the 324M gradient (one process per
+    GPU): this library's peer-memory kernels against ``torch.distributed`` (NCCL),
+    CUDA-event time as the max over ranks, and the fraction of the link roofline
+    (bytes that must enter each GPU over NVLink / 770 GB/s)."""
+    import os
+
+    import torch.distributed as dist
+
+    from ..parallel.comm import PeerComm, SymmetricBuffer
+    from .gemm import check_status
+    rank, world, local = (int(os.environ[k]) for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=device)
+    comm = PeerComm(device, ctas=32)
+    n = 324_000_000 // (4 * world * 64) * (4 * world * 64)      # fp32 elements, sliceable
+    grads = SymmetricBuffer(n * 4, device)
+    params, shadows = SymmetricBuffer(n * 4, device), SymmetricBuffer(n * 2, device)
+    flat = grads.view(torch.float32, n)
+    flat.normal_()
+    per = n // world
+    shard, m, v = (torch.zeros(per, device=device) for _ in range(3))
+    plain = torch.randn(n, device=device)
+    pieces = torch.empty(n, device=device, dtype=torch.bfloat16)
+    piece = torch.randn(per, device=device).bfloat16()
+    stats = torch.tensor([1.0, 1.0, 1.0], device=device)
+    slots = iter(range(0, 48))
+
+    def timed(fn) -> float:
+        for _ in range(2):
+            fn()
+        samples = []
+        for _ in range(iters):
+            dist.barrier()
+            torch.cuda.synchronize()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            fn()
+            end.record()
+            end.synchronize()
+            samples.append(begin.elapsed_time(end) * 1000)
+        worst = torch.tensor(statistics.median(samples), device=device)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        return worst.item()
+
+    s_ar, s_rs, s_ag, s_gather = (next(slots) for _ in range(4))
+    share = (world - 1) / world
+    cases = [
+        # name, ours, NCCL, bytes entering each GPU
+        ("allreduce_f32 (+1/W scale, norm partials)",
+         lambda: comm.allreduce(grads, 0, n, 1.0 / world, s_ar),
+         lambda: dist.all_reduce(plain), 2 * share * n * 4),
+        ("reduce_scatter_f32 (+scale, norm partials)",
+         lambda: comm.reduce_scatter(grads, 0, n, 1.0 / world, shard, s_rs),
+         lambda: dist.reduce_scatter_tensor(shard, plain), share * n * 4),
+        ("adamw + all-gather (fp32 params, bf16 copies)",
+         lambda: comm.adamw_allgather(params, shadows, 0, n, shard, m, v, step=1, lr=1e-3,
+                                      beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1,
+                                      coef=stats[1:2], ok=stats[2:3], slot=s_ag),
+         lambda: dist.all_gather_into_tensor(plain, shard), share * n * 6),
+        ("all-gather of bf16 shards (pull)",
+         lambda: comm.allgather_bytes(shadows, 0, per * 2, s_gather),
+         lambda: dist.all_gather_into_tensor(pieces, piece), share * n * 2),
+    ]
+    rows = []
+    for name, ours, nccl, link_bytes in cases:
+        mine, theirs = timed(ours), timed(nccl)
+        floor = link_bytes / (LINK_GBS * 1e9) * 1e6
+        rows.append({"op": name, "us": mine, "nccl_us": theirs, "link_mb": link_bytes / 2 ** 20,
+                     "link_floor_us": floor, "frac_of_link_roofline": floor / mine})
+    torch.cuda.synchronize()
+    check_status()
+    dist.barrier()
+    for buffer in (grads, params, shadows):
+        buffer.close()
+    comm.close()
+    dist.destroy_process_group()
+    return {"rank": rank, "world": world, "elements": n, "rows": rows}
+
+
 def mma_issue_rate() -> str:
     """Compile ops/mma_issue_rate.cu for sm_100a into a temporary directory and run it."""
     import subprocess
@@ -337,7 +423,7 @@ def mma_issue_rate() -> str:
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__,
                                      formatter_class=argparse.RawDescriptionHelpFormatter)
-    parser.add_argument("what", choices=[*SUITES, "step", "once", "mma", "tp"])
+    parser.add_argument("what", choices=[*SUITES, "step", "once", "mma", "tp", "comm"])
     parser.add_argument("name", nargs="?", help="operation for 'once' (e.g. w13_swiglu, attn_bwd)")
     parser.add_argument("--repeat", type=int, default=3)
     parser.add_argument("--json", action="store_true")
@@ -346,6 +432,19 @@ def main() -> None:
         raise SystemExit("a CUDA GPU is required")
     if args.what == "mma":
         print(mma_issue_rate(), end="")
+        return
+    if args.what == "comm":
+        table = collective_table()
+        if table["rank"] == 0:
+            if args.json:
+                print(json.dumps(table))
+                return
+            print(f"{table['world']} ranks, {table['elements']} fp32 elements; microseconds, max over "
+                  f"ranks; link roofline = bytes entering a GPU / {LINK_GBS:.0f} GB/s")
+            for row in table["rows"]:
+                print(f"{row['op']:46s} {row['us']:9.1f}  NCCL {row['nccl_us']:9.1f}  "
+                      f"{row['link_mb']:8.1f} MB  floor {row['link_floor_us']:8.1f}  "
+                      f"{row['frac_of_link_roofline']:.2f} of link roofline")
         return
     if args.what == "tp":
         table = tensor_parallel_table()

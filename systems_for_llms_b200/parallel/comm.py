@@ -150,6 +150,11 @@ class PeerComm:
         self.flags = SymmetricBuffer(handle.sfl_comm_flag_bytes(), device, group)
         self.slots = handle.sfl_comm_slots()
         self.ctas = min(ctas, handle.sfl_comm_max_ctas())
+        # The optimizer pass runs after backward with the GPU to itself: its kernels
+        # (AdamW arithmetic on 34 bytes per element plus the parameter push) take the
+        # whole machine instead of the few CTAs that collectives overlapped with
+        # backward are limited to.
+        self.update_ctas = handle.sfl_comm_max_ctas()
         self._epochs = [0] * self.slots
         self.status = status_word(self.device)
         self._structs: dict = {}
@@ -216,7 +221,7 @@ class PeerComm:
             ctypes.byref(self.struct(params, shadows)), offset, count, grad.data_ptr(),
             exp_avg.data_ptr(), exp_avg_sq.data_ptr(), lr, beta1, beta2, eps, weight_decay,
             1.0 - beta1 ** step, 1.0 - beta2 ** step, _lib.ptr(coef), _lib.ptr(ok), slot,
-            self.next_epoch(slot), self.ctas, self.status.data_ptr(), _lib.stream_ptr())
+            self.next_epoch(slot), self.update_ctas, self.status.data_ptr(), _lib.stream_ptr())
         _lib.check(code, "sfl_adamw_allgather")
 
     def adamw_allgather_ranges(self, params: SymmetricBuffer, shadows: SymmetricBuffer,
@@ -238,7 +243,8 @@ class PeerComm:
             ctypes.byref(self.struct(params, shadows)), ranges.data_ptr(), ranges.shape[0],
             grad.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr(), lr, beta1, beta2, eps,
             weight_decay, 1.0 - beta1 ** step, 1.0 - beta2 ** step, _lib.ptr(coef), _lib.ptr(ok),
-            slot, self.next_epoch(slot), self.ctas, self.status.data_ptr(), _lib.stream_ptr())
+            slot, self.next_epoch(slot), self.update_ctas, self.status.data_ptr(),
+            _lib.stream_ptr())
         _lib.check(code, "sfl_adamw_allgather_ranges")
 
     def allgather_bytes(self, buffer: SymmetricBuffer, offset_bytes: int, chunk_bytes: int,
