@@ -14,7 +14,8 @@ Two numbers are reported.  ``value`` is timed on the device with CUDA events
 around exactly K optimizer steps whose token batches already sit in device
 memory; ``e2e.value`` goes through the public step function
 (``parallel.train.train_step``): per step it samples the global batch, copies
-each microbatch from pinned host memory, and reads loss and gradient norm back.
+each microbatch from pinned host memory, and reads loss and gradient norm back;
+that loop runs W warm-up steps of its own before its K timed ones.
 Both are the maximum over ranks.  ``--impl reference`` runs the unmodified
 reference package installed under ``baseline/_ref`` through its own runner and
 reports its own throughput figure in the same JSON shape.
