@@ -338,27 +338,66 @@ __global__ void norm_finalize_kernel(const float* __restrict__ partial, int n, f
   }
 }
 
+// One AdamW update, in the operation order of torch.optim.AdamW (single-tensor path).
+__device__ __forceinline__ void adamw_one(float& pi, float gi, float& mi, float& vi, float lr,
+                                          float beta1, float beta2, float eps, float wd,
+                                          float step_size, float bias2_sqrt, float grad_scale,
+                                          bool has_coef, float coef) {
+  if (grad_scale != 1.0f) gi *= grad_scale;
+  if (has_coef) gi *= coef;
+  pi = pi * (1.0f - lr * wd);
+  mi = mi + (gi - mi) * (1.0f - beta1);
+  vi = vi * beta2 + (1.0f - beta2) * gi * gi;
+  const float denom = sqrtf(vi) / bias2_sqrt + eps;
+  pi = pi - step_size * (mi / denom);
+}
+
+// Four elements per thread and trip (16-byte loads and stores on every stream) when
+// the arrays allow it; 34 bytes move per element, so the kernel is pure bandwidth.
 __global__ void __launch_bounds__(256)
 adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
              float* __restrict__ v, __nv_bfloat16* __restrict__ shadow, long n, float lr,
              float beta1, float beta2, float eps, float wd, float bias1, float bias2_sqrt,
              const float* __restrict__ grad_coef, float grad_scale,
-             const float* __restrict__ ok_flag) {
+             const float* __restrict__ ok_flag, int vectorized) {
   if (ok_flag != nullptr && *ok_flag == 0.0f) return;
-  const float coef = grad_coef != nullptr ? *grad_coef : 1.0f;
+  const bool has_coef = grad_coef != nullptr;
+  const float coef = has_coef ? *grad_coef : 1.0f;
   const float step_size = lr / bias1;
   const long stride = static_cast<long>(gridDim.x) * blockDim.x;
-  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
-    // Same operation order as torch.optim.AdamW (single-tensor path).
-    float gi = g[i];
-    if (grad_scale != 1.0f) gi *= grad_scale;
-    if (grad_coef != nullptr) gi *= coef;
-    float pi = p[i] * (1.0f - lr * wd);
-    float mi = m[i];
-    mi = mi + (gi - mi) * (1.0f - beta1);
-    float vi = v[i] * beta2 + (1.0f - beta2) * gi * gi;
-    const float denom = sqrtf(vi) / bias2_sqrt + eps;
-    pi = pi - step_size * (mi / denom);
+  const long i0 = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  long done = 0;
+  if (vectorized) {
+    const long n4 = n >> 2;
+    for (long i = i0; i < n4; i += stride) {
+      float4 p4 = reinterpret_cast<float4*>(p)[i];
+      const float4 g4 = reinterpret_cast<const float4*>(g)[i];
+      float4 m4 = reinterpret_cast<float4*>(m)[i];
+      float4 v4 = reinterpret_cast<float4*>(v)[i];
+      adamw_one(p4.x, g4.x, m4.x, v4.x, lr, beta1, beta2, eps, wd, step_size, bias2_sqrt,
+                grad_scale, has_coef, coef);
+      adamw_one(p4.y, g4.y, m4.y, v4.y, lr, beta1, beta2, eps, wd, step_size, bias2_sqrt,
+                grad_scale, has_coef, coef);
+      adamw_one(p4.z, g4.z, m4.z, v4.z, lr, beta1, beta2, eps, wd, step_size, bias2_sqrt,
+                grad_scale, has_coef, coef);
+      adamw_one(p4.w, g4.w, m4.w, v4.w, lr, beta1, beta2, eps, wd, step_size, bias2_sqrt,
+                grad_scale, has_coef, coef);
+      reinterpret_cast<float4*>(p)[i] = p4;
+      reinterpret_cast<float4*>(m)[i] = m4;
+      reinterpret_cast<float4*>(v)[i] = v4;
+      if (shadow != nullptr) {
+        uint2 o;
+        o.x = pack_bf16(p4.x, p4.y);
+        o.y = pack_bf16(p4.z, p4.w);
+        reinterpret_cast<uint2*>(shadow)[i] = o;
+      }
+    }
+    done = n4 << 2;
+  }
+  for (long i = done + i0; i < n; i += stride) {
+    float pi = p[i], mi = m[i], vi = v[i];
+    adamw_one(pi, g[i], mi, vi, lr, beta1, beta2, eps, wd, step_size, bias2_sqrt, grad_scale,
+              has_coef, coef);
     p[i] = pi;
     m[i] = mi;
     v[i] = vi;
@@ -598,9 +637,13 @@ extern "C" int sfl_adamw(float* p, const float* g, float* m, float* v, void* sha
                          float bias2, const float* grad_coef, float grad_scale,
                          const float* ok_flag, void* stream) {
   if (n <= 0) return 0;
-  adamw_kernel<<<grid_for(n, 256, 148 * 16), 256, 0, SFL_STREAM(stream)>>>(
+  const uintptr_t all = reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) |
+                        reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v);
+  const int vectorized = (all & 15) == 0 && (reinterpret_cast<uintptr_t>(shadow) & 7) == 0;
+  adamw_kernel<<<grid_for(vectorized ? (n + 3) / 4 : n, 256, 148 * 16), 256, 0,
+                 SFL_STREAM(stream)>>>(
       p, g, m, v, static_cast<__nv_bfloat16*>(shadow), n, lr, beta1, beta2, eps, wd, bias1,
-      sqrtf(bias2), grad_coef, grad_scale, ok_flag);
+      sqrtf(bias2), grad_coef, grad_scale, ok_flag, vectorized);
   SFL_RET();
 }
 
