@@ -268,17 +268,18 @@ cross_entropy_kernel(const __nv_bfloat16* __restrict__ logits, long ld,
   __shared__ float scratch[33];
   const int row = blockIdx.x;
   const __nv_bfloat16* lr = logits + static_cast<long>(row) * ld;
+  // The gradient may overwrite the logits in place: fetch the target's logit before
+  // any thread of the block can have stored anything.
+  const int64_t tgt = targets[row];
+  const bool tgt_ok = tgt >= 0 && tgt < vocab;
+  const float target_logit = (threadIdx.x == 0 && tgt_ok) ? __bfloat162float(lr[tgt]) : 0.f;
   float mx = -INFINITY;
   for (int i = threadIdx.x; i < vocab; i += blockDim.x) mx = fmaxf(mx, __bfloat162float(lr[i]));
   mx = block_max(mx, scratch);
   float sum = 0.f;
   for (int i = threadIdx.x; i < vocab; i += blockDim.x) sum += expf(__bfloat162float(lr[i]) - mx);
   sum = block_sum(sum, scratch);
-  const int64_t tgt = targets[row];
-  if (threadIdx.x == 0) {
-    const float tl = (tgt >= 0 && tgt < vocab) ? __bfloat162float(lr[tgt]) - mx : 0.f;
-    row_loss[row] = logf(sum) - tl;
-  }
+  if (threadIdx.x == 0) row_loss[row] = logf(sum) - (tgt_ok ? target_logit - mx : 0.f);
   if (dlogits != nullptr) {
     __nv_bfloat16* dr = dlogits + static_cast<long>(row) * ld;
     const float inv = 1.0f / sum;
@@ -286,6 +287,78 @@ cross_entropy_kernel(const __nv_bfloat16* __restrict__ logits, long ld,
       float p = expf(__bfloat162float(lr[i]) - mx) * inv;
       if (i == tgt) p -= 1.0f;
       dr[i] = __float2bfloat16_rn(p * grad_scale);
+    }
+  }
+}
+
+// The same for rows that fit in registers (vocab a multiple of 8 and at most
+// 256 x 8 x 8 = 16384, 16-byte aligned rows): the row is read once with 16-byte
+// loads, exp is evaluated once per element and the gradient leaves as 16-byte
+// stores.
+constexpr int kCeVecs = 8;  // 16-byte vectors per thread
+__global__ void __launch_bounds__(256)
+cross_entropy_vec_kernel(const __nv_bfloat16* __restrict__ logits, long ld,
+                         const int64_t* __restrict__ targets, float* __restrict__ row_loss,
+                         __nv_bfloat16* __restrict__ dlogits, float grad_scale, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  const int row = blockIdx.x;
+  const __nv_bfloat16* lr = logits + static_cast<long>(row) * ld;
+  const int nvec = vocab >> 3;
+  const int64_t tgt = targets[row];
+  const bool tgt_ok = tgt >= 0 && tgt < vocab;
+  const float target_logit = (threadIdx.x == 0 && tgt_ok) ? __bfloat162float(lr[tgt]) : 0.f;
+  float e[kCeVecs][8];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int k = 0; k < kCeVecs; ++k) {
+    const int idx = threadIdx.x + k * 256;
+    if (idx < nvec) {
+      const uint4 q = *reinterpret_cast<const uint4*>(lr + idx * 8);
+      const float2 a = unpack_bf16(q.x), b = unpack_bf16(q.y), c = unpack_bf16(q.z),
+                   d = unpack_bf16(q.w);
+      e[k][0] = a.x; e[k][1] = a.y; e[k][2] = b.x; e[k][3] = b.y;
+      e[k][4] = c.x; e[k][5] = c.y; e[k][6] = d.x; e[k][7] = d.y;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mx = fmaxf(mx, e[k][j]);
+    }
+  }
+  mx = block_max(mx, scratch);
+  float sum = 0.f;
+#pragma unroll
+  for (int k = 0; k < kCeVecs; ++k) {
+    if (threadIdx.x + k * 256 < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        e[k][j] = expf(e[k][j] - mx);
+        sum += e[k][j];
+      }
+    }
+  }
+  sum = block_sum(sum, scratch);
+  if (threadIdx.x == 0) row_loss[row] = logf(sum) - (tgt_ok ? target_logit - mx : 0.f);
+  if (dlogits != nullptr) {
+    __nv_bfloat16* dr = dlogits + static_cast<long>(row) * ld;
+    const float inv = 1.0f / sum;
+#pragma unroll
+    for (int k = 0; k < kCeVecs; ++k) {
+      const int idx = threadIdx.x + k * 256;
+      if (idx < nvec) {
+        float p[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          p[j] = e[k][j] * inv;
+          if (idx * 8 + j == tgt) p[j] -= 1.0f;
+          p[j] *= grad_scale;
+        }
+        uint4 o;
+        o.x = pack_bf16(p[0], p[1]);
+        o.y = pack_bf16(p[2], p[3]);
+        o.z = pack_bf16(p[4], p[5]);
+        o.w = pack_bf16(p[6], p[7]);
+        *reinterpret_cast<uint4*>(dr + idx * 8) = o;
+      }
     }
   }
 }
@@ -610,6 +683,11 @@ extern "C" int sfl_cross_entropy(const void* logits, long ld, const int64_t* tar
                                  float* row_loss, void* dlogits, float grad_scale, int rows,
                                  int vocab, void* stream) {
   if (rows <= 0 || vocab <= 0) return -2;
+  const uintptr_t bases = reinterpret_cast<uintptr_t>(logits) | reinterpret_cast<uintptr_t>(dlogits);
+  if ((vocab & 7) == 0 && vocab <= 256 * kCeVecs * 8 && (ld & 7) == 0 && (bases & 15) == 0)
+    return launch_pdl(cross_entropy_vec_kernel, dim3(rows), dim3(256), 0, SFL_STREAM(stream),
+                      static_cast<const __nv_bfloat16*>(logits), ld, targets, row_loss,
+                      static_cast<__nv_bfloat16*>(dlogits), grad_scale, vocab);
   return launch_pdl(cross_entropy_kernel, dim3(rows), dim3(256), 0, SFL_STREAM(stream),
                     static_cast<const __nv_bfloat16*>(logits), ld, targets, row_loss,
                     static_cast<__nv_bfloat16*>(dlogits), grad_scale, vocab);

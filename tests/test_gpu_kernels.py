@@ -151,7 +151,7 @@ def test_rmsnorm_forward_backward(dev, rows, dim):
     assert rel(dw, wr.grad + 1) < 1e-4
 
 
-@pytest.mark.parametrize("rows,vocab", [(512, 10000), (16, 32), (7, 1000)])
+@pytest.mark.parametrize("rows,vocab", [(512, 10000), (16, 32), (7, 1000), (5, 1003), (3, 20000)])
 def test_cross_entropy(dev, rows, vocab):
     from systems_for_llms_b200.ops import functional as K
     ld = -(-vocab // 8) * 8
