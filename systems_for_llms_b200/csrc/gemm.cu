@@ -1099,7 +1099,9 @@ wgrad_grouped_kernel(const __grid_constant__ GroupedMaps maps,
 // and the input gradients of the column-parallel layers (backward) are products
 // whose reduction dimension is split over the ranks: every rank holds a partial
 // [M, N] result and all of them need the sum (the reference all-reduces after
-// F.linear, distributed/llmdist/tensor_parallel.py).  This kernel is the GEMM and
+// F.linear: distributed/llmdist/tensor_parallel.py:40-45 for the forward sums of
+// the output and down projections, :25-36 for the input gradients of the
+// column-parallel layers).  This kernel is the GEMM and
 // that all-reduce in one launch, tile by tile over NVLink peer memory:
 //
 //   * the 128-row tile strips are owned round-robin by the ranks;
