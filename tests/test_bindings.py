@@ -66,3 +66,20 @@ def test_fused_tensor_parallel_gemm_validates_before_launching(library):
     table.world = 2
     assert call(*args(200, 2)) == -2          # N must be whole 256-column tiles
     assert call(*args(256, 2)) == -2          # pointer tables not filled in
+
+
+def test_new_elementwise_entry_points_validate_before_launching(library):
+    handle = library._handle
+    bwd = handle.sfl_embedding_bwd
+    bwd.restype = ctypes.c_int
+    bwd.argtypes = None
+    p = ctypes.c_void_p(256)
+    # rows <= 0, and more rows than fit in shared memory, are refused without a launch
+    assert bwd(p, p, p, 0, 8, 10, 0, p, p, None) == -2
+    assert bwd(p, p, p, 60000, 8, 10, 0, p, p, None) == -2
+    assert bwd(p, p, None, 16, 8, 10, 0, p, p, None) == -2
+    scale = handle.sfl_scale_bf16_unless_one
+    scale.restype = ctypes.c_int
+    scale.argtypes = None
+    assert scale(None, ctypes.c_long(8), p, None) == -2
+    assert scale(p, ctypes.c_long(0), p, None) == 0            # nothing to do
