@@ -390,7 +390,6 @@ sqnorm_partial_kernel(const float* __restrict__ x, long n, float* __restrict__ p
 
 __global__ void norm_finalize_kernel(const float* __restrict__ partial, int n, float sum_scale,
                                      float max_norm, float* __restrict__ out) {
-  __shared__ float scratch[33];
   // Double accumulation in a fixed order keeps the total independent of n's split.
   double s = 0.0;
   for (int i = threadIdx.x; i < n; i += blockDim.x) s += static_cast<double>(partial[i]);
@@ -401,7 +400,6 @@ __global__ void norm_finalize_kernel(const float* __restrict__ partial, int n, f
     if (threadIdx.x < o) dsum[threadIdx.x] += dsum[threadIdx.x + o];
     __syncthreads();
   }
-  (void)scratch;
   if (threadIdx.x == 0) {
     const float norm = sqrtf(static_cast<float>(dsum[0] * static_cast<double>(sum_scale)));
     out[0] = norm;
