@@ -83,3 +83,31 @@ def test_new_elementwise_entry_points_validate_before_launching(library):
     scale.argtypes = None
     assert scale(None, ctypes.c_long(8), p, None) == -2
     assert scale(p, ctypes.c_long(0), p, None) == 0            # nothing to do
+
+
+def test_fused_tensor_parallel_staging_arithmetic_stays_in_bounds(library):
+    """The kernel's strip and flag addressing, restated on the host, for the largest
+    indices of several shapes: every 4 KB block and every flag word must lie inside
+    the buffers whose sizes the library reports."""
+    BM, BN, WARPS, PEERS, BLOCK = 128, 256, 8, 8, 4096
+    for M, N, world in [(4096, 1024, 2), (4096, 1024, 8), (1000, 512, 2), (130, 256, 3),
+                        (16384, 2048, 4)]:
+        m_tiles, n_tiles = -(-M // BM), N // BN
+        tiles = m_tiles * n_tiles
+        stage = library.sfl_gemm_tp_stage_bytes(M, N, world)
+        flags = library.sfl_gemm_tp_tile_flag_bytes(M, N)
+        tile_elems = BM * BN
+        worst_block = worst_flag = 0
+        for rank in (0, world - 1):
+            for tile in (0, tiles - 1):
+                for quarter in range(4):
+                    strip = quarter * 32
+                    base = ((rank * tiles + tile) * tile_elems + strip * BN) * 2
+                    for chunk in range(BN // 64):
+                        worst_block = max(worst_block, base + chunk * BLOCK + BLOCK)
+                for warp in range(WARPS):
+                    worst_flag = max(worst_flag, ((tile * PEERS + rank) * WARPS + warp) * 4 + 4)
+        assert worst_block <= stage, (M, N, world)
+        assert worst_flag <= flags, (M, N, world)
+        # strips of one tile tile the 64 KB exactly: 4 quarters x 4 chunks x 4 KB
+        assert 4 * (BN // 64) * BLOCK == tile_elems * 2
