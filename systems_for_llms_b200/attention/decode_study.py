@@ -157,6 +157,45 @@ def geomean(values):
     return math.exp(statistics.mean(math.log(v) for v in values)) if values else None
 
 
+L2_BYTES = 126 * 1024 * 1024
+
+
+def cold_copies(cache_bytes: int) -> int:
+    """Cache copies to rotate over so that no call finds its operands in L2."""
+    return max(1, min(64, math.ceil(2 * L2_BYTES / max(1, cache_bytes))))
+
+
+def time_cold(build, copies: int, *, repeats: int = 12) -> dict:
+    """``build(i)`` returns the zero-argument operator for cache copy ``i``; one CUDA
+    graph runs all copies back to back and the median per-call time is reported."""
+    import torch
+    operators = [build(i) for i in range(copies)]
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            for operator in operators:
+                operator()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for operator in operators:
+                operator()
+        graph.replay()
+        stream.synchronize()
+        samples = []
+        for _ in range(repeats):
+            begin, end = (torch.cuda.Event(enable_timing=True) for _ in range(2))
+            begin.record(stream)
+            graph.replay()
+            end.record(stream)
+            end.synchronize()
+            samples.append(begin.elapsed_time(end) / copies)
+    torch.cuda.current_stream().wait_stream(stream)
+    return {"median_ms": statistics.median(samples), "min_ms": min(samples),
+            "max_ms": max(samples), "copies": copies, "repeats": repeats, "mode": "cuda_graph_cold"}
+
+
 def summarise_case(record: dict) -> None:
     """Best split overall and per variant, ratios, cache bandwidth - from recorded timings."""
     timings = record["timings"]
@@ -239,6 +278,36 @@ def benchmark(output: Path, deadline: float):
                 key=lambda op: record["timings"][f"cuda_{op.variant}_split_{op.splits}"]
                 ["median_ms"]).scratch_bytes
             summarise_case(record)
+            # cold-L2 figures for the best split of each variant and the baseline
+            copies = cold_copies(record["cache_bytes"])
+            caches = [(k, v)] + [(torch.randn_like(k), torch.randn_like(v))
+                                 for _ in range(copies - 1)]
+            lengths = inputs[3]
+            record["cold_timings"] = {}
+            for variant, name in record["best_observed_by_variant"].items():
+                splits = operators[name].splits
+                record["cold_timings"][name] = time_cold(
+                    lambda i, s=splits, w=variant: prepare(q, *caches[i], lengths, splits=s,
+                                                           variant=w), copies)
+            if "sdpa_flash" in operators:
+                def flash_on(i):
+                    kc, vc = caches[i]
+
+                    def call():
+                        with sdpa_kernel(SDPBackend.FLASH_ATTENTION):
+                            return F.scaled_dot_product_attention(q.unsqueeze(2), kc, vc,
+                                                                  enable_gqa=True).squeeze(2)
+                    return call
+                record["cold_timings"]["sdpa_flash"] = time_cold(flash_on, copies)
+            cold_best = min((n for n in record["cold_timings"] if n.startswith("cuda_")),
+                            key=lambda n: record["cold_timings"][n]["median_ms"])
+            cold_ms = record["cold_timings"][cold_best]["median_ms"]
+            record.update(cold_best=cold_best,
+                          cold_kv_bandwidth_gbs=record["cache_bytes"] / (cold_ms * 1e6))
+            if "sdpa_flash" in record["cold_timings"]:
+                record["cold_sdpa_flash_over_best"] = (
+                    record["cold_timings"]["sdpa_flash"]["median_ms"] / cold_ms)
+            del caches
             records.append(record)
             write_json(output / "cases" / f"case-{index:02d}-seed-{seed}.json", record)
             write_json(output / "benchmark.json", records)

@@ -26,6 +26,7 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "launch.cuh"
 #include "ptx.cuh"
@@ -675,6 +676,479 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
+// ===================================================== forward, two streams ====
+// Head dimension 64.  With one 128-row query tile per CTA the tensor pipe finishes
+// a score tile and a P V product in about 500 cycles while the softmax of the tile
+// needs 16,384 exponentials - over 1,000 cycles of the SM's special-function units -
+// and every hand-over between the two costs a barrier round trip, so a CTA that
+// alternates them leaves both units idle most of the time.  Here a CTA runs TWO
+// independent streams of work items (slots).  Each slot is a complete pipeline of
+// its own: a TMA warp, an MMA warp, a softmax warpgroup, a query tile, K/V rings, a
+// score tile and an output accumulator in tensor memory.  The slots share nothing
+// but the SM, so whenever one of them waits (for its scores, for its probabilities)
+// the other one has the tensor pipe and the special-function units:
+//
+//   tensor pipe :  S0=Q0 K0(j)^T | O1+=P1 V1(j-1), S1=Q1 K1(j)^T | O0+=P0 V0(j), S0=... |
+//   softmax 0   :                  max/exp of S0(j) ........... P0 |                      ...
+//   softmax 1   :  ... exp of S1(j-1) .. P1 |                        max/exp of S1(j) ..
+//
+// P is written back over its own score tile in tensor memory as packed 16-bit
+// pairs and fed to the P V product as the A operand from tensor memory
+// (tcgen05.mma with a tensor-memory A operand), which also lifts the shared-memory
+// read limit of 128 x 64 x 16 products (4 KB of A per instruction); P_TMEM = false
+// keeps P in a swizzled shared-memory tile instead.
+//
+// Work items are numbered heaviest first and dealt to the 2 x grid slots in rounds
+// of alternating direction, as in the one-stream kernel below.  The order of a
+// slot's MMAs - S(j), then for every tile [P V(j), S(j+1)] - together with the
+// in-order execution of one thread's tcgen05.mma instructions makes most hand-overs
+// implicit: when the softmax warps see S(j) complete, P V(j-1) has completed too, so
+// the P tile and the output accumulator may be touched, and the K tile of step j and
+// the V tile of step j-1 handed back to the TMA warp, without a further wait or a
+// tcgen05.commit of their own (the MMA thread issues one commit per tile).
+constexpr int kFwd2Threads = 384;  // per slot: TMA warp, MMA warp, softmax warpgroup
+
+template <bool P_TMEM>
+struct Fwd2Smem {
+  static constexpr int kTileBytes = kTile * 64 * 2;  // one 128 x 64 operand tile
+  static constexpr int kPBytes = kTile * kTile * 2;
+  static constexpr int kQBufs = P_TMEM ? 2 : 1;  // next item's query tile prefetched
+  static constexpr int kStages = 2;
+  static constexpr int kSlotBytes =
+      kTileBytes * (kQBufs + 2 * kStages) + (P_TMEM ? 0 : kPBytes);
+  static constexpr int kSharedBytes = 1536;  // Fwd2Shared
+  static constexpr int kBytes = 2 * kSlotBytes + kSharedBytes + 1024;
+};
+
+struct Fwd2SlotBars {
+  uint64_t q_full[2], q_empty[2];
+  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+  uint64_t s_full;   // score tile complete (MMA commit)
+  uint64_t p_ready;  // P tile written, accumulator rescaled (128 arrivals)
+  uint64_t o_full;   // last P V product of an item complete (MMA commit)
+  uint64_t o_free;   // epilogue has read the accumulator (128 arrivals)
+  int col_doc[kTile];
+};
+
+struct Fwd2Shared {
+  Fwd2SlotBars slot[2];
+  uint32_t tmem_base;
+  int abort;
+};
+static_assert(sizeof(Fwd2Shared) <= Fwd2Smem<true>::kSharedBytes, "shared control block too large");
+
+// Work items of one slot: item w covers query tile (num_q_tiles - 1 - w / BH) of
+// (batch, head) w % BH; slot g of G takes w = r G + (r odd ? G - 1 - g : g).
+struct SlotWalk {
+  int G, g, rounds, num_items, r;
+  __device__ __forceinline__ int next() {
+    while (r < rounds) {
+      const int rr = r++;
+      const int w = rr * G + ((rr & 1) ? G - 1 - g : g);
+      if (w < num_items) return w;
+    }
+    return -1;
+  }
+};
+
+__device__ __forceinline__ void named_barrier_slot(int slot) {
+  asm volatile("bar.sync %0, 128;" ::"r"(slot + 1) : "memory");
+}
+
+// Phase timers of CTA 0 (cycles, summed), compiled in with -DSFL_ATTN_TRACE and read back
+// with sfl_attn_trace_read: softmax warp 0 of slot 0 - [0] waiting for scores, [1] loading
+// them, [2] row maximum and rescale, [3] exponentials and P store, [4] epilogue, [5] tiles;
+// MMA thread of slot 0 - [8] waiting for P and V, [9] issuing a P V product, [10] waiting
+// for K (and Q), [11] issuing a score product and its commit, [12] tiles.
+#ifdef SFL_ATTN_TRACE
+__device__ unsigned long long g_attn_trace[16];
+#define SFL_TRACE_DECL(cond)      \
+  const bool tracing_ = (cond);   \
+  long long trace_t_ = clock64();
+#define SFL_TRACE_MARK(slot)                                                          \
+  if (tracing_) {                                                                     \
+    const long long now_ = clock64();                                                 \
+    atomicAdd(&g_attn_trace[slot], static_cast<unsigned long long>(now_ - trace_t_)); \
+    trace_t_ = now_;                                                                  \
+  }
+#define SFL_TRACE_COUNT(slot) \
+  if (tracing_) atomicAdd(&g_attn_trace[slot], 1ull);
+#else
+#define SFL_TRACE_DECL(cond)
+#define SFL_TRACE_MARK(slot)
+#define SFL_TRACE_COUNT(slot)
+#endif
+
+template <bool FP16, bool P_TMEM>
+__global__ void __launch_bounds__(kFwd2Threads, 1)
+attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+  constexpr int D = 64;
+  using L = Fwd2Smem<P_TMEM>;
+  constexpr int QB = L::kQBufs;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  Fwd2Shared* sh = reinterpret_cast<Fwd2Shared*>(smem + 2 * L::kSlotBytes);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // warps 0, 1: TMA and MMA of slot 0; warps 2, 3: of slot 1; warps 4-7 and 8-11: softmax
+  const int w = warp < 4 ? (warp >> 1) : ((warp - 4) >> 2);
+  uint8_t* slot_base = smem + w * L::kSlotBytes;
+  uint8_t* sQ = slot_base;                        // QB tiles
+  uint8_t* sK = slot_base + QB * L::kTileBytes;   // kStages tiles
+  uint8_t* sV = sK + L::kStages * L::kTileBytes;  // kStages tiles
+  uint8_t* sP = sV + L::kStages * L::kTileBytes;  // only when !P_TMEM
+  Fwd2SlotBars& bar = sh->slot[w];
+
+  const int num_q_tiles = (p.N + kTile - 1) / kTile;
+  const int BH = p.B * p.H;
+  const int num_items = num_q_tiles * BH;
+  const int G = 2 * static_cast<int>(gridDim.x);
+  const int rounds = (num_items + G - 1) / G;
+  SlotWalk walk{G, 2 * static_cast<int>(blockIdx.x) + w, rounds, num_items, 0};
+  auto item_tile = [&](int item) { return num_q_tiles - 1 - item / BH; };
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      Fwd2SlotBars& b = sh->slot[i];
+      for (int s = 0; s < 2; ++s) {
+        mbar_init(&b.q_full[s], 1);
+        mbar_init(&b.q_empty[s], 1);
+        mbar_init(&b.k_full[s], 1);
+        mbar_init(&b.k_empty[s], 1);
+        mbar_init(&b.v_full[s], 1);
+        mbar_init(&b.v_empty[s], 1);
+      }
+      mbar_init(&b.s_full, 1);
+      mbar_init(&b.p_ready, 128);
+      mbar_init(&b.o_full, 1);
+      mbar_init(&b.o_free, 128);
+    }
+    sh->abort = 0;
+    mbar_fence_init();
+    prefetch_tensormap(&tmQ);
+    prefetch_tensormap(&tmK);
+    prefetch_tensormap(&tmV);
+  }
+  if (warp == 1) {
+    tmem_alloc(&sh->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sh->tmem_base;
+  pdl_launch_dependents();
+  pdl_wait();
+  volatile int* abort = &sh->abort;
+  // tensor memory: score tiles at columns [0,128) and [128,256), outputs at 256 and 320
+  const uint32_t tS = tmem + static_cast<uint32_t>(w * kTile);
+  const uint32_t tO = tmem + static_cast<uint32_t>(256 + w * D);
+
+  if (warp == 0 || warp == 2) {
+    // ---------------------------------------------------- TMA producer ----
+    if (lane == 0) {
+      uint32_t it = 0, qi = 0;
+      int item;
+      bool ok = true;
+      while (ok && (item = walk.next()) >= 0) {
+        const int q_tile = item_tile(item), bh = item % BH;
+        const int b = bh / p.H, h = bh % p.H;
+        const TileRange range = tile_range(p.sched, q_tile, p.N, false);
+        const int n_tiles = range.end - range.begin;
+        if (n_tiles <= 0) continue;
+        const int qb = qi % QB;
+        if (!bounded_wait(&bar.q_empty[qb], ((qi / QB) & 1) ^ 1, abort, p.status,
+                          kStatusTimeoutEmpty))
+          break;
+        mbar_expect_tx(&bar.q_full[qb], L::kTileBytes);
+        load_rows<D>(sQ + qb * L::kTileBytes, &tmQ, &bar.q_full[qb], q_tile * kTile, h, b);
+        ++qi;
+        for (int j = 0; j < n_tiles; ++j, ++it) {
+          const int other = tile_info(p.sched, range, j).other;
+          const int s = it & 1;
+          const uint32_t ph = ((it >> 1) & 1) ^ 1;
+          if (!bounded_wait(&bar.k_empty[s], ph, abort, p.status, kStatusTimeoutEmpty)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&bar.k_full[s], L::kTileBytes);
+          load_rows<D>(sK + s * L::kTileBytes, &tmK, &bar.k_full[s], other * kTile, h, b);
+          if (!bounded_wait(&bar.v_empty[s], ph, abort, p.status, kStatusTimeoutEmpty)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&bar.v_full[s], L::kTileBytes);
+          load_rows<D>(sV + s * L::kTileBytes, &tmV, &bar.v_full[s], other * kTile, h, b);
+        }
+      }
+    }
+  } else if (warp == 1 || warp == 3) {
+    // ------------------------------------------------------ MMA issuer ----
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = idesc_16bit(FP16, kTile, kTile, false, false);
+      constexpr uint32_t idesc_pv = idesc_16bit(FP16, kTile, D, false, true);
+      // descriptors of the first reduction step of every buffer; the others follow by
+      // constant offsets
+      const uint64_t q_desc0 = desc_kmajor(smem_u32(sQ), kTile, 0);
+      const uint64_t k_desc0 = desc_kmajor(smem_u32(sK), kTile, 0);
+      const uint64_t v_desc0 = desc_mnmajor(smem_u32(sV), 0);
+      const uint64_t p_desc0 = desc_kmajor(smem_u32(sP), kTile, 0);
+      (void)p_desc0;
+      // The score products run one tile ahead of the P V products: a second cursor over
+      // the same item sequence.
+      SlotWalk qk_walk = walk;
+      int qk_n = 0, qk_j = 0;
+      bool qk_done = false;
+      auto qk_advance = [&]() {
+        qk_n = qk_j = 0;
+        int next_item;
+        while ((next_item = qk_walk.next()) >= 0) {
+          const TileRange t = tile_range(p.sched, item_tile(next_item), p.N, false);
+          if (t.end - t.begin > 0) {
+            qk_n = t.end - t.begin;
+            return;
+          }
+        }
+        qk_done = true;
+      };
+      uint32_t qk_it = 0, q_qi = 0;
+      SFL_TRACE_DECL(blockIdx.x == 0 && warp == 1)
+      auto issue_qk = [&]() -> bool {
+        if (qk_done) return true;
+        const int qb = q_qi % QB;
+        const int s = qk_it & 1;
+        if (qk_j == 0 && !bounded_wait(&bar.q_full[qb], (q_qi / QB) & 1, abort, p.status,
+                                       kStatusTimeoutFull))
+          return false;
+        if (!bounded_wait(&bar.k_full[s], (qk_it >> 1) & 1, abort, p.status, kStatusTimeoutFull))
+          return false;
+        tc_fence_after();
+        SFL_TRACE_MARK(10)
+        const uint64_t qd = umma_desc_advance(q_desc0, qb * L::kTileBytes);
+        const uint64_t kd = umma_desc_advance(k_desc0, s * L::kTileBytes);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma_bf16_ss(tS, umma_desc_advance(qd, k * 32), umma_desc_advance(kd, k * 32), idesc_qk,
+                       k != 0);
+        umma_commit(&bar.s_full);
+        ++qk_it;
+        if (++qk_j == qk_n) {
+          umma_commit(&bar.q_empty[qb]);
+          ++q_qi;
+          qk_advance();
+        }
+        SFL_TRACE_MARK(11)
+        return true;
+      };
+      qk_advance();
+      bool ok = issue_qk();
+      uint32_t it = 0, items = 0;
+      int item;
+      while (ok && (item = walk.next()) >= 0) {
+        const TileRange range = tile_range(p.sched, item_tile(item), p.N, false);
+        const int n_tiles = range.end - range.begin;
+        if (n_tiles <= 0) continue;
+        for (int j = 0; j < n_tiles && ok; ++j, ++it) {
+          const int s = it & 1;
+          if (!bounded_wait(&bar.p_ready, it & 1, abort, p.status, kStatusTimeoutTmemFull) ||
+              !bounded_wait(&bar.v_full[s], (it >> 1) & 1, abort, p.status, kStatusTimeoutFull) ||
+              (j == 0 && items > 0 &&
+               !bounded_wait(&bar.o_free, (items - 1) & 1, abort, p.status,
+                             kStatusTimeoutTmemEmpty))) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          SFL_TRACE_MARK(8)
+          const uint64_t vd = umma_desc_advance(v_desc0, s * L::kTileBytes);
+          if constexpr (P_TMEM) {
+#pragma unroll
+            for (int k = 0; k < kTile / 16; ++k)
+              umma_bf16_ts(tO, tS + k * 8, umma_desc_advance(vd, k * 2048), idesc_pv,
+                           (j | k) != 0);
+          } else {
+#pragma unroll
+            for (int k = 0; k < kTile / 16; ++k)
+              umma_bf16_ss(tO, umma_desc_advance(p_desc0, (k >> 2) * (kTile * 128) + (k & 3) * 32),
+                           umma_desc_advance(vd, k * 2048), idesc_pv, (j | k) != 0);
+          }
+          if (j == n_tiles - 1) {
+            umma_commit(&bar.o_full);
+            ++items;
+          }
+          SFL_TRACE_MARK(9)
+          SFL_TRACE_COUNT(12)
+          // the score tile of step it + 1 goes where P of this step is: in order, after
+          ok = issue_qk();
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------ softmax + epilogue ----
+    const int quarter = warp & 3;  // tensor-memory lane quarter this warp may access
+    const int row = quarter * 32 + lane;
+    const bool leader = (warp & 3) == 0 && lane == 0;  // hands K/V stages back
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const float scale_log2 = p.scale * kLog2e;
+    uint32_t it = 0;     // key tiles processed by this slot
+    uint32_t items = 0;  // items with key tiles finished by this slot
+    bool ok = true;
+    int item;
+    SFL_TRACE_DECL(blockIdx.x == 0 && warp == 4 && lane == 0)
+    while (ok && (item = walk.next()) >= 0) {
+      const int q_tile = item_tile(item), bh = item % BH;
+      const int b = bh / p.H, h = bh % p.H;
+      const TileRange range = tile_range(p.sched, q_tile, p.N, false);
+      const int n_tiles = range.end - range.begin;
+      const int q = q_tile * kTile + row;
+      float m_used = -INFINITY;
+      float l = 0.f;
+      for (int j = 0; j < n_tiles && ok; ++j, ++it) {
+        const TileInfo t = tile_info(p.sched, range, j);
+        if (!bounded_wait(&bar.s_full, it & 1, abort, p.status, kStatusTimeoutTmemFull)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        // S(j) complete: the score product has read K(j), and P V(j-1), issued before it,
+        // has read V(j-1).
+        if (leader) {
+          mbar_arrive(&bar.k_empty[it & 1]);
+          if (j > 0) mbar_arrive(&bar.v_empty[(it - 1) & 1]);
+        }
+        SFL_TRACE_MARK(0)
+        float x[kTile];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld_32x32f(tS + lane_base + c * 32, x + c * 32);
+        tmem_ld_wait();
+        SFL_TRACE_MARK(1)
+        const int k0 = t.other * kTile;
+        const bool ragged = (k0 + kTile > p.N) || (q_tile * kTile + kTile > p.N);
+        if (!t.full || ragged) {
+          const RowMask rm = row_mask_for_query(p.sched, q, k0, p.N);
+          apply_mask(x, rm, static_cast<uint32_t>(t.bitmap >> ((row >> 4) * 8)) & 0xffu);
+          if (p.sched.doc != nullptr) {
+            named_barrier_slot(w);  // previous readers of the label tile are done
+            bar.col_doc[row] = k0 + row < p.N ? p.sched.doc[k0 + row] : -1;
+            named_barrier_slot(w);
+            apply_doc_mask(x, bar.col_doc, q < p.N ? p.sched.doc[q] : -2);
+          }
+        }
+        float mx8[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) mx8[c] = x[c];
+#pragma unroll
+        for (int c = 8; c < kTile; ++c) mx8[c & 7] = fmaxf(mx8[c & 7], x[c]);
+        float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                         fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+        mx *= scale_log2;
+        // Lazy rescale: keep a stale maximum until it is off by more than 2^8.
+        const bool grow = mx > m_used + 8.0f;
+        if (__any_sync(0xffffffffu, grow)) {
+          if (j > 0) {
+            const float alpha = grow ? fast_exp2(m_used - mx) : 1.0f;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              float o[32];
+              tmem_ld_32x32f(tO + lane_base + c * 32, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] *= alpha;
+              tmem_st_32x32(tO + lane_base + c * 32, o);
+            }
+            l *= alpha;
+          }
+          if (grow) m_used = mx;
+        }
+        const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        SFL_TRACE_MARK(2)
+        if constexpr (P_TMEM) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t packed[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const float p0 = fast_exp2(fmaf(x[c * 32 + i], scale_log2, neg_m));
+              const float p1 = fast_exp2(fmaf(x[c * 32 + i + 1], scale_log2, neg_m));
+              sum4[(i >> 1) & 3] += p0 + p1;
+              packed[i >> 1] = pack2<FP16>(p0, p1);
+            }
+            // P over its own scores: 16-bit pairs, 16 columns per 32 scores
+            tmem_st_32x16(tS + lane_base + c * 16, packed);
+          }
+          tmem_st_wait();
+        } else {
+          uint32_t packed[64];
+#pragma unroll
+          for (int c = 0; c < kTile; c += 2) {
+            const float p0 = fast_exp2(fmaf(x[c], scale_log2, neg_m));
+            const float p1 = fast_exp2(fmaf(x[c + 1], scale_log2, neg_m));
+            sum4[(c >> 1) & 3] += p0 + p1;
+            packed[c >> 1] = pack2<FP16>(p0, p1);
+          }
+          store_row_swizzled(sP, row, packed);
+          fence_proxy_async_smem();
+          tmem_st_wait();  // a rescale's stores, if any
+        }
+        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        tc_fence_before();
+        mbar_arrive(&bar.p_ready);
+        SFL_TRACE_MARK(3)
+        SFL_TRACE_COUNT(5)
+      }
+      if (!ok) break;
+      if (n_tiles > 0) {
+        if (!bounded_wait(&bar.o_full, items & 1, abort, p.status, kStatusTimeoutTmemFull)) break;
+        tc_fence_after();
+        if (leader) mbar_arrive(&bar.v_empty[(it - 1) & 1]);  // the item's last V tile
+      }
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      uint8_t* orow = static_cast<uint8_t*>(p.o) +
+                      2 * (b * p.o_sb + h * p.o_sh + static_cast<long>(q) * p.o_st);
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        float o[32];
+        if (n_tiles > 0) {
+          tmem_ld_32x32f(tO + lane_base + c * 32, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0.f;
+        }
+        if (q < p.N) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 v;
+            v.x = pack2<FP16>(o[8 * i + 0] * inv, o[8 * i + 1] * inv);
+            v.y = pack2<FP16>(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
+            v.z = pack2<FP16>(o[8 * i + 4] * inv, o[8 * i + 5] * inv);
+            v.w = pack2<FP16>(o[8 * i + 6] * inv, o[8 * i + 7] * inv);
+            *reinterpret_cast<uint4*>(orow + (c * 32 + i * 8) * 2) = v;
+          }
+        }
+      }
+      if (n_tiles > 0) {  // the accumulator may be overwritten by the next item
+        tc_fence_before();
+        mbar_arrive(&bar.o_free);
+        ++items;
+      }
+      if (q < p.N && p.lse != nullptr)
+        p.lse[(static_cast<long>(b) * p.H + h) * p.N + q] =
+            l > 0.f ? (m_used + log2f(l)) * kLn2 : -INFINITY;
+      SFL_TRACE_MARK(4)
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
 // ============================================================= backward ====
 // Shared layout of the two backward kernels: an "owned" pair of resident tiles,
 // a ring of streamed tile pairs, and two [128 x 128] tiles written by the compute
@@ -1208,6 +1682,31 @@ extern "C" int sfl_attn_fwd(const SflAttnTensor* q, const SflAttnTensor* k, cons
   p.o = o->ptr; p.o_sb = o->stride_b; p.o_sh = o->stride_h; p.o_st = o->stride_t;
   p.lse = lse; p.is_fp16 = is_fp16; p.status = status;
   const int items = ((N + kTile - 1) / kTile) * B * H;
+  // SFL_ATTN_FWD: 1 = one work stream per CTA (the only form for head dimension 128),
+  // 2 = two streams with P in tensor memory (default for head dimension 64),
+  // 3 = two streams with P in shared memory.
+  static const int variant = [] {
+    const char* v = getenv("SFL_ATTN_FWD");
+    return v == nullptr ? 2 : atoi(v);
+  }();
+  if (D == 64 && variant != 1) {
+    const int slots = (items + 1) / 2;
+    dim3 grid2(slots < attn_sm_count() ? slots : attn_sm_count());
+    auto go = [&](auto kern, int bytes) -> int {
+      int rc = set_smem(kern, bytes);
+      if (rc) return rc;
+      return launch_pdl(kern, grid2, dim3(kFwd2Threads), bytes, stream, tq, tk, tv, p);
+    };
+    int rc;
+    if (variant == 3)
+      rc = is_fp16 ? go(attn_fwd2_kernel<true, false>, Fwd2Smem<false>::kBytes)
+                   : go(attn_fwd2_kernel<false, false>, Fwd2Smem<false>::kBytes);
+    else
+      rc = is_fp16 ? go(attn_fwd2_kernel<true, true>, Fwd2Smem<true>::kBytes)
+                   : go(attn_fwd2_kernel<false, true>, Fwd2Smem<true>::kBytes);
+    if (rc) return rc;
+    return static_cast<int>(cudaGetLastError());
+  }
   dim3 grid(items < attn_sm_count() ? items : attn_sm_count());
 #define SFL_FWD(D_, F_)                                                                   \
   {                                                                                       \
@@ -1283,6 +1782,20 @@ extern "C" int sfl_attn_bwd(const SflAttnTensor* q, const SflAttnTensor* k, cons
   else { if (is_fp16) SFL_BWD(128, true) else SFL_BWD(128, false) }
 #undef SFL_BWD
   return static_cast<int>(cudaGetLastError());
+}
+
+// Copies and clears the phase timers of the two-stream forward kernel; returns -1 when the
+// library was built without -DSFL_ATTN_TRACE.
+extern "C" int sfl_attn_trace_read(unsigned long long* out16) {
+#ifdef SFL_ATTN_TRACE
+  unsigned long long zero[16] = {};
+  cudaError_t e = cudaMemcpyFromSymbol(out16, g_attn_trace, sizeof(zero));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return static_cast<int>(cudaMemcpyToSymbol(g_attn_trace, zero, sizeof(zero)));
+#else
+  (void)out16;
+  return -1;
+#endif
 }
 
 extern "C" int sfl_rope_bwd(void* x_bf16, long ld, const float* cos, const float* sin, long rows,

@@ -38,9 +38,14 @@
 
 namespace sfl {
 
-// Polling budget of a peer wait (iterations of roughly 200 ns): about two
-// seconds by default, then the wait gives up and the kernel reports a status.
-__device__ uint32_t g_peer_spin_limit = 1u << 23;
+// Polling budget of a peer wait (iterations of roughly 200 ns).  The default, about ten
+// seconds, is sized for training: ranks of one job reach a collective at different times
+// (a garbage-collection pause, a page fault in a memory-mapped data file, lazy module
+// loading on the first step) and a budget near the skew would turn ordinary jitter into a
+// failed step.  Tests of the timeout path set a millisecond budget
+// (sfl_comm_set_spin_limit).  When the budget runs out the wait gives up and the kernel
+// reports a status, which the trainers read back every step.
+__device__ uint32_t g_peer_spin_limit = 48u << 20;
 
 __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch) {
   const uint32_t limit = g_peer_spin_limit;
@@ -75,8 +80,13 @@ __device__ __forceinline__ bool ready_barrier(const CommView& c, int slot, uint3
 // Every block calls this after its last peer write.  The last block to arrive
 // publishes "done" to all peers and waits for theirs, so when the kernel ends
 // every peer's writes into this rank's buffers have landed.
+//
+// A block whose ready-wait ran out still arrives here (`healthy` false) without having
+// touched any peer: the arrival counter then returns to zero as usual, so the slot works
+// again after the host has dealt with the reported status, and "done" is not traded by a
+// launch in which any wait failed on this rank.
 __device__ __forceinline__ void done_barrier(const CommView& c, int slot, uint32_t epoch,
-                                             int* status) {
+                                             int* status, bool healthy = true) {
   __shared__ int last;
   // The block barrier orders every thread's stores before thread 0's fence, which
   // is cumulative: one system fence per block instead of one per thread (each
@@ -90,6 +100,7 @@ __device__ __forceinline__ void done_barrier(const CommView& c, int slot, uint32
   __syncthreads();
   if (!last) return;
   if (threadIdx.x == 0) *counter_ptr(c.flags[c.rank], slot) = 0;
+  if (!healthy || (status != nullptr && *static_cast<volatile int*>(status) != 0)) return;
   if (threadIdx.x < c.world) {
     st_release_sys(flag_ptr(c.flags[threadIdx.x], slot, 1, c.rank), epoch);
     if (!wait_flag(flag_ptr(c.flags[c.rank], slot, 1, threadIdx.x), epoch))
@@ -135,7 +146,10 @@ __global__ void __launch_bounds__(256)
 reduce_kernel(const CommView c, long offset, long count, float scale, int slot, uint32_t epoch,
               float* __restrict__ local_out, int accumulate_partial, int accumulate_out,
               int* status) {
-  if (!ready_barrier(c, slot, epoch, status)) return;
+  if (!ready_barrier(c, slot, epoch, status)) {
+    done_barrier(c, slot, epoch, status, false);
+    return;
+  }
   long begin, end;
   slice_of(count, c.world, c.rank, &begin, &end);
   float sq = 0.f;
@@ -318,7 +332,10 @@ adamw_allgather_kernel(const CommView params, const CommView shadows, ShardedAda
                        int slot, uint32_t epoch, int* status) {
   // Peers must have finished reading the old parameters (their forward/backward
   // is complete when they reach this kernel), hence the ready barrier.
-  if (!ready_barrier(params, slot, epoch, status)) return;
+  if (!ready_barrier(params, slot, epoch, status)) {
+    done_barrier(params, slot, epoch, status, false);
+    return;
+  }
   adamw_allgather_range(params, shadows, a);
   done_barrier(params, slot, epoch, status);
 }
@@ -332,7 +349,10 @@ __global__ void __launch_bounds__(256)
 adamw_allgather_ranges_kernel(const CommView params, const CommView shadows,
                               ShardedAdamParams a, const long* __restrict__ ranges, int num_ranges,
                               int slot, uint32_t epoch, int* status) {
-  if (!ready_barrier(params, slot, epoch, status)) return;
+  if (!ready_barrier(params, slot, epoch, status)) {
+    done_barrier(params, slot, epoch, status, false);
+    return;
+  }
   const float* grad = a.grad;
   float* m = a.m;
   float* v = a.v;
@@ -353,7 +373,10 @@ adamw_allgather_ranges_kernel(const CommView params, const CommView shadows,
 __global__ void __launch_bounds__(256)
 allgather_kernel(const CommView c, long offset_bytes, long chunk_bytes, int slot, uint32_t epoch,
                  int* status) {
-  if (!ready_barrier(c, slot, epoch, status)) return;
+  if (!ready_barrier(c, slot, epoch, status)) {
+    done_barrier(c, slot, epoch, status, false);
+    return;
+  }
   const long vecs = chunk_bytes >> 4;
   const long total = vecs * (c.world - 1);
   const long stride = static_cast<long>(gridDim.x) * blockDim.x;
@@ -386,7 +409,10 @@ allgather_kernel(const CommView c, long offset_bytes, long chunk_bytes, int slot
 __global__ void __launch_bounds__(256)
 allgather_into_kernel(const CommView c, long src_off, long chunk_bytes, char* __restrict__ dst,
                       int slot, uint32_t epoch, int* status) {
-  if (!ready_barrier(c, slot, epoch, status)) return;
+  if (!ready_barrier(c, slot, epoch, status)) {
+    done_barrier(c, slot, epoch, status, false);
+    return;
+  }
   const long vecs = chunk_bytes >> 4;
   const long total = vecs * c.world;
   const long stride = static_cast<long>(gridDim.x) * blockDim.x;
@@ -422,7 +448,10 @@ __global__ void __launch_bounds__(256)
 reduce_rows_resid_kernel(const CommView c, const CommView o, long in_off, long out_off,
                          const float* __restrict__ resid, long rows, int cols, int slot,
                          uint32_t epoch, int* status) {
-  if (!ready_barrier(c, slot, epoch, status)) return;
+  if (!ready_barrier(c, slot, epoch, status)) {
+    done_barrier(c, slot, epoch, status, false);
+    return;
+  }
   const long per = (rows + c.world - 1) / c.world;
   const long r0 = per * c.rank;
   const long r1 = r0 + per < rows ? r0 + per : rows;
@@ -483,7 +512,10 @@ reduce_rows_resid_kernel(const CommView c, const CommView o, long in_off, long o
 __global__ void __launch_bounds__(256)
 allreduce_rows_f32_kernel(const CommView c, const CommView o, long in_off, long out_off,
                           long count, int slot, uint32_t epoch, int* status) {
-  if (!ready_barrier(c, slot, epoch, status)) return;
+  if (!ready_barrier(c, slot, epoch, status)) {
+    done_barrier(c, slot, epoch, status, false);
+    return;
+  }
   long begin, end;
   slice_of(count, c.world, c.rank, &begin, &end);
   const long stride = static_cast<long>(gridDim.x) * blockDim.x;
@@ -548,6 +580,8 @@ extern "C" int sfl_ipc_close_handle(void* ptr) {
   return static_cast<int>(cudaIpcCloseMemHandle(ptr));
 }
 extern "C" int sfl_comm_set_spin_limit(unsigned iterations) {
+  const int rc = sfl_gemm_tp_set_spin_limit(iterations);  // the fused GEMM + all-reduce kernels
+  if (rc != 0) return rc;
   return static_cast<int>(cudaMemcpyToSymbol(g_peer_spin_limit, &iterations, sizeof(iterations)));
 }
 extern "C" long sfl_comm_flag_bytes(void) { return static_cast<long>(kFlagBytes); }

@@ -1126,6 +1126,15 @@ wgrad_grouped_kernel(const __grid_constant__ GroupedMaps maps,
 // waiting for this rank; every wait is bounded and reports through the status
 // word.  Stores to peers go through the swizzled staging tile of each epilogue
 // warp and leave as full 128-byte rows.
+//
+// Requirements the host entry point enforces or relies on: the grid is the same on
+// every rank (it is min(tiles, SM count) of identical shapes on identical GPUs) and
+// never exceeds the SM count, so that with one CTA per SM every CTA of the grid is
+// resident at once; CTA x only ever waits for CTA x of a peer, so no wait depends on
+// a CTA that cannot be scheduled.  Running another kernel that pins SMs for the whole
+// duration on the same device at the same time would void that argument.  Once a peer
+// wait has run out the warp reports it, stops the CTA's pipeline and touches no peer
+// memory again.
 struct TpFuse {
   int rank, world;
   char* stage[kMaxPeers];           // [source rank][tile][4 strips][4 chunks] 4 KB blocks
@@ -1147,10 +1156,13 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 
 constexpr int kTpBN = 256;
-constexpr uint32_t kTpSpinLimit = 1u << 22;  // about a second of polling
+// Same budget as the collectives (comm.cu: about ten seconds by default, sized for the
+// skew between training ranks); sfl_comm_set_spin_limit sets both.
+__device__ uint32_t g_tp_spin_limit = 48u << 20;
 
 __device__ __forceinline__ bool tp_wait_flag(const uint32_t* flag, uint32_t epoch) {
-  for (uint32_t spin = 0; spin < kTpSpinLimit; ++spin) {
+  const uint32_t limit = g_tp_spin_limit;
+  for (uint32_t spin = 0; spin < limit; ++spin) {
     if (reached(ld_acquire_sys(flag), epoch)) return true;
     if (spin > 64) __nanosleep(200);
   }
@@ -1318,6 +1330,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       st_release_sys(flag_ptr(f.flags[lane], f.slot, 0, f.rank), f.epoch);
     }
     bool peers_ready = false;
+    bool peer_failed = false;  // warp-uniform: a peer wait ran out, no further peer traffic
     int acc = 0;
     uint32_t acc_phase = 0;
     // Phase times of the first tile of CTA 0's first epilogue warp, when asked for:
@@ -1347,7 +1360,16 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (!peers_ready) {
         const bool ok = lane >= f.world ||
                         tp_wait_flag(flag_ptr(f.flags[f.rank], f.slot, 0, lane), f.epoch);
-        if (!__all_sync(0xffffffffu, ok) && lane == 0) report_status(p.status, kStatusTimeoutPeer);
+        if (!__all_sync(0xffffffffu, ok)) {
+          // A peer never entered the kernel: nothing may be stored into its buffers.
+          // Stop this CTA's pipeline and leave without any peer access.
+          if (lane == 0) {
+            report_status(p.status, kStatusTimeoutPeer);
+            *abort = 1;
+          }
+          peer_failed = true;
+          break;
+        }
         peers_ready = true;
       }
       mark();
@@ -1401,7 +1423,16 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           ok = tp_wait_flag(f.tile_flags[f.rank] +
                                 (static_cast<long>(tile) * kMaxPeers + lane) * kEpiWarps + wslot,
                             f.tile_epoch);
-        if (!__all_sync(0xffffffffu, ok) && lane == 0) report_status(p.status, kStatusTimeoutPeer);
+        if (!__all_sync(0xffffffffu, ok)) {
+          // The strips of this tile never arrived: the sum would be wrong, so no row
+          // of it is stored anywhere and the CTA stops.
+          if (lane == 0) {
+            report_status(p.status, kStatusTimeoutPeer);
+            *abort = 1;
+          }
+          peer_failed = true;
+          break;
+        }
         mark();
         const int row = m0 + strip + lane;
         const bool row_ok = row < p.M;
@@ -1493,8 +1524,12 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     last = __shfl_sync(0xffffffffu, last, 0);
     if (last) {
+      // The counter is reset whatever happened, so the slot can be used again; "done" is
+      // only traded when no wait of this launch has run out on this rank.
       if (lane == 0) *counter_ptr(f.flags[f.rank], f.slot) = 0;
-      if (lane < f.world) {
+      const bool healthy = !peer_failed && *abort == 0 &&
+                           (p.status == nullptr || *static_cast<volatile int*>(p.status) == 0);
+      if (healthy && lane < f.world) {
         st_release_sys(flag_ptr(f.flags[lane], f.slot, 1, f.rank), f.epoch);
         if (!tp_wait_flag(flag_ptr(f.flags[f.rank], f.slot, 1, lane), f.epoch))
           report_status(p.status, kStatusTimeoutPeer);
@@ -1749,6 +1784,10 @@ extern "C" int sfl_gemm_bf16(const void* a, long lda, int a_mn, const void* b, l
 // Weight gradients of up to four linear layers in one launch; see the kernel.
 // Every matrix must be addressable by TMA (16-byte aligned base and pitch);
 // returns -2 otherwise so the caller can fall back to one product at a time.
+extern "C" int sfl_gemm_tp_set_spin_limit(unsigned iterations) {
+  return static_cast<int>(cudaMemcpyToSymbol(sfl::g_tp_spin_limit, &iterations, sizeof(iterations)));
+}
+
 extern "C" int sfl_gemm_wgrad_grouped(const SflWgradProblem* problems, int count, int* status,
                                       void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);

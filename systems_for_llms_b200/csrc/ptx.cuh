@@ -78,6 +78,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking test of a phase.  try_wait may suspend the thread for a while when the
+// phase is incomplete; a thread that serves several independent pipelines polls with this
+// instead, so that one pipeline that is not ready never delays another that is.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait.  Roughly two seconds of polling before it gives up; a healthy
 // pipeline stage completes in microseconds.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {

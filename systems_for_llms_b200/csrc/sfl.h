@@ -203,8 +203,12 @@ int sfl_ipc_close_handle(void* ptr);
 long sfl_comm_flag_bytes(void); /* size every rank's flag buffer must have           */
 int sfl_comm_slots(void);       /* independent barrier slots (one per bucket/use)    */
 int sfl_comm_max_ctas(void);
-/* Polling budget of peer waits in ~200 ns iterations (default 2^23, about 2 s). */
+/* Polling budget of every peer wait, in iterations of about 200 ns.  The default (48 x 2^20,
+ * about ten seconds) is sized for the skew between the ranks of a training job; tests of
+ * the timeout path set a millisecond.  Covers the collectives and the fused GEMM +
+ * all-reduce kernels (sfl_gemm_tp_set_spin_limit sets only the latter). */
 int sfl_comm_set_spin_limit(unsigned iterations);
+int sfl_gemm_tp_set_spin_limit(unsigned iterations);
 
 typedef struct SflComm {
   int rank, world;   /* world <= 8                                               */

@@ -57,16 +57,41 @@ def is_current() -> bool:
             and STAMP_PATH.read_text().strip() == source_hash())
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every ``csrc/*.cu`` for sm_100a and link ``libsfl_b200.so``."""
+def build(force: bool = False, verbose: bool = False, *, defines: tuple[str, ...] = (),
+          output: Path | None = None) -> Path:
+    """Compile every ``csrc/*.cu`` for sm_100a and link ``libsfl_b200.so``.
+
+    ``defines`` (e.g. ``("SFL_DEBUG_BOUNDS",)``) builds an instrumented variant; it must be
+    given its own ``output`` path and is loaded by setting ``SFL_LIBRARY`` to that path
+    before the first kernel call (``ops/lib.py``).  Concurrent callers (the ranks of one
+    job started on a fresh checkout) serialise on a lock file and re-check the stamp once
+    they hold it, so only the first one compiles.
+    """
+    if defines:
+        if output is None:
+            raise ValueError("an instrumented build needs its own output path")
+        return _compile(Path(output), Path(output).with_suffix(".objects"), verbose, defines)
     if not force and is_current():
         return LIB_PATH
+    import fcntl
+    with open(LIB_DIR / "libsfl_b200.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and is_current():      # another process built it meanwhile
+                return LIB_PATH
+            _compile(LIB_PATH, LIB_DIR / "build", verbose, ())
+            STAMP_PATH.write_text(source_hash() + "\n")
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+    return LIB_PATH
+
+
+def _compile(target: Path, build_dir: Path, verbose: bool, defines: tuple[str, ...]) -> Path:
     nvcc = _nvcc()
     if nvcc is None:
         raise RuntimeError("nvcc not found; cannot build the sm_100a kernel library")
-    build_dir = LIB_DIR / "build"
-    build_dir.mkdir(exist_ok=True)
-    extra = ["-Xptxas", "-v"] if verbose else []
+    build_dir.mkdir(parents=True, exist_ok=True)
+    extra = (["-Xptxas", "-v"] if verbose else []) + [f"-D{name}" for name in defines]
 
     def compile_one(src: Path) -> Path:
         obj = build_dir / (src.stem + ".o")
@@ -80,16 +105,19 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
         objects = list(pool.map(compile_one, sources()))
-    temporary = LIB_PATH.with_suffix(".so.tmp")
+    temporary = target.with_suffix(f".tmp{os.getpid()}")
     link = [nvcc, "-shared", "-o", str(temporary), *map(str, objects)]
     result = subprocess.run(link, capture_output=True, text=True)
     if result.returncode != 0:
         raise RuntimeError(f"link failed:\n{result.stderr}")
-    os.replace(temporary, LIB_PATH)
-    STAMP_PATH.write_text(source_hash() + "\n")
-    return LIB_PATH
+    os.replace(temporary, target)
+    return target
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    # python -m systems_for_llms_b200.ops.build [--force] [--verbose] [-DNAME ... --output PATH]
+    names = tuple(arg[2:] for arg in sys.argv[1:] if arg.startswith("-D"))
+    out = Path(sys.argv[sys.argv.index("--output") + 1]) if "--output" in sys.argv else None
+    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, defines=names,
+                 output=out)
     print(path)

@@ -46,6 +46,32 @@ def check_status(device: torch.device | None = None) -> None:
             raise RuntimeError(f"sm_100a kernel reported status {code} on {dev}")
 
 
+def status_report(device: torch.device) -> torch.Tensor:
+    """The status word of ``device`` as a one-element fp32 tensor on that device (zero when
+    no kernel of this library has run there), for a trainer to append to the values it reads
+    back every step anyway: a wait that ran out then stops the run at that step instead of
+    letting it continue on incomplete gradients or activations."""
+    device = torch.device(device)
+    if device.type != "cuda":
+        return torch.zeros(1, device=device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    word = _status_words.get(device)
+    if word is None:
+        return torch.zeros(1, device=device)
+    return word.to(torch.float32)
+
+
+def raise_on_status(code: float, device) -> None:
+    """Counterpart of ``status_report`` once the value is on the host."""
+    if code != 0:
+        word = _status_words.get(torch.device(device))
+        if word is not None:
+            word.zero_()
+        raise RuntimeError(f"sm_100a kernel reported status {int(code)} on {device}: a bounded "
+                           "wait ran out, so this step's results are incomplete")
+
+
 def _operand(t: torch.Tensor) -> tuple[int, int]:
     if t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
         raise ValueError("GEMM operands must be 2-D bf16 with a contiguous last dimension")

@@ -9,6 +9,7 @@ can never pass on the wrong code path.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_long, c_uint, c_void_p
 from functools import lru_cache
 
@@ -142,9 +143,16 @@ class _Library:
 
 @lru_cache(maxsize=1)
 def lib() -> "_Library":
-    if not _build.LIB_PATH.exists() or not _build.is_current():
-        _build.build()
-    handle = ctypes.CDLL(str(_build.LIB_PATH))
+    """The kernel library.  ``SFL_LIBRARY=/path/lib.so`` loads an instrumented variant built
+    with ``ops.build.build(defines=..., output=...)`` (bounds-checked stores, phase timers)
+    instead of the in-tree optimised build."""
+    override = os.environ.get("SFL_LIBRARY")
+    if override:
+        handle = ctypes.CDLL(override)
+    else:
+        if not _build.LIB_PATH.exists() or not _build.is_current():
+            _build.build()
+        handle = ctypes.CDLL(str(_build.LIB_PATH))
     library = _Library(handle)
     for name, argtypes in {**_SIGNATURES, **_OPTIONAL}.items():
         library._bind(name, argtypes)

@@ -294,8 +294,11 @@ def train_step(strategy: Strategy, data, config, sampler, device, *, global_batc
     # update skips itself on a non-finite norm, so the vote can ride along with
     # the single read-back at the end of the step without changing the outcome.
     norm = strategy.reduce_and_update()
-    report = torch.stack([loss_sum.float(), torch.isfinite(loss_sum).float(),
-                          norm.float().to(device)])
+    # The device status word rides along: a peer or pipeline wait that ran out during this
+    # step must stop the run here, not after the last step.
+    from ..ops.gemm import raise_on_status, status_report
+    report = torch.cat([torch.stack([loss_sum.float(), torch.isfinite(loss_sum).float(),
+                                     norm.float().to(device)]), status_report(device)])
     if world > 1:
         # one collective: the loss sums, and so do the finiteness votes (all ranks
         # finite <=> the votes add up to the world size)
@@ -303,7 +306,8 @@ def train_step(strategy: Strategy, data, config, sampler, device, *, global_batc
         dist.all_reduce(votes)
         report[:2] = votes
         report[1] = (votes[1] >= world - 0.5).float()
-    mean_loss, finite, norm_value = report.tolist()
+    mean_loss, finite, norm_value, status_code = report.tolist()
+    raise_on_status(status_code, device)
     if not finite:
         raise FloatingPointError("Non-finite training loss on a rank")
     if not math.isfinite(norm_value):

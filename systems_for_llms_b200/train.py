@@ -128,7 +128,10 @@ def train_step(model: TransformerLM, optimizer: torch.optim.Optimizer, data: np.
         norm = torch.nn.utils.clip_grad_norm_(model.parameters(), config.grad_clip,
                                               error_if_nonfinite=True)
         optimizer.step()
-    loss_value, norm_value = torch.stack([running.float(), norm.float().to(device)]).tolist()
+    from .ops.gemm import raise_on_status, status_report
+    loss_value, norm_value, status_code = torch.cat(
+        [torch.stack([running.float(), norm.float().to(device)]), status_report(device)]).tolist()
+    raise_on_status(status_code, device)
     if not math.isfinite(loss_value):
         raise FloatingPointError("non-finite training loss")
     if not math.isfinite(norm_value):
