@@ -203,6 +203,12 @@ __device__ __forceinline__ RowMask row_mask_for_key(const AttnSchedule& s, int k
   return m;
 }
 
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -699,13 +705,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 // keeps P in a swizzled shared-memory tile instead.
 //
 // Work items are numbered heaviest first and dealt to the 2 x grid slots in rounds
-// of alternating direction, as in the one-stream kernel below.  The order of a
-// slot's MMAs - S(j), then for every tile [P V(j), S(j+1)] - together with the
-// in-order execution of one thread's tcgen05.mma instructions makes most hand-overs
-// implicit: when the softmax warps see S(j) complete, P V(j-1) has completed too, so
-// the P tile and the output accumulator may be touched, and the K tile of step j and
-// the V tile of step j-1 handed back to the TMA warp, without a further wait or a
-// tcgen05.commit of their own (the MMA thread issues one commit per tile).
+// of alternating direction, as in the one-stream kernel below.
+//
+// Inside a slot the softmax warps copy a finished score tile into registers and hand
+// the tensor-memory tile straight back (s_free), so the MMA warp issues S(j+1) while
+// the softmax of tile j is still computing: when its P tile is written, the next
+// scores are already there and the turn-around of the tensor pipe (barrier, issue,
+// execution, commit: about 2,000 cycles) is off the critical path.  P therefore has
+// columns of its own next to the score tile (per slot: S 128, P 64, O 64 columns of
+// tensor memory).  Before the softmax warps touch P or the accumulator again they
+// wait for the previous P V product (pv_done), which by then has long finished.
 constexpr int kFwd2Threads = 384;  // per slot: TMA warp, MMA warp, softmax warpgroup
 
 template <bool P_TMEM>
@@ -724,8 +733,9 @@ struct Fwd2SlotBars {
   uint64_t q_full[2], q_empty[2];
   uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
   uint64_t s_full;   // score tile complete (MMA commit)
+  uint64_t s_free;   // score tile copied to registers (128 arrivals)
   uint64_t p_ready;  // P tile written, accumulator rescaled (128 arrivals)
-  uint64_t o_full;   // last P V product of an item complete (MMA commit)
+  uint64_t pv_done;  // P V product complete (MMA commit); the item's last one ends it
   uint64_t o_free;   // epilogue has read the accumulator (128 arrivals)
   int col_doc[kTile];
 };
@@ -758,10 +768,18 @@ __device__ __forceinline__ void named_barrier_slot(int slot) {
 // Phase timers of CTA 0 (cycles, summed), compiled in with -DSFL_ATTN_TRACE and read back
 // with sfl_attn_trace_read: softmax warp 0 of slot 0 - [0] waiting for scores, [1] loading
 // them, [2] row maximum and rescale, [3] exponentials and P store, [4] epilogue, [5] tiles;
-// MMA thread of slot 0 - [8] waiting for P and V, [9] issuing a P V product, [10] waiting
-// for K (and Q), [11] issuing a score product and its commit, [12] tiles.
+// [6] waiting for the previous P V product; MMA warp of slot 0 - [8] waiting for P and V,
+// [9] issuing a P V product, [10] waiting for the score tile to be free and for K (and Q),
+// [11] issuing a score product, [12] tiles.
 #ifdef SFL_ATTN_TRACE
 __device__ unsigned long long g_attn_trace[16];
+__device__ unsigned long long g_attn_stamps[64];  // globaltimer of CTA 0: see SFL_STAMP uses
+__device__ __forceinline__ void attn_stamp(int at) {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  if (at < 64) g_attn_stamps[at] = t;
+}
+#define SFL_STAMP(cond, at) if (cond) attn_stamp(at);
 #define SFL_TRACE_DECL(cond)      \
   const bool tracing_ = (cond);   \
   long long trace_t_ = clock64();
@@ -777,12 +795,19 @@ __device__ unsigned long long g_attn_trace[16];
 #define SFL_TRACE_DECL(cond)
 #define SFL_TRACE_MARK(slot)
 #define SFL_TRACE_COUNT(slot)
+#define SFL_STAMP(cond, at)
 #endif
 
 template <bool FP16, bool P_TMEM>
 __global__ void __launch_bounds__(kFwd2Threads, 1)
 attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+#ifdef SFL_ATTN_TRACE
+  const long long kernel_t0 = clock64();
+  unsigned long long kernel_ns0;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(kernel_ns0));
+#endif
+  SFL_STAMP(blockIdx.x == 0 && threadIdx.x == 0, 0)
   constexpr int D = 64;
   using L = Fwd2Smem<P_TMEM>;
   constexpr int QB = L::kQBufs;
@@ -821,8 +846,9 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mbar_init(&b.v_empty[s], 1);
       }
       mbar_init(&b.s_full, 1);
+      mbar_init(&b.s_free, 128);
       mbar_init(&b.p_ready, 128);
-      mbar_init(&b.o_full, 1);
+      mbar_init(&b.pv_done, 1);
       mbar_init(&b.o_free, 128);
     }
     sh->abort = 0;
@@ -839,12 +865,15 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sh->tmem_base;
+  SFL_STAMP(blockIdx.x == 0 && threadIdx.x == 0, 1)
   pdl_launch_dependents();
   pdl_wait();
+  SFL_STAMP(blockIdx.x == 0 && threadIdx.x == 0, 2)
   volatile int* abort = &sh->abort;
-  // tensor memory: score tiles at columns [0,128) and [128,256), outputs at 256 and 320
-  const uint32_t tS = tmem + static_cast<uint32_t>(w * kTile);
-  const uint32_t tO = tmem + static_cast<uint32_t>(256 + w * D);
+  // tensor memory of a slot: scores [0,128), P as 16-bit pairs [128,192), output [192,256)
+  const uint32_t tS = tmem + static_cast<uint32_t>(w * 256);
+  const uint32_t tP = tS + 128;
+  const uint32_t tO = tS + 192;
 
   if (warp == 0 || warp == 2) {
     // ---------------------------------------------------- TMA producer ----
@@ -886,7 +915,13 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else if (warp == 1 || warp == 3) {
     // ------------------------------------------------------ MMA issuer ----
-    if (lane == 0) {
+    // The whole warp walks the loop and waits on the barriers together; one elected
+    // lane issues.  With warp-uniform control flow the descriptors, tensor-memory
+    // addresses and loop counters live in uniform registers, which is where
+    // tcgen05.mma takes its operands from: issuing from inside a single-lane branch
+    // costs a register-to-uniform move per operand and made the issue of a 128 x 64 x 16
+    // product slower than its execution.
+    {
       constexpr uint32_t idesc_qk = idesc_16bit(FP16, kTile, kTile, false, false);
       constexpr uint32_t idesc_pv = idesc_16bit(FP16, kTile, D, false, true);
       // descriptors of the first reduction step of every buffer; the others follow by
@@ -914,11 +949,14 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         qk_done = true;
       };
       uint32_t qk_it = 0, q_qi = 0;
-      SFL_TRACE_DECL(blockIdx.x == 0 && warp == 1)
-      auto issue_qk = [&]() -> bool {
+      SFL_TRACE_DECL(blockIdx.x == 0 && warp == 1 && lane == 0)
+      auto issue_qk = [&](bool after_tile, uint32_t prev) -> bool {
         if (qk_done) return true;
         const int qb = q_qi % QB;
         const int s = qk_it & 1;
+        if (after_tile &&
+            !bounded_wait(&bar.s_free, prev & 1, abort, p.status, kStatusTimeoutTmemEmpty))
+          return false;
         if (qk_j == 0 && !bounded_wait(&bar.q_full[qb], (q_qi / QB) & 1, abort, p.status,
                                        kStatusTimeoutFull))
           return false;
@@ -928,14 +966,18 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         SFL_TRACE_MARK(10)
         const uint64_t qd = umma_desc_advance(q_desc0, qb * L::kTileBytes);
         const uint64_t kd = umma_desc_advance(k_desc0, s * L::kTileBytes);
+        const bool last = qk_j + 1 == qk_n;
+        if (elect_one()) {
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k)
-          umma_bf16_ss(tS, umma_desc_advance(qd, k * 32), umma_desc_advance(kd, k * 32), idesc_qk,
-                       k != 0);
-        umma_commit(&bar.s_full);
+          for (int k = 0; k < D / 16; ++k)
+            umma_bf16_ss(tS, umma_desc_advance(qd, k * 32), umma_desc_advance(kd, k * 32),
+                         idesc_qk, k != 0);
+          umma_commit(&bar.s_full);
+          if (last) umma_commit(&bar.q_empty[qb]);
+        }
+        __syncwarp();
         ++qk_it;
         if (++qk_j == qk_n) {
-          umma_commit(&bar.q_empty[qb]);
           ++q_qi;
           qk_advance();
         }
@@ -943,7 +985,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         return true;
       };
       qk_advance();
-      bool ok = issue_qk();
+      bool ok = issue_qk(false, 0);
       uint32_t it = 0, items = 0;
       int item;
       while (ok && (item = walk.next()) >= 0) {
@@ -951,6 +993,9 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int n_tiles = range.end - range.begin;
         if (n_tiles <= 0) continue;
         for (int j = 0; j < n_tiles && ok; ++j, ++it) {
+          // scores of the next tile as soon as the softmax warps have copied this one
+          ok = issue_qk(true, it);
+          if (!ok) break;
           const int s = it & 1;
           if (!bounded_wait(&bar.p_ready, it & 1, abort, p.status, kStatusTimeoutTmemFull) ||
               !bounded_wait(&bar.v_full[s], (it >> 1) & 1, abort, p.status, kStatusTimeoutFull) ||
@@ -963,25 +1008,25 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tc_fence_after();
           SFL_TRACE_MARK(8)
           const uint64_t vd = umma_desc_advance(v_desc0, s * L::kTileBytes);
-          if constexpr (P_TMEM) {
+          if (elect_one()) {
+            if constexpr (P_TMEM) {
 #pragma unroll
-            for (int k = 0; k < kTile / 16; ++k)
-              umma_bf16_ts(tO, tS + k * 8, umma_desc_advance(vd, k * 2048), idesc_pv,
-                           (j | k) != 0);
-          } else {
+              for (int k = 0; k < kTile / 16; ++k)
+                umma_bf16_ts(tO, tP + k * 8, umma_desc_advance(vd, k * 2048), idesc_pv,
+                             (j | k) != 0);
+            } else {
 #pragma unroll
-            for (int k = 0; k < kTile / 16; ++k)
-              umma_bf16_ss(tO, umma_desc_advance(p_desc0, (k >> 2) * (kTile * 128) + (k & 3) * 32),
-                           umma_desc_advance(vd, k * 2048), idesc_pv, (j | k) != 0);
+              for (int k = 0; k < kTile / 16; ++k)
+                umma_bf16_ss(tO,
+                             umma_desc_advance(p_desc0, (k >> 2) * (kTile * 128) + (k & 3) * 32),
+                             umma_desc_advance(vd, k * 2048), idesc_pv, (j | k) != 0);
+            }
+            umma_commit(&bar.pv_done);
           }
-          if (j == n_tiles - 1) {
-            umma_commit(&bar.o_full);
-            ++items;
-          }
+          __syncwarp();
+          if (j == n_tiles - 1) ++items;
           SFL_TRACE_MARK(9)
           SFL_TRACE_COUNT(12)
-          // the score tile of step it + 1 goes where P of this step is: in order, after
-          ok = issue_qk();
         }
       }
     }
@@ -1012,17 +1057,15 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           break;
         }
         tc_fence_after();
-        // S(j) complete: the score product has read K(j), and P V(j-1), issued before it,
-        // has read V(j-1).
-        if (leader) {
-          mbar_arrive(&bar.k_empty[it & 1]);
-          if (j > 0) mbar_arrive(&bar.v_empty[(it - 1) & 1]);
-        }
+        if (leader) mbar_arrive(&bar.k_empty[it & 1]);  // the score product has read K(j)
+        SFL_STAMP(blockIdx.x == 0 && warp == 4 && lane == 0, 8 + 2 * static_cast<int>(it))
         SFL_TRACE_MARK(0)
         float x[kTile];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld_32x32f(tS + lane_base + c * 32, x + c * 32);
         tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(&bar.s_free);  // the next scores may overwrite the tile
         SFL_TRACE_MARK(1)
         const int k0 = t.other * kTile;
         const bool ragged = (k0 + kTile > p.N) || (q_tile * kTile + kTile > p.N);
@@ -1036,14 +1079,26 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             apply_doc_mask(x, bar.col_doc, q < p.N ? p.sched.doc[q] : -2);
           }
         }
+        // three-input maxima: 64 instructions instead of 127, in eight independent chains
         float mx8[8];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) mx8[c] = x[c];
+        for (int c = 0; c < 8; ++c) mx8[c] = fmaxf(x[2 * c], x[2 * c + 1]);
 #pragma unroll
-        for (int c = 8; c < kTile; ++c) mx8[c & 7] = fmaxf(mx8[c & 7], x[c]);
-        float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                         fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+        for (int c = 16; c < kTile; c += 2) mx8[(c >> 1) & 7] = fmax3(mx8[(c >> 1) & 7], x[c], x[c + 1]);
+        float mx = fmax3(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(mx8[3], mx8[4], mx8[5]),
+                         fmaxf(mx8[6], mx8[7]));
         mx *= scale_log2;
+        SFL_TRACE_MARK(2)
+        // P and the accumulator belong to the previous P V product until it is done.
+        if (j > 0) {
+          if (!bounded_wait(&bar.pv_done, (it - 1) & 1, abort, p.status, kStatusTimeoutTmemFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          if (leader) mbar_arrive(&bar.v_empty[(it - 1) & 1]);
+        }
+        SFL_TRACE_MARK(6)
         // Lazy rescale: keep a stale maximum until it is off by more than 2^8.
         const bool grow = mx > m_used + 8.0f;
         if (__any_sync(0xffffffffu, grow)) {
@@ -1064,7 +1119,6 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-        SFL_TRACE_MARK(2)
         if constexpr (P_TMEM) {
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
@@ -1076,8 +1130,8 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               sum4[(i >> 1) & 3] += p0 + p1;
               packed[i >> 1] = pack2<FP16>(p0, p1);
             }
-            // P over its own scores: 16-bit pairs, 16 columns per 32 scores
-            tmem_st_32x16(tS + lane_base + c * 16, packed);
+            // 16-bit pairs: 16 columns of tensor memory per 32 probabilities
+            tmem_st_32x16(tP + lane_base + c * 16, packed);
           }
           tmem_st_wait();
         } else {
@@ -1096,14 +1150,16 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         tc_fence_before();
         mbar_arrive(&bar.p_ready);
+        SFL_STAMP(blockIdx.x == 0 && warp == 4 && lane == 0, 9 + 2 * static_cast<int>(it))
         SFL_TRACE_MARK(3)
         SFL_TRACE_COUNT(5)
       }
       if (!ok) break;
-      if (n_tiles > 0) {
-        if (!bounded_wait(&bar.o_full, items & 1, abort, p.status, kStatusTimeoutTmemFull)) break;
+      if (n_tiles > 0) {  // the item's last P V product
+        if (!bounded_wait(&bar.pv_done, (it - 1) & 1, abort, p.status, kStatusTimeoutTmemFull))
+          break;
         tc_fence_after();
-        if (leader) mbar_arrive(&bar.v_empty[(it - 1) & 1]);  // the item's last V tile
+        if (leader) mbar_arrive(&bar.v_empty[(it - 1) & 1]);
       }
       const float inv = l > 0.f ? 1.0f / l : 0.f;
       uint8_t* orow = static_cast<uint8_t*>(p.o) +
@@ -1138,11 +1194,22 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (q < p.N && p.lse != nullptr)
         p.lse[(static_cast<long>(b) * p.H + h) * p.N + q] =
             l > 0.f ? (m_used + log2f(l)) * kLn2 : -INFINITY;
+      SFL_STAMP(blockIdx.x == 0 && warp == 4 && lane == 0, 40 + static_cast<int>(items))
       SFL_TRACE_MARK(4)
     }
   }
   tc_fence_before();
   __syncthreads();
+  SFL_STAMP(blockIdx.x == 0 && threadIdx.x == 0, 3)
+#ifdef SFL_ATTN_TRACE
+  if (threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) {
+    unsigned long long ns1;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(ns1));
+    const int at = blockIdx.x == 0 ? 13 : 14;   // [13] CTA 0, [14] last CTA: cycles in the kernel
+    atomicAdd(&g_attn_trace[at], static_cast<unsigned long long>(clock64() - kernel_t0));
+    if (blockIdx.x == 0) atomicAdd(&g_attn_trace[15], ns1 - kernel_ns0);  // [15] nanoseconds, CTA 0
+  }
+#endif
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
@@ -1794,6 +1861,16 @@ extern "C" int sfl_attn_trace_read(unsigned long long* out16) {
   return static_cast<int>(cudaMemcpyToSymbol(g_attn_trace, zero, sizeof(zero)));
 #else
   (void)out16;
+  return -1;
+#endif
+}
+
+// The raw time stamps (nanoseconds) of the last traced launch; -1 without -DSFL_ATTN_TRACE.
+extern "C" int sfl_attn_stamps_read(unsigned long long* out64) {
+#ifdef SFL_ATTN_TRACE
+  return static_cast<int>(cudaMemcpyFromSymbol(out64, g_attn_stamps, 64 * sizeof(unsigned long long)));
+#else
+  (void)out64;
   return -1;
 #endif
 }
