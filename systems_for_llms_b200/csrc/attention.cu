@@ -1323,7 +1323,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && n_tiles > 0) {
+    // The whole warp walks the loop; one elected lane issues, so that descriptors and
+    // tensor-memory addresses stay in uniform registers (see attn_fwd2_kernel).
+    if (n_tiles > 0) {
       // The streamed tile is handled as two halves of 64 columns so that the tensor
       // pipe works on the scores of half h+1 and the accumulation of half h-1 while
       // the compute warps turn half h into probabilities: TMEM columns and the
@@ -1352,17 +1354,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
         // rows [64 hh, 64 hh + 64) of the streamed pair (A then B, kTileBytes apart)
         const uint64_t in_a = umma_desc_advance(in_k0, s * 2 * L::kTileBytes + hh * 64 * 128);
         const uint64_t in_b = umma_desc_advance(in_a, L::kTileBytes);
+        if (elect_one()) {
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k)  // S^T = K Q^T   or   S = Q K^T
-          umma_bf16_ss(tS + hh * 64, own_a[k],
-                       umma_desc_advance(in_a, (k >> 2) * (kTile * 128) + (k & 3) * 32), idesc_s,
-                       k != 0);
+          for (int k = 0; k < D / 16; ++k)  // S^T = K Q^T   or   S = Q K^T
+            umma_bf16_ss(tS + hh * 64, own_a[k],
+                         umma_desc_advance(in_a, (k >> 2) * (kTile * 128) + (k & 3) * 32), idesc_s,
+                         k != 0);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k)  // dP^T = V dO^T  or  dP = dO V^T
-          umma_bf16_ss(tDP + hh * 64, own_b[k],
-                       umma_desc_advance(in_b, (k >> 2) * (kTile * 128) + (k & 3) * 32), idesc_s,
-                       k != 0);
-        umma_commit(&bars->sp_full[hh]);
+          for (int k = 0; k < D / 16; ++k)  // dP^T = V dO^T  or  dP = dO V^T
+            umma_bf16_ss(tDP + hh * 64, own_b[k],
+                         umma_desc_advance(in_b, (k >> 2) * (kTile * 128) + (k & 3) * 32), idesc_s,
+                         k != 0);
+          umma_commit(&bars->sp_full[hh]);
+        }
+        __syncwarp();
         return true;
       };
       bool ok = bounded_wait(&bars->own_full, 0, abort, p.status, kStatusTimeoutFull);
@@ -1384,23 +1389,26 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
         const uint64_t mn_b = umma_desc_advance(mn_a, L::kTileBytes);
         const uint64_t p_half = umma_desc_advance(p_k0, hh * (kTile * 128));
         const uint64_t ds_half = umma_desc_advance(ds_k0, hh * (kTile * 128));
-        if constexpr (KV_OWNED) {
+        if (elect_one()) {
+          if constexpr (KV_OWNED) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k)  // dV += P^T dO
-            umma_bf16_ss(tAcc0, umma_desc_advance(p_half, k * 32),
-                         umma_desc_advance(mn_b, k * 2048), idesc_acc, (h | k) != 0);
+            for (int k = 0; k < 4; ++k)  // dV += P^T dO
+              umma_bf16_ss(tAcc0, umma_desc_advance(p_half, k * 32),
+                           umma_desc_advance(mn_b, k * 2048), idesc_acc, (h | k) != 0);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)  // dK += dS^T Q
-            umma_bf16_ss(tAcc1, umma_desc_advance(ds_half, k * 32),
-                         umma_desc_advance(mn_a, k * 2048), idesc_acc, (h | k) != 0);
-        } else {
+            for (int k = 0; k < 4; ++k)  // dK += dS^T Q
+              umma_bf16_ss(tAcc1, umma_desc_advance(ds_half, k * 32),
+                           umma_desc_advance(mn_a, k * 2048), idesc_acc, (h | k) != 0);
+          } else {
 #pragma unroll
-          for (int k = 0; k < 4; ++k)  // dQ += dS K
-            umma_bf16_ss(tAcc0, umma_desc_advance(ds_half, k * 32),
-                         umma_desc_advance(mn_a, k * 2048), idesc_acc, (h | k) != 0);
+            for (int k = 0; k < 4; ++k)  // dQ += dS K
+              umma_bf16_ss(tAcc0, umma_desc_advance(ds_half, k * 32),
+                           umma_desc_advance(mn_a, k * 2048), idesc_acc, (h | k) != 0);
+          }
+          if (hh == 1) umma_commit(&bars->in_empty[s]);
+          umma_commit(&bars->acc_done[hh]);
         }
-        if (hh == 1) umma_commit(&bars->in_empty[s]);
-        umma_commit(&bars->acc_done[hh]);
+        __syncwarp();
         if (more && !early && !issue_scores(h + 1)) break;
       }
     }

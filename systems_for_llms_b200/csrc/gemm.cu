@@ -767,8 +767,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
   } else if (warp == 1) {
     // -------------------------------------------------------- MMA issuer ----
-    if (lane == 0) {
+    // The whole warp walks the loops and waits on the barriers; one elected lane
+    // issues.  Control flow and every operand (descriptors, tensor-memory address,
+    // counters) are then warp-uniform and live in uniform registers, which is where
+    // tcgen05.mma reads its operands: issued from inside a one-lane branch each MMA
+    // pays for moving them there, which costs more than a 128 x 128 x 16 product takes.
+    {
       constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      const uint32_t smem_base = smem_u32(smem);
+      const uint64_t a_desc0 = A_MN ? umma_smem_desc(smem_base, BK * 128, 1024)
+                                    : umma_smem_desc(smem_base, 16, 1024);
+      const uint64_t b_desc0 = B_MN ? umma_smem_desc(smem_base + kTileABytes, BK * 128, 1024)
+                                    : umma_smem_desc(smem_base + kTileABytes, 16, 1024);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -790,24 +800,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             break;
           }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + stage * Cfg::kStageBytes);
-          const uint32_t b_addr = a_addr + kTileABytes;
+          const uint64_t a_stage = umma_desc_advance(a_desc0, stage * Cfg::kStageBytes);
+          const uint64_t b_stage = umma_desc_advance(b_desc0, stage * Cfg::kStageBytes);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t a_desc = A_MN ? umma_smem_desc(a_addr + k * 2048, BK * 128, 1024)
-                                         : umma_smem_desc(a_addr + k * 32, 16, 1024);
-            const uint64_t b_desc = B_MN ? umma_smem_desc(b_addr + k * 2048, BK * 128, 1024)
-                                         : umma_smem_desc(b_addr + k * 32, 16, 1024);
-            umma_bf16_ss(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0);
+            for (int k = 0; k < BK / 16; ++k)
+              umma_bf16_ss(d_tmem, umma_desc_advance(a_stage, k * (A_MN ? 2048 : 32)),
+                           umma_desc_advance(b_stage, k * (B_MN ? 2048 : 32)), idesc,
+                           (kb | k) != 0);
+            umma_commit(&bars->empty[stage]);
+            if (kb == num_kb - 1) umma_commit(&bars->tmem_full[acc]);
           }
-          umma_commit(&bars->empty[stage]);
+          __syncwarp();
           if (++stage == Cfg::kStages) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (!ok) break;
-        umma_commit(&bars->tmem_full[acc]);
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1;
@@ -993,8 +1003,12 @@ wgrad_grouped_kernel(const __grid_constant__ GroupedMaps maps,
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    // converged warp, one elected issuing lane (see gemm_kernel)
+    {
       constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, true, true);
+      const uint32_t smem_base = smem_u32(smem);
+      const uint64_t a_desc0 = umma_smem_desc(smem_base, BK * 128, 1024);
+      const uint64_t b_desc0 = umma_smem_desc(smem_base + kTileABytes, BK * 128, 1024);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -1017,22 +1031,23 @@ wgrad_grouped_kernel(const __grid_constant__ GroupedMaps maps,
             break;
           }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + stage * Cfg::kStageBytes);
-          const uint32_t b_addr = a_addr + kTileABytes;
+          const uint64_t a_stage = umma_desc_advance(a_desc0, stage * Cfg::kStageBytes);
+          const uint64_t b_stage = umma_desc_advance(b_desc0, stage * Cfg::kStageBytes);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t a_desc = umma_smem_desc(a_addr + k * 2048, BK * 128, 1024);
-            const uint64_t b_desc = umma_smem_desc(b_addr + k * 2048, BK * 128, 1024);
-            umma_bf16_ss(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0);
+            for (int k = 0; k < BK / 16; ++k)
+              umma_bf16_ss(d_tmem, umma_desc_advance(a_stage, k * 2048),
+                           umma_desc_advance(b_stage, k * 2048), idesc, (kb | k) != 0);
+            umma_commit(&bars->empty[stage]);
+            if (kb == num_kb - 1) umma_commit(&bars->tmem_full[acc]);
           }
-          umma_commit(&bars->empty[stage]);
+          __syncwarp();
           if (++stage == Cfg::kStages) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (!ok) break;
-        umma_commit(&bars->tmem_full[acc]);
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1;
@@ -1272,8 +1287,13 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    // converged warp, one elected issuing lane (see gemm_kernel)
+    {
       constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, false, B_MN);
+      const uint32_t smem_base = smem_u32(smem);
+      const uint64_t a_desc0 = umma_smem_desc(smem_base, 16, 1024);
+      const uint64_t b_desc0 = B_MN ? umma_smem_desc(smem_base + kTileABytes, BK * 128, 1024)
+                                    : umma_smem_desc(smem_base + kTileABytes, 16, 1024);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -1295,23 +1315,24 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             break;
           }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + stage * Cfg::kStageBytes);
-          const uint32_t b_addr = a_addr + kTileABytes;
+          const uint64_t a_stage = umma_desc_advance(a_desc0, stage * Cfg::kStageBytes);
+          const uint64_t b_stage = umma_desc_advance(b_desc0, stage * Cfg::kStageBytes);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t a_desc = umma_smem_desc(a_addr + k * 32, 16, 1024);
-            const uint64_t b_desc = B_MN ? umma_smem_desc(b_addr + k * 2048, BK * 128, 1024)
-                                         : umma_smem_desc(b_addr + k * 32, 16, 1024);
-            umma_bf16_ss(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0);
+            for (int k = 0; k < BK / 16; ++k)
+              umma_bf16_ss(d_tmem, umma_desc_advance(a_stage, k * 32),
+                           umma_desc_advance(b_stage, k * (B_MN ? 2048 : 32)), idesc,
+                           (kb | k) != 0);
+            umma_commit(&bars->empty[stage]);
+            if (kb == num_kb - 1) umma_commit(&bars->tmem_full[acc]);
           }
-          umma_commit(&bars->empty[stage]);
+          __syncwarp();
           if (++stage == Cfg::kStages) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (!ok) break;
-        umma_commit(&bars->tmem_full[acc]);
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1;
