@@ -1,6 +1,7 @@
 """Headline benchmark: training throughput of the 324M decoder at sequence 1024.
 
     python bench.py --gpus N --steps K --warmup W [--impl ours|reference] [--mode MODE]
+                    [--checkpointing none|block] [--seq-len S --global-batch B --microbatch M]
 
 Metric and configuration are the reference's distributed protocol (324,092,928
 parameters, bf16 autocast with fp32 parameters and AdamW state, global batch 32 x
@@ -9,6 +10,8 @@ process drives one GPU (``--mode single``, 8 accumulation steps); N processes
 under ``torch.distributed.run`` train data-parallel (``ddp`` by default; ``zero1``,
 ``fsdp`` and ``tp`` selectable) on the same global batch, so scaling is strong.
 Token ids are synthetic uniform-random, weights are randomly initialised.
+``--seq-len 4096 --global-batch 8 --microbatch 1`` is the reference's long-context
+workload (same model, same tokens per update); both arms honour the three flags.
 
 Two numbers are reported.  ``value`` is timed on the device with CUDA events
 around exactly K optimizer steps whose token batches already sit in device
@@ -35,13 +38,30 @@ from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
 METRIC = "tokens/s 324M s1024 @1/2/4/8 B200 (DDP/shard/FSDP/TP), max over ranks; peak GiB"
-GLOBAL_BATCH, MICROBATCH, SEQ = 32, 4, 1024
+GLOBAL_BATCH, MICROBATCH, SEQ = 32, 4, 1024      # defaults; main() applies the flags
 PUBLISHED = {  # tokens/s on 8xH200 / 1xH200 from the reference's confirmation study
     ("single", 1): 67021.0, ("ddp", 2): 126224.0, ("ddp", 4): 226220.0, ("ddp", 8): 397738.0,
     ("zero1", 2): 121692.0, ("zero1", 4): 218501.0, ("zero1", 8): 353293.0,
     ("fsdp", 2): 70471.0, ("fsdp", 4): 134447.0, ("fsdp", 8): 231534.0,
     ("tp", 2): 60115.0, ("tp", 4): 57363.0, ("tp", 8): 55733.0,
 }
+PUBLISHED_BLOCK = {("single", 1): 35587.0, ("ddp", 8): 213460.0, ("fsdp", 2): 44347.0,
+                   ("fsdp", 4): 80889.0, ("fsdp", 8): 150249.0, ("tp", 2): 31988.0,
+                   ("tp", 4): 30117.0, ("tp", 8): 27414.0}
+PUBLISHED_S4096 = {("single", 1, "none"): 63273.0, ("single", 1, "block"): 34239.0,
+                   ("ddp", 8, "none"): 395309.0, ("ddp", 8, "block"): 195089.0,
+                   ("zero1", 8, "block"): 183612.0, ("fsdp", 8, "block"): 147702.0,
+                   ("tp", 8, "block"): 27775.0}
+
+
+def published_for(mode: str, world: int, checkpointing: str):
+    """The reference's published tokens/s for this workload (H200), or None."""
+    if (GLOBAL_BATCH, MICROBATCH, SEQ) == (32, 4, 1024):
+        table = PUBLISHED if checkpointing == "none" else PUBLISHED_BLOCK
+        return table.get((mode, world))
+    if (GLOBAL_BATCH, MICROBATCH, SEQ) == (8, 1, 4096):
+        return PUBLISHED_S4096.get((mode, world, checkpointing))
+    return None
 
 
 def model_config() -> dict:
@@ -202,6 +222,11 @@ def run_ours(args) -> None:
     base = TransformerLM(**asdict(config.model), device=device, dtype=torch.float32)
     strategy = runner.Strategy(mode, base, config, device, world=world, rank=rank,
                                sync_policy="last", bucket_cap_mb=args.bucket_cap_mb)
+    if strategy.engine is None:
+        # the portable PyTorch-operator path is the oracle, not the product: never time it
+        raise SystemExit("the sm_100a fused engine did not engage for this model and mode; "
+                         "refusing to benchmark the portable path")
+    from systems_for_llms_b200.parallel.comm import reset_symmetric_peak, symmetric_memory_bytes
     accumulation = runner.validate_layout(mode, world, GLOBAL_BATCH, MICROBATCH, "last")
     sampler = torch.Generator(device="cpu").manual_seed(config.seed + 1)
     tokens_per_step = GLOBAL_BATCH * SEQ
@@ -239,6 +264,8 @@ def run_ours(args) -> None:
         device_step()
     barrier()
     check_status(device)
+    torch.cuda.reset_peak_memory_stats(device)
+    reset_symmetric_peak()
     launches_before = kernel_lib.launch_count()
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank, device_uuid(local_rank), enabled=rank == 0) as clocks:
@@ -274,14 +301,18 @@ def run_ours(args) -> None:
     # host's agree; report the longer of the two
     e2e_seconds = max(time.perf_counter() - tick, e2e_begin.elapsed_time(e2e_end) / 1e3)
     peak = torch.cuda.max_memory_allocated(device)
+    symmetric = symmetric_memory_bytes()["peak"]
+    optimizer_bytes = strategy.optimizer_state_bytes()
     if world > 1:
-        stats = torch.tensor([device_ms, e2e_seconds, float(peak)], device=device,
-                             dtype=torch.float64)
+        stats = torch.tensor([device_ms, e2e_seconds, float(peak), float(peak + symmetric),
+                              float(optimizer_bytes)], device=device, dtype=torch.float64)
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        device_ms, e2e_seconds, peak = stats.tolist()
+        device_ms, e2e_seconds, peak, true_peak, optimizer_bytes = stats.tolist()
+    else:
+        true_peak = peak + symmetric
     if rank == 0:
         value = args.steps * tokens_per_step / (device_ms / 1e3)
-        published = PUBLISHED.get((mode, world))
+        published = published_for(mode, world, args.checkpointing)
         emit({
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": device_ms / args.steps,
@@ -297,8 +328,12 @@ def run_ours(args) -> None:
             "clocks": clocks.summary(),
             "e2e": {"value": args.steps * tokens_per_step / e2e_seconds, "unit": "tokens/s",
                     "h2d_bytes_per_step": GLOBAL_BATCH * (SEQ + 1) * 8,
-                    "d2h_bytes_per_step": 3 * 4 * world, "last_loss": values["loss"]},
+                    "d2h_bytes_per_step": 4 * 4 * world, "last_loss": values["loss"]},
             "gpu_launches": launches, "peak_allocated_gib": peak / 2 ** 30,
+            # buffers mapped on peer GPUs are allocated outside PyTorch's allocator
+            "peak_with_symmetric_gib": true_peak / 2 ** 30,
+            "optimizer_state_gib_max_rank": optimizer_bytes / 2 ** 30,
+            "execution_path": "sm_100a fused engine",
             "published_reference_tokens_per_s": published,
         })
     strategy.close()
@@ -350,7 +385,7 @@ def run_reference(args) -> None:
                                  microbatch_size=MICROBATCH, warmup_steps=args.warmup,
                                  sync_policy="last", bucket_cap_mb=25.0)
     if rank == 0:
-        published = PUBLISHED.get((mode, world))
+        published = published_for(mode, world, args.checkpointing)
         emit({
             "metric": METRIC, "value": summary["tokens_per_second"], "unit": "tokens/s",
             "n_gpus": world, "steps": summary["measured_steps"], "warmup": args.warmup,
@@ -362,16 +397,20 @@ def run_reference(args) -> None:
             "config": {"model": "324M decoder (24 layers, d_model 1024, 16 heads, d_ff 2752, vocab 10000)",
                        "global_batch": GLOBAL_BATCH, "seq_len": SEQ, "microbatch": MICROBATCH,
                        "parallelism": f"{mode}-{world}gpu" if world > 1 else "single",
+                       "checkpointing": args.checkpointing,
                        "timing": "the reference's own host-timed synchronized steps, max over ranks"},
             "clocks": clocks.summary(),
             "e2e": {"value": summary["tokens_per_second"], "unit": "tokens/s",
                     "h2d_bytes_per_step": GLOBAL_BATCH * (SEQ + 1) * 8,
                     "d2h_bytes_per_step": 3 * 4 * world},
             "peak_allocated_gib": (summary["peak_cuda_allocated_bytes"] or 0) / 2 ** 30,
+            "optimizer_state_gib_max_rank":
+                (summary.get("optimizer_state_bytes_max_rank") or 0) / 2 ** 30,
         })
 
 
 def main() -> None:
+    global GLOBAL_BATCH, MICROBATCH, SEQ
     parser = argparse.ArgumentParser(description=__doc__,
                                      formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
@@ -381,9 +420,15 @@ def main() -> None:
     parser.add_argument("--mode", choices=["single", "naive", "ddp", "zero1", "fsdp", "tp"])
     parser.add_argument("--checkpointing", choices=["none", "block"], default="none")
     parser.add_argument("--bucket-cap-mb", type=float, default=25.0)
+    parser.add_argument("--seq-len", type=int, default=SEQ)
+    parser.add_argument("--global-batch", type=int, default=GLOBAL_BATCH)
+    parser.add_argument("--microbatch", type=int, default=MICROBATCH)
     args = parser.parse_args()
     if args.warmup < 3:
         parser.error("--warmup must be at least 3")
+    if min(args.seq_len, args.global_batch, args.microbatch) < 1:
+        parser.error("--seq-len, --global-batch and --microbatch must be positive")
+    GLOBAL_BATCH, MICROBATCH, SEQ = args.global_batch, args.microbatch, args.seq_len
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -83,6 +83,21 @@ def wrap_device_memory(address: int, nbytes: int, device: torch.device) -> torch
     return torch.as_tensor(_DevicePointer(address, nbytes), device=device)
 
 
+_symmetric_bytes = {"live": 0, "peak": 0}
+
+
+def symmetric_memory_bytes() -> dict:
+    """Bytes of this process's own symmetric buffers: ``live`` now and the ``peak`` since
+    the last ``reset_symmetric_peak``.  They come from ``cudaMalloc`` directly, so
+    ``torch.cuda.max_memory_allocated`` does not see them; a true peak figure of a
+    multi-GPU run is the allocator's peak plus this peak."""
+    return dict(_symmetric_bytes)
+
+
+def reset_symmetric_peak() -> None:
+    _symmetric_bytes["peak"] = _symmetric_bytes["live"]
+
+
 class SymmetricBuffer:
     """``nbytes`` of device memory on every rank of ``group``, mapped on all peers.
 
@@ -104,6 +119,8 @@ class SymmetricBuffer:
             base = c_void_p()
             _lib.check(handle.sfl_ipc_alloc(ctypes.byref(base), self.nbytes), "sfl_ipc_alloc")
             self._base = base.value
+            _symmetric_bytes["live"] += self.nbytes
+            _symmetric_bytes["peak"] = max(_symmetric_bytes["peak"], _symmetric_bytes["live"])
             self.peer_ptrs = [None] * self.world
             self.peer_ptrs[self.rank] = self._base
             self._opened = []
@@ -136,6 +153,7 @@ class SymmetricBuffer:
             self.local = None
             handle.sfl_ipc_free(self._base)
             self._base = None
+            _symmetric_bytes["live"] -= self.nbytes
 
 
 class PeerComm:

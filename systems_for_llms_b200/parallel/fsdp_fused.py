@@ -77,10 +77,16 @@ class FusedShardedTransformer(nn.Module):
         # ---- replicated norm weights ---------------------------------------------
         self.norm_params = [p for p in engine.params if p.dim() == 1]
         norm_numel = sum(p.numel() for p in self.norm_params)
-        padded = -(-norm_numel // (4 * W * 64)) * (4 * W * 64)
+        quantum = 4 * W * 64
+        padded = -(-norm_numel // quantum) * quantum
+        self.norm_numel = padded
+        # One more quantum behind the norm gradients carries this rank's squared shard
+        # norm through the same peer all-reduce, so the global gradient norm needs no
+        # collective of its own (element `padded` of the buffer).
         self.norm_flat = torch.zeros(padded, dtype=torch.float32, device=device)
-        self.norm_grad_buf = pm.SymmetricBuffer(padded * 4, device, group)
-        self.norm_grad = self.norm_grad_buf.view(torch.float32, padded)
+        self.norm_grad_buf = pm.SymmetricBuffer((padded + quantum) * 4, device, group)
+        self.norm_grad_all = self.norm_grad_buf.view(torch.float32, padded + quantum)
+        self.norm_grad = self.norm_grad_all[:padded]
         self.norm_exp_avg = torch.zeros_like(self.norm_flat)
         self.norm_exp_avg_sq = torch.zeros_like(self.norm_flat)
         self.norm_offsets = {}
@@ -280,15 +286,17 @@ class FusedShardedTransformer(nn.Module):
                       weight_decay: float) -> torch.Tensor:
         current = torch.cuda.current_stream()
         current.wait_stream(self.stream)
-        # replicated norm gradients: one small all-reduce
-        self.comm.allreduce(self.norm_grad_buf, 0, self.norm_grad.numel(), 1.0 / self.world,
+        # Squared norm of the owned gradient slices (deterministic partial sums), times the
+        # world size because the all-reduce below averages; then ONE peer all-reduce covers
+        # the replicated norm-weight gradients and that scalar.
+        local = K.grad_norm_and_coef(self.grad_shard, float("inf"))
+        self.norm_grad_all[self.norm_numel] = local[0] * local[0] * self.world
+        self.comm.allreduce(self.norm_grad_buf, 0, self.norm_grad_all.numel(), 1.0 / self.world,
                             self._next_slot())
-        shard_sq = torch.linalg.vector_norm(self.grad_shard, 2, dtype=torch.float32).square()
-        dist.all_reduce(shard_sq, group=self.group)
-        norm_sq = torch.linalg.vector_norm(self.norm_grad, 2, dtype=torch.float32).square()
-        norm = (shard_sq + norm_sq).sqrt()
-        coef = (max_norm / (norm + 1e-6)).clamp(max=1.0).reshape(1)
-        ok = torch.isfinite(norm).float().reshape(1)
+        stats = K.grad_norm_and_coef(self.norm_grad, max_norm,
+                                     extra_partials=self.norm_grad_all[self.norm_numel:
+                                                                       self.norm_numel + 1])
+        norm, coef, ok = stats[0], stats[1:2], stats[2:3]
         self.step_count += 1
         common = dict(step=self.step_count, lr=lr, beta1=betas[0], beta2=betas[1], eps=eps,
                       weight_decay=weight_decay, coef=coef, ok_flag=ok)
@@ -350,9 +358,44 @@ class ShardedStepper:
         return self.sharded.clip_and_step(max_norm, lr=group["lr"], betas=group["betas"],
                                           eps=group["eps"], weight_decay=group["weight_decay"])
 
+    def layout_sha256(self) -> str:
+        """Identity of the sharding: the flat ranges, the slice of each that this world size
+        gives a rank, and the replicated norm layout."""
+        import hashlib
+        import json
+        s = self.sharded
+        body = {"ranges": [list(r) for r in s.ranges], "chunks": list(s.chunks),
+                "world_size": s.world, "norm_numel": int(s.norm_flat.numel())}
+        return hashlib.sha256(json.dumps(body, sort_keys=True).encode()).hexdigest()
+
     def state_dict(self) -> dict:
         s = self.sharded
         return {"format_version": 1, "layout": "flat slices per range",
+                "sharding": {"rank": s.rank, "world_size": s.world,
+                             "layout_sha256": self.layout_sha256()},
                 "rank": s.rank, "world_size": s.world, "step": s.step_count,
                 "exp_avg": s.exp_avg, "exp_avg_sq": s.exp_avg_sq,
-                "norm_exp_avg": s.norm_exp_avg, "norm_exp_avg_sq": s.norm_exp_avg_sq}
+                "norm_exp_avg": s.norm_exp_avg, "norm_exp_avg_sq": s.norm_exp_avg_sq,
+                "param_groups": [{k: v for k, v in group.items() if k != "params"}
+                                 for group in self.param_groups]}
+
+    def load_state_dict(self, state_dict: dict) -> None:
+        """Restores this rank's moments and step count; refuses a shard written by another
+        rank, for another world size or another parameter layout (the guard of the
+        reference's sharded optimizer, distributed/llmdist/optim_shard.py:142-152)."""
+        meta = state_dict.get("sharding", {})
+        s = self.sharded
+        if (state_dict.get("format_version") != 1 or meta.get("rank") != s.rank
+                or meta.get("world_size") != s.world
+                or meta.get("layout_sha256") != self.layout_sha256()):
+            raise ValueError(
+                "Optimizer shard does not match this rank, world size or parameter layout")
+        for name in ("exp_avg", "exp_avg_sq", "norm_exp_avg", "norm_exp_avg_sq"):
+            target = getattr(s, name)
+            source = state_dict[name]
+            if tuple(source.shape) != tuple(target.shape):
+                raise ValueError(f"optimizer shard tensor {name} has the wrong shape")
+            target.copy_(source)
+        s.step_count = int(state_dict["step"])
+        for group, saved in zip(self.param_groups, state_dict.get("param_groups", [])):
+            group.update({k: v for k, v in saved.items() if k != "params"})

@@ -249,6 +249,7 @@ class TensorParallelComm:
         self._tile_epoch = 0
         # SFL_TP_UNFUSED=1 keeps the GEMM and its reduction as two kernels (A/B runs)
         self.fuse_gemm = os.environ.get("SFL_TP_UNFUSED", "0") != "1"
+        self.fuse_wide = os.environ.get("SFL_TP_FUSE_WIDE", "0") == "1"
 
     def _ensure(self, rows: int, cols: int) -> None:
         if rows <= self.rows and cols == self.cols:
@@ -287,8 +288,16 @@ class TensorParallelComm:
         return self.pool.view(torch.float32, rows * cols, offset).view(rows, cols)
 
     def can_fuse(self, cols: int) -> bool:
-        """The one-kernel GEMM + all-reduce needs whole 256-column tiles."""
-        return self.fuse_gemm and self.comm.world > 1 and cols % 256 == 0
+        """The one-kernel GEMM + all-reduce needs whole 256-column tiles.
+
+        It is the default for groups of two (every rank finishes every row).  For larger
+        groups the kernel switches to owned tiles, whose waits rely on every rank running
+        the same grid with all CTAs resident; that form is opt-in (``SFL_TP_FUSE_WIDE=1``)
+        and the two-kernel path (GEMM, then ``reduce_rows``) is the default there.
+        """
+        if not (self.fuse_gemm and self.comm.world > 1 and cols % 256 == 0):
+            return False
+        return self.comm.world == 2 or self.fuse_wide
 
     def _next_tile_epoch(self) -> int:
         self._tile_epoch += 1

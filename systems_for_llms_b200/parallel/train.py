@@ -449,6 +449,15 @@ def run(config: TrainConfig, output_dir, *, mode="single", global_batch_size=8,
                                  "resume unsupported"),
         }
         (output / f"rank-{rank}-metadata.json").write_text(json.dumps(metadata, indent=2) + "\n")
+        if save_final_state:
+            # The state before the first update, gathered like the final one: parity checks
+            # compare the UPDATE (final - initial), which a tolerance on raw parameters
+            # cannot resolve after a handful of small steps.
+            state = strategy.full_state()
+            if rank == 0:
+                torch.save({"model": {name: value.detach().cpu() for name, value in state.items()}},
+                           output / "initial-state.pt")
+            del state
         synchronize(device)
         if world > 1:
             dist.barrier()
@@ -523,9 +532,17 @@ def run(config: TrainConfig, output_dir, *, mode="single", global_batch_size=8,
             check_status(device)
         batch_stream_hash = hashlib.sha256("".join(
             row["batch_start_sha256"] for row in rows if row["event"] == "train").encode()).hexdigest()
+        symmetric_peak = 0
+        if cuda:
+            from .comm import symmetric_memory_bytes
+            symmetric_peak = symmetric_memory_bytes()["peak"]
         rank_result = {
             "rank": rank,
             "peak_cuda_allocated_bytes": torch.cuda.max_memory_allocated(device) if cuda else None,
+            # peer-mapped buffers are allocated outside PyTorch's allocator
+            "symmetric_buffer_bytes": symmetric_peak if cuda else None,
+            "peak_cuda_allocated_with_symmetric_bytes":
+                torch.cuda.max_memory_allocated(device) + symmetric_peak if cuda else None,
             "peak_cuda_reserved_bytes": torch.cuda.max_memory_reserved(device) if cuda else None,
             "optimizer_state_bytes": strategy.optimizer_state_bytes(),
             "local_parameter_bytes": local_parameter_bytes(),
@@ -564,6 +581,8 @@ def run(config: TrainConfig, output_dir, *, mode="single", global_batch_size=8,
             "valid_loss": last_valid_loss, "profiled": bool(profile_steps), "ranks": ranks,
             "peak_cuda_allocated_bytes": max(i["peak_cuda_allocated_bytes"] for i in ranks) if cuda else None,
             "peak_cuda_reserved_bytes": max(i["peak_cuda_reserved_bytes"] for i in ranks) if cuda else None,
+            "peak_cuda_allocated_with_symmetric_bytes":
+                max(i["peak_cuda_allocated_with_symmetric_bytes"] for i in ranks) if cuda else None,
             "optimizer_state_bytes_max_rank": max(i["optimizer_state_bytes"] for i in ranks),
             "optimizer_state_bytes_sum": sum(i["optimizer_state_bytes"] for i in ranks),
             "batch_stream_sha256": batch_stream_hash,

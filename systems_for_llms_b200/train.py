@@ -260,7 +260,18 @@ def _metadata(config, config_dict, device, model, data_identity, source, parent)
         "peak_memory_scope": "training and evaluation after model initialization",
         "workload": ("synthetic pipeline check" if config.data.kind == "synthetic"
                      else "tokenized language modeling"),
+        # which of the two code paths this configuration selects (the portable path is
+        # the numerical oracle; a run that silently fell back to it is not a
+        # measurement of the kernels)
+        "execution_path": execution_path(model, config, device),
     }
+
+
+def execution_path(model: TransformerLM, config: TrainConfig, device: torch.device) -> str:
+    if device.type != "cuda" or config.precision != "bf16":
+        return "portable PyTorch operators"
+    from .models import fused
+    return "sm_100a fused engine" if fused.eligible(model) else "portable PyTorch operators"
 
 
 def _run(config: TrainConfig, output_dir: Path, resume, stop_after, started: float) -> dict:
@@ -366,6 +377,8 @@ def _run(config: TrainConfig, output_dir: Path, resume, stop_after, started: flo
             "wall_seconds": time.perf_counter() - started, "timing_scope": TIMING_SCOPE,
             "peak_cuda_allocated_bytes": torch.cuda.max_memory_allocated(device) if cuda else None,
             "peak_cuda_reserved_bytes": torch.cuda.max_memory_reserved(device) if cuda else None,
+            "execution_path": ("sm_100a fused engine" if getattr(model, "_fused", None) is not None
+                               else "portable PyTorch operators"),
         }
         record("finish", status=summary["status"])
         (output_dir / "summary.json").write_text(
