@@ -13,6 +13,11 @@ the output directory of ``distributed_plan.run_plan`` it
   within-seed ratios for the canonical questions - DDP and TP against one GPU,
   sharded AdamW and FSDP against DDP, block checkpointing against none
   (``paired_comparisons``);
+* accounts for what the launch cost: one row per stage with the wall time of its launcher
+  pipeline, the GPUs it held and the GPU-minutes that makes (the reference bills dollars
+  per function second, distributed/analyze.py:152-169; GPU-minutes are the unit here),
+  next to the estimate recorded before the launch and the GPU-seconds the measured
+  updates actually used;
 * writes ``summary.json`` and a Markdown report with the hashes of its inputs, and
   optional PNG/SVG plots when matplotlib is installed (Agg backend).
 
@@ -167,6 +172,55 @@ def paired_comparisons(rows: list[dict]) -> list[dict]:
     return result
 
 
+def _positive(value, what: str) -> float:
+    if not common.is_finite(value, positive=True):
+        raise ValueError(f"{what} must be finite and positive")
+    return float(value)
+
+
+def cost_rows(run_dir: str | Path, cases: list[dict] | None = None) -> list[dict]:
+    """GPU-minutes per stage from the launcher's and the campaign's own records.
+
+    ``run_dir`` is the study directory a launcher pipeline wrote (``<stage>/study``); its
+    parent holds ``launch-summary.json`` and, for a campaign, the grandparent holds
+    ``campaign.json`` with one record per stage.  A stage that never reported is listed
+    with ``None`` figures rather than dropped.
+    """
+    run_dir = Path(run_dir)
+    stage_root = run_dir.parent
+    campaign_path = stage_root.parent / "campaign.json"
+    stages = []
+    if campaign_path.is_file():
+        campaign = common.read_json(campaign_path)
+        for definition, record in zip(campaign["definition"]["stages"], campaign["stages"]):
+            stages.append((definition["name"], Path(definition["output_dir"]), definition, record))
+    elif (stage_root / "launch-summary.json").is_file():
+        stages.append((None, stage_root, {}, {}))
+    rows = []
+    for name, root, definition, record in stages:
+        report_path = root / "launch-summary.json"
+        report = common.read_json(report_path) if report_path.is_file() else {}
+        estimate = report.get("estimate", definition.get("estimate", {}))
+        gpus = report.get("gpus", definition.get("options", {}).get("gpus"))
+        seconds = report.get("wall_seconds")
+        used = None
+        if seconds is not None and gpus is not None:
+            used = (_positive(seconds, "launcher wall time") * _positive(gpus, "GPU count") / 60)
+        rows.append({"stage": name or report.get("stage"),
+                     "status": report.get("status", record.get("status", "not_reported")),
+                     "wall_seconds": seconds, "allocated_gpus": gpus, "gpu_minutes_used": used,
+                     "gpu_minutes_at_timeouts": estimate.get("worst_case_gpu_minutes"),
+                     "recorded_estimate": estimate})
+    if cases is not None:
+        # the measured updates belong to the stage whose study directory was analysed
+        active = sum(row["active_gpu_seconds_measured"] for row in cases
+                     if row.get("active_gpu_seconds_measured") is not None)
+        for row, (_, root, _, _) in zip(rows, stages):
+            if root.resolve() == stage_root.resolve():
+                row["active_gpu_minutes_measured"] = active / 60
+    return rows
+
+
 def build_summary(run_dir: str | Path) -> dict:
     run_dir = Path(run_dir)
     aggregate = common.read_json(run_dir / "aggregate.json")
@@ -190,7 +244,7 @@ def build_summary(run_dir: str | Path) -> dict:
             "status": aggregate["status"], "input_sha256": inputs,
             "baseline_match_fields": list(MATCH_KEYS), "timing_note": TIMING_NOTE,
             "cost_note": COST_NOTE, "cases": rows, "policies": policy_statistics(rows),
-            "paired": paired_comparisons(rows)}
+            "paired": paired_comparisons(rows), "cost": cost_rows(run_dir, rows)}
 
 
 def _fmt(value, digits=2) -> str:
@@ -231,6 +285,16 @@ def render_report(summary: dict) -> str:
             _fmt(median("throughput_ratio"), 3), _fmt(median("allocated_memory_ratio"), 3),
             _fmt(median("optimizer_state_ratio"), 3),
             _fmt(median("validation_loss_difference"), 4)]) + " |")
+    if summary.get("cost"):
+        lines += ["", "## Cost (GPU-minutes)", "",
+                  "| stage | status | GPUs | wall s | GPU-min used | GPU-min at time limits | "
+                  "GPU-min in measured updates |", "|---|---|---|---|---|---|---|"]
+        for row in summary["cost"]:
+            lines.append("| " + " | ".join([
+                str(row["stage"]), str(row["status"]), _fmt(row["allocated_gpus"]),
+                _fmt(row["wall_seconds"], 1), _fmt(row["gpu_minutes_used"], 2),
+                _fmt(row["gpu_minutes_at_timeouts"], 1),
+                _fmt(row.get("active_gpu_minutes_measured"), 2)]) + " |")
     failed = [row for row in summary["cases"] if row["status"] != "completed"]
     if failed:
         lines += ["", "## Cases without a result", ""]
