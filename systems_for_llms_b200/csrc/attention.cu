@@ -654,7 +654,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = 0.f;
         }
-        if (q < p.N) {
+        if (q < p.N && SFL_BOUNDS_OK(q >= 0 && b >= 0 && b < p.B && h >= 0 && h < p.H, p.status)) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             uint4 v;
@@ -1174,7 +1174,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = 0.f;
         }
-        if (q < p.N) {
+        if (q < p.N && SFL_BOUNDS_OK(q >= 0 && b >= 0 && b < p.B && h >= 0 && h < p.H, p.status)) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             uint4 v;
@@ -1634,7 +1634,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
             }
             out_mul = 1.0f;
           }
-          if (own_pos < p.N) {
+          if (own_pos < p.N &&
+              SFL_BOUNDS_OK(own_pos >= 0 && b < p.B && h < p.H && c * 32 + 32 <= D, p.status)) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               uint4 v;

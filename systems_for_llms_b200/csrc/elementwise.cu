@@ -67,6 +67,7 @@ __global__ void rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __r
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
+  if (!SFL_BOUNDS_OK(row >= 0 && dim > 0, nullptr)) return;
   const float* xr = x + static_cast<long>(row) * dim;
   __nv_bfloat16* yr = y + static_cast<long>(row) * dim;
   float ss = 0.f;

@@ -864,7 +864,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        if (row < p.M) EpilogueOp<EPI>::apply(p, row, col0, v, w);
+        if (row < p.M &&
+            SFL_BOUNDS_OK(row >= 0 && col0 >= 0 && col0 < p.N && tile < num_tiles && n0 < p.N,
+                          p.status))
+          EpilogueOp<EPI>::apply(p, row, col0, v, w);
       }
       tc_fence_before();
       mbar_arrive(&bars->tmem_empty[acc]);

@@ -27,6 +27,20 @@ __device__ __forceinline__ void report_status(int* status, int code) {
   if (status != nullptr) atomicCAS(status, 0, code);
 }
 
+// Debug build (-DSFL_DEBUG_BOUNDS, built with ops/build.py defines=("SFL_DEBUG_BOUNDS",) and
+// loaded through SFL_LIBRARY): per-thread global stores whose address is computed in the
+// kernel are preceded by a predicate on the logical extents of their target (row below the
+// row count, column below the width, batch and head below theirs).  A store that fails it
+// is skipped and the status word gets kStatusBadArgument, so an indexing bug shows up as a
+// reported status instead of a silent out-of-bounds write; the optimised build compiles
+// the predicate away.  compute-sanitizer is not available everywhere these kernels run.
+#ifdef SFL_DEBUG_BOUNDS
+#define SFL_BOUNDS_OK(cond, status) \
+  ((cond) ? true : (::sfl::report_status((status), ::sfl::kStatusBadArgument), false))
+#else
+#define SFL_BOUNDS_OK(cond, status) (true)
+#endif
+
 // ------------------------------------------------------------------ misc ----
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
