@@ -370,9 +370,20 @@ extern "C" int sfl_decode_static(const void* q, const void* k, const void* v, co
                                  void* out, int B, int Hq, int Hkv, int N, int D, int splits,
                                  float scale, int tile_variant, int is_fp16, void* stream_) {
   using namespace sfl;
+  // Everything is checked before anything is queued on the stream: plain C callers are
+  // the audience of this entry point, and a null pointer would reach the kernel.
+  if (q == nullptr || k == nullptr || v == nullptr || lengths == nullptr || out == nullptr)
+    return fail_static(-2, "sfl_decode_static: q, k, v, lengths and out must not be null");
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || N <= 0 || Hq % Hkv || splits < 1 || splits > 128 ||
       (D != 64 && D != 128))
     return fail_static(-2, "sfl_decode_static: unsupported shape (see sfl_decode)");
+  {
+    const int ratio = Hq / Hkv;
+    if (ratio != 1 && ratio != 2 && ratio != 4 && ratio != 8)
+      return fail_static(-2, "sfl_decode_static: query heads per KV head must be 1, 2, 4 or 8");
+  }
+  if (!(scale > 0.0f) || !isfinite(scale))
+    return fail_static(-2, "sfl_decode_static: scale must be finite and positive");
   const long slots = static_cast<long>(B) * Hq * splits;
   if (slots > kStaticSlots || static_cast<long>(B) * Hkv > kStaticCounters) {
     char text[200];

@@ -220,3 +220,58 @@ def test_embedding_backward_is_a_deterministic_scatter_add(dev, rows, dim, vocab
     too_many = torch.zeros(K.EMBEDDING_BWD_MAX_ROWS + 1, dtype=torch.int64, device=dev)
     assert not K.embedding_bwd(torch.zeros(too_many.numel(), 8, device=dev), too_many,
                                torch.zeros(4, 8, device=dev), False)
+
+
+@pytest.mark.parametrize("d_model,heads,d_ff,ranks", [(512, 8, 1408, 4), (512, 8, 1408, 8),
+                                                      (1024, 16, 2752, 8)])
+def test_gemm_tensor_parallel_shard_shapes(dev, d_model, heads, d_ff, ranks):
+    """The products of one tensor-parallel rank: narrow outputs (two heads, or one), a
+    feed-forward slice that is only a multiple of 8 (344, 176) as output width and as
+    reduction length (TMA zero-fills the ragged last 64-deep step)."""
+    from systems_for_llms_b200.ops import gemm as G
+    M, aw, ff = 1024, d_model // ranks, d_ff // ranks
+    dk = d_model // heads
+    x = rnd(dev, M, d_model, seed=1)
+    wqkv = rnd(dev, 3 * aw, d_model, scale=0.05, seed=2)
+    wo = rnd(dev, d_model, aw, scale=0.05, seed=3)
+    w13 = rnd(dev, 2 * ff, d_model, scale=0.05, seed=4)
+    w2 = rnd(dev, d_model, ff, scale=0.05, seed=5)
+    attn = rnd(dev, M, aw, seed=6)
+    resid = torch.randn(M, d_model, device=dev)
+    T = 256
+    inv = 1.0 / (10000.0 ** (torch.arange(0, dk, 2, device=dev).float() / dk))
+    angles = torch.arange(T, device=dev).float()[:, None] * inv[None]
+    cos, sin = (f(angles).bfloat16().float().contiguous() for f in (torch.cos, torch.sin))
+    # q|k|v projection with rotary epilogue: the v columns are the plain product
+    qkv = G.linear_fwd_rope(x, wqkv, cos, sin, T, 2 * aw, dk)
+    plain = (x.float() @ wqkv.float().t())
+    assert rel(qkv[:, 2 * aw:], plain[:, 2 * aw:]) < 1e-2
+    # row-parallel products (reduction over the local width) as partial sums
+    assert rel(G.linear_fwd(attn, wo), attn.float() @ wo.float().t()) < 1e-2
+    assert rel(G.linear_fwd_resid(attn, wo, resid),
+               resid + (attn.float() @ wo.float().t()).bfloat16().float()) < 5e-3
+    g, a13 = G.swiglu_fwd(x, w13, ff)
+    a = (x.float() @ w13.float().t()).bfloat16().float()
+    want_g = torch.nn.functional.silu(a[:, :ff]) * a[:, ff:]
+    assert rel(a13, a) < 1e-2 and rel(g, want_g) < 2e-2
+    assert rel(G.linear_fwd(g, w2), g.float() @ w2.float().t()) < 1e-2
+    # backward: activation derivative, input gradients, weight gradients
+    dy = rnd(dev, M, d_model, seed=7)
+    d13 = G.swiglu_bwd(dy, w2, a13)
+    dg = (dy.float() @ w2.float()).bfloat16().float()
+    a1, a3 = a13[:, :ff].float(), a13[:, ff:].float()
+    sig = torch.sigmoid(a1)
+    want = torch.cat([dg * a3 * (sig + a1 * sig * (1 - sig)), dg * a1 * sig], dim=1)
+    assert rel(d13, want) < 2e-2
+    assert rel(G.linear_dgrad(d13, w13), d13.float() @ w13.float()) < 1e-2
+    dqkv = rnd(dev, M, 3 * aw, seed=8)
+    assert rel(G.linear_dgrad(dqkv, wqkv), dqkv.float() @ wqkv.float()) < 1e-2
+    problems, wants = [], []
+    for dy_, x_ in ((dy, g), (d13, x), (dy, attn), (dqkv, x)):
+        grad = torch.zeros(dy_.shape[1], x_.shape[1], device=dev)
+        problems.append((dy_, x_, grad, False))
+        wants.append(dy_.float().t() @ x_.float())
+    G.wgrad_grouped(problems)
+    check(dev)
+    for (_, _, grad, _), want in zip(problems, wants):
+        assert rel(grad, want) < 1e-3

@@ -77,3 +77,23 @@ def test_oversized_request_is_refused(library):
     code, _ = call_static(library, q, k, k, lengths, splits, "tile")
     assert code != 0
     assert b"capacity" in library.sfl_decode_static_error()
+
+
+def test_bad_group_ratio_and_null_pointers_are_refused_before_anything_is_queued(library):
+    """A plain C caller gets a message naming the problem instead of a faulting kernel or a
+    misleading launch failure: both are rejected before the stream sees any work."""
+    device = torch.device("cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    B, Hq, Hkv, N, D = 1, 6, 2, 64, 64                       # three query heads per KV head
+    q = torch.zeros(B, Hq, D, device=device, dtype=torch.bfloat16)
+    k = torch.zeros(B, Hkv, N, D, device=device, dtype=torch.bfloat16)
+    lengths = torch.full((B,), N, dtype=torch.int32, device=device)
+    code, _ = call_static(library, q, k, k, lengths, 2, "tile")
+    assert code == -2
+    assert b"1, 2, 4 or 8" in library.sfl_decode_static_error()
+    out = torch.empty_like(q)
+    code = library.sfl_decode_static(q.data_ptr(), None, k.data_ptr(), lengths.data_ptr(),
+                                     out.data_ptr(), B, 4, Hkv, N, D, 2, D ** -0.5, 1, 0, stream)
+    assert code == -2
+    assert b"must not be null" in library.sfl_decode_static_error()
+    torch.cuda.synchronize()
