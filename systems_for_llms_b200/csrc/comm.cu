@@ -216,6 +216,11 @@ reduce_kernel(const CommView c, long offset, long count, float scale, int slot, 
   __syncthreads();
   if (threadIdx.x < c.world)
     *partial_ptr(c.flags[threadIdx.x], slot, c.rank, blockIdx.x) = total;
+  // Entries of CTAs this launch does not have: zero on every peer, so that the norm
+  // may add up all kMaxCtas entries of a slot whatever grid its reductions ran on.
+  if (blockIdx.x == 0 && !accumulate_partial)
+    for (int i = gridDim.x + threadIdx.x; i < kMaxCtas; i += blockDim.x)
+      for (int p = 0; p < c.world; ++p) *partial_ptr(c.flags[p], slot, c.rank, i) = 0.f;
   done_barrier(c, slot, epoch, status);
 }
 
@@ -248,18 +253,32 @@ int launch_reduce(const CommView& v, long offset, long count, float scale, int s
 }
 
 // out[0] = sqrt(sum of all partials of the given slots), out[1] = clip coef, out[2] = finite.
-__global__ void comm_norm_finalize_kernel(const uint32_t* flags, const int* slots, int n_slots,
-                                          int world, int ctas, float max_norm,
-                                          const float* extra_sq, float* out) {
-  // One thread: a few thousand adds in a fixed order, identical on every rank.
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  double total = extra_sq != nullptr ? static_cast<double>(*extra_sq) : 0.0;
-  for (int s = 0; s < n_slots; ++s)
-    for (int r = 0; r < world; ++r)
-      for (int k = 0; k < ctas; ++k)
-        total += static_cast<double>(
-            *(reinterpret_cast<const float*>(flags + kFlagWords) +
-              (slots[s] * kMaxPeers + r) * kMaxCtas + k));
+// One block: thread t adds entries t, t + 256, ... of the [slot][rank][CTA] table in that
+// order, then the 256 sums are folded by a fixed tree - the same arithmetic in the same order
+// on every rank, whatever the grid size of the reductions that left the partials (unused CTA
+// entries of a slot are zero, see reduce_kernel).
+__global__ void __launch_bounds__(256)
+comm_norm_finalize_kernel(const uint32_t* flags, const int* slots, int n_slots, int world,
+                          float max_norm, const float* extra_sq, float* out) {
+  __shared__ double fold[256];
+  const float* table = reinterpret_cast<const float*>(flags + kFlagWords);
+  const int per_slot = world * kMaxCtas;
+  const long entries = static_cast<long>(n_slots) * per_slot;
+  double mine = 0.0;
+  for (long i = threadIdx.x; i < entries; i += 256) {
+    const int s = static_cast<int>(i / per_slot);
+    const int within = static_cast<int>(i - static_cast<long>(s) * per_slot);
+    const int r = within / kMaxCtas, k = within - r * kMaxCtas;
+    mine += static_cast<double>(table[(slots[s] * kMaxPeers + r) * kMaxCtas + k]);
+  }
+  fold[threadIdx.x] = mine;
+  __syncthreads();
+  for (int width = 128; width > 0; width >>= 1) {
+    if (threadIdx.x < width) fold[threadIdx.x] += fold[threadIdx.x + width];
+    __syncthreads();
+  }
+  if (threadIdx.x != 0) return;
+  const double total = fold[0] + (extra_sq != nullptr ? static_cast<double>(*extra_sq) : 0.0);
   const float norm = sqrtf(static_cast<float>(total));
   out[0] = norm;
   const float coef = max_norm / (norm + 1e-6f);
@@ -613,9 +632,9 @@ extern "C" int sfl_reduce_scatter_f32(const SflComm* comm, long offset, long cou
 extern "C" int sfl_comm_norm_finalize(const SflComm* comm, const int* slots_dev, int n_slots,
                                       int ctas, float max_norm, const float* extra_sq, float* out,
                                       void* stream) {
-  ctas = clamp_ctas(ctas);
-  comm_norm_finalize_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint32_t*>(comm->flags[comm->rank]), slots_dev, n_slots, comm->world, ctas,
+  (void)ctas;  // every CTA entry of a slot is added; unused ones are zero
+  comm_norm_finalize_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint32_t*>(comm->flags[comm->rank]), slots_dev, n_slots, comm->world,
       max_norm, extra_sq, out);
   return static_cast<int>(cudaGetLastError());
 }

@@ -201,22 +201,25 @@ class PeerComm:
 
     # ------------------------------------------------------------ launchers --
     def allreduce(self, buffer: SymmetricBuffer, offset: int, count: int, scale: float,
-                  slot: int, accumulate_partial: bool = False) -> None:
-        """In-place ``scale * sum`` over ranks of fp32 ``buffer[offset:offset+count]``."""
+                  slot: int, accumulate_partial: bool = False, ctas: int | None = None) -> None:
+        """In-place ``scale * sum`` over ranks of fp32 ``buffer[offset:offset+count]``.
+        ``ctas`` overrides the group's grid size (a reduction with nothing left to overlap
+        with may take the whole GPU); a slot must keep one grid size within a step."""
         code = _lib.lib().sfl_allreduce_f32(
             ctypes.byref(self.struct(buffer)), offset, count, scale, slot, self.next_epoch(slot),
-            int(accumulate_partial), self.ctas, self.status.data_ptr(), _lib.stream_ptr())
+            int(accumulate_partial), ctas or self.ctas, self.status.data_ptr(), _lib.stream_ptr())
         _lib.check(code, "sfl_allreduce_f32")
 
     def reduce_scatter(self, buffer: SymmetricBuffer, offset: int, count: int, scale: float,
                        out: torch.Tensor | None, slot: int,
-                       accumulate_partial: bool = False, accumulate_out: bool = False) -> None:
+                       accumulate_partial: bool = False, accumulate_out: bool = False,
+                       ctas: int | None = None) -> None:
         """Rank r keeps ``scale * sum`` of slice r (compact in ``out``); with
         ``accumulate_out`` the result is added to what ``out`` already holds."""
         flags = int(accumulate_partial) | (int(accumulate_out) << 1)
         code = _lib.lib().sfl_reduce_scatter_f32(
             ctypes.byref(self.struct(buffer)), offset, count, scale, _lib.ptr(out), slot,
-            self.next_epoch(slot), flags, self.ctas, self.status.data_ptr(),
+            self.next_epoch(slot), flags, ctas or self.ctas, self.status.data_ptr(),
             _lib.stream_ptr())
         _lib.check(code, "sfl_reduce_scatter_f32")
 

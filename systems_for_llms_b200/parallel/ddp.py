@@ -199,6 +199,12 @@ class BucketedDDP(nn.Module):
         stream = state["stream"]
         stream.wait_stream(torch.cuda.current_stream())
         scale = 1.0 / self.world
+        # Buckets that only become final with the last gradient of the backward pass have
+        # nothing left to hide behind: they take the whole GPU instead of the few CTAs that
+        # reductions overlapped with backward are limited to.  A bucket index always gets
+        # the same treatment, so each slot keeps one grid size.
+        tail = ready_from == 0 and len(state["ranges"]) <= state["slot_count"]
+        ctas = comm.update_ctas if tail else None
         with torch.cuda.stream(stream):
             for index in launch:
                 begin, end = state["ranges"][index]
@@ -208,9 +214,10 @@ class BucketedDDP(nn.Module):
                 if self.mode == "scatter":
                     offset = state["shard_offsets"][index]
                     out = state["shard"][offset:offset + self._slice_len(begin, end)]
-                    comm.reduce_scatter(grads, begin, end - begin, scale, out, slot, accumulate)
+                    comm.reduce_scatter(grads, begin, end - begin, scale, out, slot, accumulate,
+                                        ctas=ctas)
                 else:
-                    comm.allreduce(grads, begin, end - begin, scale, slot, accumulate)
+                    comm.allreduce(grads, begin, end - begin, scale, slot, accumulate, ctas=ctas)
 
     def _finish_peer(self, max_norm: float) -> torch.Tensor:
         state = self._peer
