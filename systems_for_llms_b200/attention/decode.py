@@ -5,8 +5,12 @@ Interface of the reference binding (attention_lab/cuda_decode/kernel.py:27-118):
 validates, allocates scratch and output once and returns a ``PreparedDecode``
 whose call launches on the current stream without allocating - so it can be
 captured in a CUDA graph, and ``lengths`` may be edited in place between calls;
-``decode(...)`` is the one-shot form.  The kernel (csrc/decode.cu) merges the
-splits inside the same launch.
+``decode(...)`` is the one-shot form.  The kernels merge the splits inside the same
+launch.  Three variants: ``"token"`` and ``"tile"`` are the reference's two softmax
+schedules on the CUDA cores (csrc/decode.cu); ``"mma"`` computes the scores of a GQA
+group and the weighted value sum as tcgen05 matrix products fed by TMA
+(csrc/attention.cu, ``decode_mma_kernel``) - the one that keeps up with HBM when
+several query heads share a KV head.
 """
 
 from __future__ import annotations
@@ -22,6 +26,9 @@ from ..ops import lib as _lib
 _P = c_void_p
 _lib.register_signature("sfl_decode", [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int,
                                        c_int, c_int, c_int, c_float, c_int, c_int, _P])
+_lib.register_signature("sfl_decode_mma", [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int,
+                                           c_int, c_int, c_int, c_float, c_int, _P, _P])
+VARIANTS = ("token", "tile", "mma")
 
 
 def _validate(q, k, v, lengths, splits):
@@ -65,10 +72,20 @@ class PreparedDecode:
     splits: int
     scale: float
     variant: str
+    status: torch.Tensor | None = None
 
     def __call__(self) -> torch.Tensor:
         B, Hq, D = self.q.shape
         Hkv, N = self.k.shape[1:3]
+        if self.variant == "mma":
+            code = _lib.lib().sfl_decode_mma(
+                self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(), self.lengths.data_ptr(),
+                self.partial_max.data_ptr(), self.partial_sum.data_ptr(),
+                self.partial_output.data_ptr(), self.counters.data_ptr(), self.output.data_ptr(),
+                B, Hq, Hkv, N, D, self.splits, self.scale, int(self.q.dtype == torch.float16),
+                self.status.data_ptr(), _lib.stream_ptr())
+            _lib.check(code, "sfl_decode_mma")
+            return self.output
         code = _lib.lib().sfl_decode(
             self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(), self.lengths.data_ptr(),
             self.partial_max.data_ptr(), self.partial_sum.data_ptr(),
@@ -91,8 +108,8 @@ def prepare(q, k, v, lengths=None, *, splits=1, scale=None, variant="token") -> 
     visible.  Zero-length rows yield zeros.  Concurrent use needs separate
     prepared operations because scratch and output are owned by the object.
     """
-    if variant not in ("token", "tile"):
-        raise ValueError("variant must be 'token' or 'tile'")
+    if variant not in VARIANTS:
+        raise ValueError("variant must be 'token', 'tile' or 'mma'")
     for tensor in (q, k, v):
         if not isinstance(tensor, torch.Tensor) or not tensor.is_cuda:
             raise ValueError("all tensors must be on the same CUDA device")
@@ -109,8 +126,10 @@ def prepare(q, k, v, lengths=None, *, splits=1, scale=None, variant="token") -> 
     normalizer = torch.empty_like(maximum)
     numerator = torch.empty(batch, heads, splits, dim, device=q.device, dtype=torch.float32)
     counters = torch.zeros(batch, kv_heads, device=q.device, dtype=torch.int32)
+    from ..ops.gemm import status_word
     return PreparedDecode(q, k, v, lengths, maximum, normalizer, numerator, counters,
-                          torch.empty_like(q), splits, float(scale), variant)
+                          torch.empty_like(q), splits, float(scale), variant,
+                          status_word(q.device))
 
 
 def decode(q, k, v, lengths=None, *, splits=1, scale=None, variant="token") -> torch.Tensor:

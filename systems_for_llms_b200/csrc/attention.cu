@@ -298,13 +298,23 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const float* src) 
   tmem_st_32x16(taddr + 16, b);
 }
 
+// A wait gives up after about two seconds by the global timer.  (An iteration count alone
+// is no bound: mbarrier.try_wait may suspend the thread for an implementation-defined time
+// per call, and millions of such calls have taken minutes on a barrier that never completed.)
 __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, volatile int* abort,
                                              int* status, int code) {
-  for (uint32_t spin = 0; spin < (1u << 23); ++spin) {
+  unsigned long long started = 0;
+  for (uint32_t spin = 0; spin < (1u << 26); ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if (spin > 2048) {
       __nanosleep(256);
       if (*abort) return false;
+      if ((spin & 1023) == 0) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        if (started == 0) started = now;
+        if (now - started > 2000000000ull) break;
+      }
     }
   }
   report_status(status, code);
@@ -1216,6 +1226,364 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
+// ====================================================== decode on tensor cores ====
+// Single-token attention over a KV cache with grouped queries, split over the cache.
+// The scores of one (batch, KV head) are a [query heads of the group] x [cached tokens]
+// matrix product and the output a [heads] x [tokens] x [D] one, so a split of the cache
+// is processed exactly like a query tile of the forward kernel above: K and V tiles of
+// 128 tokens stream in through TMA, S = Q K^T and O += P V run on tcgen05 with the
+// accumulators in tensor memory, P goes back into tensor memory as the A operand.  The
+// "query tile" holds the G <= 8 heads of the group, spread over the four lane quarters
+// (head g sits in row 32 (g mod 4) + g / 4) so that all four softmax warps have rows to
+// work on; its other rows are zero and their results are never read.  Scalar-FMA decode
+// needs about 125 warp instructions per cached token for eight heads at D = 128 and is
+// bound by the issue rate at a quarter of the memory bandwidth; here the arithmetic per
+// token is a handful of instructions and the kernel is bound by the K/V stream.
+//
+// A CTA handles one (batch, KV head, split) and leaves (m, l, u) in the log-2 domain for
+// the merge, which the last CTA of a (batch, KV head) to finish performs (decode.cu has the
+// same protocol).  Partitioning follows the reference (attention_lab/cuda_decode/
+// decode.cu:50-52): split s covers tokens [s chunk, min(length, (s + 1) chunk)) with
+// chunk = ceil(capacity / splits); empty partitions contribute (-inf, 0, 0).
+constexpr int kDecThreads = 192;  // TMA warp, MMA warp, four softmax warps
+
+template <int D>
+struct DecSmem {
+  static constexpr int kTileBytes = kTile * D * 2;
+  static constexpr int kStages = 2;
+  static constexpr int kBytes = kTileBytes * (1 + 2 * kStages) + 1024 + 1024;
+};
+
+struct DecBarriers {
+  uint64_t q_ready;  // 128 arrivals: the query tile is written
+  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+  uint64_t s_full, s_free, p_ready, pv_done;
+  uint32_t tmem_base;
+  int abort;
+  int is_last;
+};
+
+struct DecParams {
+  const void* q;       // [B, Hq, D]
+  const int* lengths;  // [B]
+  float* part_m;       // [B, Hq, S]  (log2 domain)
+  float* part_l;       // [B, Hq, S]
+  float* part_u;       // [B, Hq, S, D]
+  int* counters;       // [B, Hkv], zero between launches
+  void* out;           // [B, Hq, D]
+  int B, Hq, Hkv, N, splits, G;
+  float scale;
+  int* status;
+};
+
+__device__ __forceinline__ float dec_merge_exp2(float x) { return fast_exp2(x); }
+
+template <int D, bool FP16>
+__global__ void __launch_bounds__(kDecThreads, D == 64 ? 1 : 1)
+decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                  const DecParams p) {
+  using L = DecSmem<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + L::kTileBytes;
+  uint8_t* sV = sK + L::kStages * L::kTileBytes;
+  DecBarriers* bars = reinterpret_cast<DecBarriers*>(sV + L::kStages * L::kTileBytes);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  int len = p.lengths[b];
+  len = len < 0 ? 0 : (len > p.N ? p.N : len);
+  const int chunk = (p.N + p.splits - 1) / p.splits;
+  const int begin = split * chunk;
+  const int end = min(len, begin + chunk);
+  const int n_tiles = end > begin ? (end - begin + kTile - 1) / kTile : 0;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->q_ready, 128);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->k_full[s], 1);
+      mbar_init(&bars->k_empty[s], 1);
+      mbar_init(&bars->v_full[s], 1);
+      mbar_init(&bars->v_empty[s], 1);
+    }
+    mbar_init(&bars->s_full, 1);
+    mbar_init(&bars->s_free, 128);
+    mbar_init(&bars->p_ready, 128);
+    mbar_init(&bars->pv_done, 1);
+    bars->abort = 0;
+    mbar_fence_init();
+    prefetch_tensormap(&tmK);
+    prefetch_tensormap(&tmV);
+  }
+  // 192 + D columns are used; with D = 64 two CTAs can share an SM's tensor memory
+  constexpr uint32_t kTmemCols = D == 64 ? 256 : 512;
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  volatile int* abort = &bars->abort;
+  // tensor memory: scores [0,128), P as 16-bit pairs [128,192), output [192, 192 + D)
+  const uint32_t tS = tmem, tP = tmem + 128, tO = tmem + 192;
+
+  if (warp == 0) {
+    // ---------------------------------------------------- TMA producer ----
+    if (lane == 0) {
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = ((j >> 1) & 1) ^ 1;
+        const int row0 = begin + j * kTile;
+        if (!bounded_wait(&bars->k_empty[s], ph, abort, p.status, kStatusTimeoutEmpty)) break;
+        mbar_expect_tx(&bars->k_full[s], L::kTileBytes);
+        load_rows<D>(sK + s * L::kTileBytes, &tmK, &bars->k_full[s], row0, kvh, b);
+        if (!bounded_wait(&bars->v_empty[s], ph, abort, p.status, kStatusTimeoutEmpty)) break;
+        mbar_expect_tx(&bars->v_full[s], L::kTileBytes);
+        load_rows<D>(sV + s * L::kTileBytes, &tmV, &bars->v_full[s], row0, kvh, b);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------ MMA issuer ----
+    if (n_tiles > 0) {
+      constexpr uint32_t idesc_qk = idesc_16bit(FP16, kTile, kTile, false, false);
+      constexpr uint32_t idesc_pv = idesc_16bit(FP16, kTile, D, false, true);
+      const uint64_t q_desc0 = desc_kmajor(smem_u32(sQ), kTile, 0);
+      const uint64_t k_desc0 = desc_kmajor(smem_u32(sK), kTile, 0);
+      const uint64_t v_desc0 = desc_mnmajor(smem_u32(sV), 0);
+      auto issue_qk = [&](int j) -> bool {  // scores of tile j
+        const int s = j & 1;
+        if (j > 0 &&
+            !bounded_wait(&bars->s_free, (j - 1) & 1, abort, p.status, kStatusTimeoutTmemEmpty))
+          return false;
+        if (!bounded_wait(&bars->k_full[s], (j >> 1) & 1, abort, p.status, kStatusTimeoutFull))
+          return false;
+        tc_fence_after();
+        const uint64_t kd = umma_desc_advance(k_desc0, s * L::kTileBytes);
+        if (elect_one()) {
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t off = (k >> 2) * (kTile * 128) + (k & 3) * 32;
+            umma_bf16_ss(tS, umma_desc_advance(q_desc0, off), umma_desc_advance(kd, off), idesc_qk,
+                         k != 0);
+          }
+          umma_commit(&bars->s_full);
+        }
+        __syncwarp();
+        return true;
+      };
+      bool ok = bounded_wait(&bars->q_ready, 0, abort, p.status, kStatusTimeoutFull);
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) {
+          ok = issue_qk(j + 1);
+          if (!ok) break;
+        }
+        const int s = j & 1;
+        if (!bounded_wait(&bars->p_ready, j & 1, abort, p.status, kStatusTimeoutTmemFull) ||
+            !bounded_wait(&bars->v_full[s], (j >> 1) & 1, abort, p.status, kStatusTimeoutFull)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint64_t vd = umma_desc_advance(v_desc0, s * L::kTileBytes);
+        if (elect_one()) {
+#pragma unroll
+          for (int k = 0; k < kTile / 16; ++k)
+            umma_bf16_ts(tO, tP + k * 8, umma_desc_advance(vd, k * 2048), idesc_pv, (j | k) != 0);
+          umma_commit(&bars->pv_done);
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    // ------------------------------------------------ softmax + partials ----
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    // head of the group held by this row, or -1 for a padding row
+    const int g = lane < 2 && (lane * 4 + quarter) < p.G ? lane * 4 + quarter : -1;
+    const bool leader = quarter == 0 && lane == 0;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const float scale_log2 = p.scale * kLog2e;
+    const long head = static_cast<long>(b) * p.Hq + static_cast<long>(kvh) * p.G + (g < 0 ? 0 : g);
+    // The query tile: this thread's row in the K-major swizzled layout (zero when padding).
+    {
+      const uint8_t* qrow = static_cast<const uint8_t*>(p.q) + head * D * 2;
+#pragma unroll
+      for (int half = 0; half < D / 64; ++half) {
+        uint8_t* base = sQ + half * (kTile * 128) + row * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 v = g >= 0 ? *reinterpret_cast<const uint4*>(qrow + half * 128 + c * 16)
+                                 : make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(base + ((c ^ (row & 7)) << 4)) = v;
+        }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(&bars->q_ready);
+    }
+    float m_used = -INFINITY;
+    float l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      if (!bounded_wait(&bars->s_full, j & 1, abort, p.status, kStatusTimeoutTmemFull)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      if (leader) mbar_arrive(&bars->k_empty[j & 1]);
+      float x[kTile];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32f(tS + lane_base + c * 32, x + c * 32);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&bars->s_free);
+      const int valid = end - (begin + j * kTile);  // tokens of this tile inside the partition
+      if (valid < kTile) {
+#pragma unroll
+        for (int c = 0; c < kTile; ++c) x[c] = c < valid ? x[c] : -INFINITY;
+      }
+      float mx8[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) mx8[c] = fmaxf(x[2 * c], x[2 * c + 1]);
+#pragma unroll
+      for (int c = 16; c < kTile; c += 2)
+        mx8[(c >> 1) & 7] = fmax3(mx8[(c >> 1) & 7], x[c], x[c + 1]);
+      float mx = fmax3(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(mx8[3], mx8[4], mx8[5]),
+                       fmaxf(mx8[6], mx8[7]));
+      mx *= scale_log2;
+      if (j > 0) {
+        if (!bounded_wait(&bars->pv_done, (j - 1) & 1, abort, p.status, kStatusTimeoutTmemFull)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (leader) mbar_arrive(&bars->v_empty[(j - 1) & 1]);
+      }
+      const bool grow = mx > m_used + 8.0f;
+      if (__any_sync(0xffffffffu, grow)) {
+        if (j > 0) {
+          const float alpha = grow ? fast_exp2(m_used - mx) : 1.0f;
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            float o[32];
+            tmem_ld_32x32f(tO + lane_base + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] *= alpha;
+            tmem_st_32x32(tO + lane_base + c * 32, o);
+          }
+          l *= alpha;
+        }
+        if (grow) m_used = mx;
+      }
+      const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = fast_exp2(fmaf(x[c * 32 + i], scale_log2, neg_m));
+          const float p1 = fast_exp2(fmaf(x[c * 32 + i + 1], scale_log2, neg_m));
+          sum4[(i >> 1) & 3] += p0 + p1;
+          packed[i >> 1] = pack2<FP16>(p0, p1);
+        }
+        tmem_st_32x16(tP + lane_base + c * 16, packed);
+      }
+      tmem_st_wait();
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      tc_fence_before();
+      mbar_arrive(&bars->p_ready);
+    }
+    if (ok && n_tiles > 0)
+      ok = bounded_wait(&bars->pv_done, (n_tiles - 1) & 1, abort, p.status, kStatusTimeoutTmemFull);
+    if (ok) {
+      // tcgen05.ld is a warp-wide instruction: every lane loads its row, only the lanes
+      // that hold a head store it
+      tc_fence_after();
+      const long slot = head * p.splits + split;
+      const bool direct = p.splits == 1;
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        float o[32];
+        if (n_tiles > 0) {
+          tmem_ld_32x32f(tO + lane_base + c * 32, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0.f;
+        }
+        if (g < 0) continue;
+        if (direct) {
+          uint8_t* orow = static_cast<uint8_t*>(p.out) + head * D * 2;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 v;
+            v.x = pack2<FP16>(o[8 * i + 0] * inv, o[8 * i + 1] * inv);
+            v.y = pack2<FP16>(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
+            v.z = pack2<FP16>(o[8 * i + 4] * inv, o[8 * i + 5] * inv);
+            v.w = pack2<FP16>(o[8 * i + 6] * inv, o[8 * i + 7] * inv);
+            *reinterpret_cast<uint4*>(orow + (c * 32 + i * 8) * 2) = v;
+          }
+        } else {
+          float* urow = p.part_u + slot * D + c * 32;
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<float4*>(urow + 4 * i) =
+                make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+        }
+      }
+      if (!direct && g >= 0) {
+        p.part_m[slot] = l > 0.f ? m_used : -INFINITY;
+        p.part_l[slot] = l;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+  if (p.splits == 1) return;
+
+  // ---- the last CTA of this (batch, kv head) merges the splits ------------------
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int ticket = atomicAdd(&p.counters[b * p.Hkv + kvh], 1);
+    bars->is_last = ticket == p.splits - 1;
+    if (bars->is_last) p.counters[b * p.Hkv + kvh] = 0;  // ready for the next launch
+  }
+  __syncthreads();
+  if (!bars->is_last) return;
+  __threadfence();
+  const long head0 = static_cast<long>(b) * p.Hq + static_cast<long>(kvh) * p.G;
+  for (int idx = threadIdx.x; idx < p.G * D; idx += blockDim.x) {
+    const int gg = idx / D, d = idx % D;
+    const long base = (head0 + gg) * p.splits;
+    float mm = -INFINITY;
+    for (int s = 0; s < p.splits; ++s) mm = fmaxf(mm, __ldcg(p.part_m + base + s));
+    float ll = 0.f, uu = 0.f;
+    for (int s = 0; s < p.splits; ++s) {
+      const float ms = __ldcg(p.part_m + base + s);
+      const float a = (ms == -INFINITY || mm == -INFINITY) ? 0.f : dec_merge_exp2(ms - mm);
+      ll += __ldcg(p.part_l + base + s) * a;
+      uu += __ldcg(p.part_u + (base + s) * D + d) * a;
+    }
+    const float r = ll > 0.f ? uu / ll : 0.f;
+    if constexpr (FP16)
+      static_cast<__half*>(p.out)[(head0 + gg) * D + d] = __float2half_rn(r);
+    else
+      static_cast<__nv_bfloat16*>(p.out)[(head0 + gg) * D + d] = __float2bfloat16_rn(r);
+  }
+}
+
 // ============================================================= backward ====
 // Shared layout of the two backward kernels: an "owned" pair of resident tiles,
 // a ring of streamed tile pairs, and two [128 x 128] tiles written by the compute
@@ -1882,6 +2250,51 @@ extern "C" int sfl_attn_stamps_read(unsigned long long* out64) {
   (void)out64;
   return -1;
 #endif
+}
+
+// Tensor-core split-KV decode (see decode_mma_kernel).  Same contract as sfl_decode:
+// q [B, Hq, D], k / v [B, Hkv, N, D] contiguous, lengths [B], scratch for splits > 1,
+// counters zero between launches; Hq / Hkv in {1, 2, 4, 8}; D in {64, 128}.
+extern "C" int sfl_decode_mma(const void* q, const void* k, const void* v, const int* lengths,
+                              float* part_m, float* part_l, float* part_u, int* counters,
+                              void* out, int B, int Hq, int Hkv, int N, int D, int splits,
+                              float scale, int is_fp16, int* status, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (q == nullptr || k == nullptr || v == nullptr || lengths == nullptr || out == nullptr)
+    return -2;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || N <= 0 || Hq % Hkv || splits < 1 || splits > 128 ||
+      (D != 64 && D != 128))
+    return -2;
+  const int G = Hq / Hkv;
+  if (G != 1 && G != 2 && G != 4 && G != 8) return -2;
+  if (splits > 1 && (part_m == nullptr || part_l == nullptr || part_u == nullptr ||
+                     counters == nullptr))
+    return -2;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out) |
+       reinterpret_cast<uintptr_t>(part_u)) & 15)
+    return -2;
+  SflAttnTensor kt{const_cast<void*>(k), static_cast<long>(Hkv) * N * D, static_cast<long>(N) * D, D};
+  SflAttnTensor vt{const_cast<void*>(v), static_cast<long>(Hkv) * N * D, static_cast<long>(N) * D, D};
+  if (!strides_ok(kt) || !strides_ok(vt)) return -2;
+  CUtensorMap tk, tv;
+  if (make_map(&tk, k, kt, B, Hkv, N, D) || make_map(&tv, v, vt, B, Hkv, N, D)) return -3;
+  DecParams p{};
+  p.q = q; p.lengths = lengths; p.part_m = part_m; p.part_l = part_l; p.part_u = part_u;
+  p.counters = counters; p.out = out;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.N = N; p.splits = splits; p.G = G;
+  p.scale = scale; p.status = status;
+  dim3 grid(B, Hkv, splits);
+#define SFL_DEC(D_, F_)                                                                  \
+  {                                                                                      \
+    auto kern = decode_mma_kernel<D_, F_>;                                               \
+    int rc = set_smem(kern, DecSmem<D_>::kBytes);                                        \
+    if (rc) return rc;                                                                   \
+    kern<<<grid, kDecThreads, DecSmem<D_>::kBytes, stream>>>(tk, tv, p);                 \
+  }
+  if (D == 64) { if (is_fp16) SFL_DEC(64, true) else SFL_DEC(64, false) }
+  else { if (is_fp16) SFL_DEC(128, true) else SFL_DEC(128, false) }
+#undef SFL_DEC
+  return static_cast<int>(cudaGetLastError());
 }
 
 extern "C" int sfl_rope_bwd(void* x_bf16, long ld, const float* cos, const float* sin, long rows,

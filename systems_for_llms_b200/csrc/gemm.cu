@@ -138,12 +138,21 @@ struct __align__(8) GemmBarriers {
   int abort;
 };
 
+// Gives up after about two seconds by the global timer (an iteration count alone is no bound:
+// mbarrier.try_wait may suspend the thread for an implementation-defined time per call).
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort) {
-  for (uint32_t spin = 0; spin < (1u << 23); ++spin) {
+  unsigned long long started = 0;
+  for (uint32_t spin = 0; spin < (1u << 26); ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if (spin > 2048) {
       __nanosleep(256);
       if (*abort) return false;
+      if ((spin & 1023) == 0) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        if (started == 0) started = now;
+        if (now - started > 2000000000ull) return false;
+      }
     }
   }
   return false;

@@ -109,12 +109,21 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait.  Roughly two seconds of polling before it gives up; a healthy
-// pipeline stage completes in microseconds.
+// Bounded wait: gives up after about two seconds by the global timer; a healthy pipeline
+// stage completes in microseconds.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t spin = 0; spin < (1u << 24); ++spin) {
+  unsigned long long started = 0;
+  for (uint32_t spin = 0; spin < (1u << 26); ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (spin > 4096) __nanosleep(128);
+    if (spin > 4096) {
+      __nanosleep(128);
+      if ((spin & 1023) == 0) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        if (started == 0) started = now;
+        if (now - started > 2000000000ull) return false;
+      }
+    }
   }
   return false;
 }

@@ -54,7 +54,7 @@ def test_decode_matrix(dev, dtype, D, groups):
     for lengths in ([1, 31, 32], [33, 127, 513], [0, 520, 64]):
         lens = torch.tensor(lengths, dtype=torch.int32, device=dev)
         want = reference(q, k, v, lengths, D ** -0.5)
-        for splits, variant in itertools.product([1, 3, 8], ["token", "tile"]):
+        for splits, variant in itertools.product([1, 3, 8], ["token", "tile", "mma"]):
             got = decode(q, k, v, lens, splits=splits, variant=variant)
             torch.testing.assert_close(got.float(), want, atol=tol, rtol=tol,
                                        msg=f"{lengths} {splits} {variant}")
@@ -66,24 +66,26 @@ def test_many_splits_custom_scale_and_stream(dev):
     k = torch.randn(2, 4, 4096, 128, device=dev).bfloat16()
     v = torch.randn(2, 4, 4096, 128, device=dev).bfloat16()
     lens = torch.tensor([4096, 1000], dtype=torch.int32, device=dev)
-    op = prepare(q, k, v, lens, splits=128, scale=0.05, variant="tile")
-    assert op.scratch_bytes == 2 * 32 * 128 * 4 * 2 + 2 * 32 * 128 * 128 * 4
-    stream = torch.cuda.Stream()
-    stream.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(stream):
-        got = op().clone()
-    stream.synchronize()
-    torch.testing.assert_close(got.float(), reference(q, k, v, lens.tolist(), 0.05), atol=0.02,
-                               rtol=0.02)
+    for variant in ("tile", "mma"):
+        op = prepare(q, k, v, lens, splits=128, scale=0.05, variant=variant)
+        assert op.scratch_bytes == 2 * 32 * 128 * 4 * 2 + 2 * 32 * 128 * 128 * 4
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            got = op().clone()
+        stream.synchronize()
+        torch.testing.assert_close(got.float(), reference(q, k, v, lens.tolist(), 0.05),
+                                   atol=0.02, rtol=0.02, msg=variant)
 
 
-def test_cuda_graph_replay_after_length_change(dev):
+@pytest.mark.parametrize("variant", ["tile", "mma"])
+def test_cuda_graph_replay_after_length_change(dev, variant):
     from systems_for_llms_b200.attention.decode import prepare
     q = torch.randn(1, 8, 64, device=dev).half()
     k = torch.randn(1, 2, 2048, 64, device=dev).half()
     v = torch.randn(1, 2, 2048, 64, device=dev).half()
     lens = torch.tensor([2048], dtype=torch.int32, device=dev)
-    op = prepare(q, k, v, lens, splits=16, variant="tile")
+    op = prepare(q, k, v, lens, splits=16, variant=variant)
     op()
     torch.cuda.synchronize()
     graph = torch.cuda.CUDAGraph()
