@@ -163,7 +163,8 @@ def run_case(*, batch: int = 1, heads: int = 8, length: int = 1024, dim: int = 6
              block_q: int = 128, block_k: int = 128, use_full_blocks: bool = True, seed: int = 0,
              backward: bool = False, repeats: int = 20, inner_repeats: int = 10,
              warmup: int = 3, time_baselines: bool = True, include_flex: bool = False,
-             flex_contiguous: bool = False, device: str = "cuda") -> dict:
+             flex_contiguous: bool = False, device: str = "cuda",
+             pipeline: str | None = None) -> dict:
     torch_dtype = DTYPES[dtype]
     generator = torch.Generator().manual_seed(seed)
     q, k, v = (torch.randn(batch, heads, length, dim, generator=generator).to(torch_dtype)
@@ -176,7 +177,8 @@ def run_case(*, batch: int = 1, heads: int = 8, length: int = 1024, dim: int = 6
     torch.cuda.synchronize()
     first_call = time.perf_counter()
     out = flash.attention(q, k, v, schedule, spec, document_ids=document_ids,
-                          implementation=implementation, use_full_blocks=use_full_blocks)
+                          implementation=implementation, use_full_blocks=use_full_blocks,
+                          pipeline=pipeline)
     torch.cuda.synchronize()
     first_call_ms = (time.perf_counter() - first_call) * 1000
     want = reference_attention(q, k, v, mask)
@@ -189,7 +191,8 @@ def run_case(*, batch: int = 1, heads: int = 8, length: int = 1024, dim: int = 6
               "spec": {"causal": spec.causal, "window_left": spec.window_left,
                        "window_right": spec.window_right, "same_document": spec.same_document},
               "implementation": implementation, "block_q": block_q, "block_k": block_k,
-              "use_full_blocks": use_full_blocks, "seed": seed, "correct": correct,
+              "use_full_blocks": use_full_blocks, "pipeline": pipeline or "default", "seed": seed,
+              "correct": correct,
               "max_abs_error": error, "mask_density": fraction, "first_call_ms": first_call_ms,
               "status": "passed" if correct else "failed_correctness"}
     if not correct:
@@ -199,7 +202,7 @@ def run_case(*, batch: int = 1, heads: int = 8, length: int = 1024, dim: int = 6
     output = torch.empty_like(q)
     lse = torch.empty(batch, heads, length, dtype=torch.float32, device=device)
     scale = dim ** -0.5
-    timing = time_cuda(lambda: flash.flash_fwd(q, k, v, output, lse, prepared, scale),
+    timing = time_cuda(lambda: flash.flash_fwd(q, k, v, output, lse, prepared, scale, pipeline),
                        repeats=repeats, inner_repeats=inner_repeats, warmup=warmup)
     flops = attention_flops(batch, heads, length, dim, fraction)
     result.update(latency_ms=timing["median_ms"], timing=timing,

@@ -24,7 +24,7 @@ import math
 import platform
 import random
 import time
-from dataclasses import asdict
+from dataclasses import asdict, replace
 from datetime import datetime, timezone
 from pathlib import Path
 
@@ -45,8 +45,10 @@ def build_block_plan(winners: dict | None = None, *, seed: int = 211) -> dict:
                 family = "tune-causal" if pattern == "causal" else "tune-window128"
                 winner = winners.get(family)
                 config = KernelConfig(**winner["config"]) if winner else DEFAULT
-                if config not in default_configs():
+                if config not in default_configs(64) + default_configs(128):
                     raise ValueError("selected config must belong to the declared tuning space")
+                if dim == 128:         # one forward pipeline exists at this head dimension
+                    config = replace(config, pipeline="one_stream")
                 spec = MaskSpec(causal=True, window_left=127 if pattern == "window" else None)
                 cases.append({
                     "case_id": f"block-n{length}-d{dim}-{pattern}-s{seed}", "length": length,

@@ -41,6 +41,10 @@ class AttnMask(Structure):
 _A = POINTER(AttnTensor)
 _lib.register_signature("sfl_attn_fwd", [_A, _A, _A, _A, c_void_p, c_int, c_int, c_int, c_int,
                                          c_float, POINTER(AttnMask), c_int, c_void_p, c_void_p])
+_lib.register_signature("sfl_attn_fwd_pipeline",
+                        [_A, _A, _A, _A, c_void_p, c_int, c_int, c_int, c_int, c_float,
+                         POINTER(AttnMask), c_int, c_int, c_void_p, c_void_p])
+PIPELINES = {None: 0, "default": 0, "one_stream": 1, "two_stream": 2, "two_stream_smem_p": 3}
 _lib.register_signature("sfl_attn_bwd", [_A, _A, _A, _A, _A, c_void_p, c_void_p, _A, _A, _A,
                                          c_int, c_int, c_int, c_int, c_float, POINTER(AttnMask),
                                          c_int, c_void_p, c_void_p, c_void_p, c_void_p])
@@ -163,15 +167,23 @@ def _view(t: torch.Tensor) -> AttnTensor:
     return AttnTensor(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
 
 
-def flash_fwd(q, k, v, out, lse, mask: DeviceMask, scale: float) -> None:
-    """Launch the forward kernel on [B, H, N, D] views (strided views allowed)."""
+def flash_fwd(q, k, v, out, lse, mask: DeviceMask, scale: float, pipeline: str | None = None) -> None:
+    """Launch the forward kernel on [B, H, N, D] views (strided views allowed).
+
+    ``pipeline`` picks the kernel variant (``PIPELINES``): ``two_stream`` (two independent
+    work streams per CTA, P in tensor memory; the default at head dimension 64),
+    ``two_stream_smem_p`` (P through shared memory) or ``one_stream`` (one query tile per
+    CTA; what head dimension 128 always runs)."""
+    if pipeline not in PIPELINES:
+        raise ValueError(f"pipeline must be one of {sorted(k for k in PIPELINES if k)}")
     B, H, N, D = q.shape
     fp16 = int(q.dtype == torch.float16)
     status = status_word(q.device)
-    code = _lib.lib().sfl_attn_fwd(
+    code = _lib.lib().sfl_attn_fwd_pipeline(
         ctypes.byref(_view(q)), ctypes.byref(_view(k)), ctypes.byref(_view(v)),
         ctypes.byref(_view(out)), None if lse is None else lse.data_ptr(), B, H, N, D,
-        float(scale), ctypes.byref(mask.struct), fp16, status.data_ptr(), _lib.stream_ptr())
+        float(scale), ctypes.byref(mask.struct), fp16, PIPELINES[pipeline], status.data_ptr(),
+        _lib.stream_ptr())
     _lib.check(code, "sfl_attn_fwd")
 
 
@@ -273,13 +285,14 @@ def _doc_list(document_ids):
 
 def attention(q, k, v, schedule, spec, *, document_ids=None, implementation="csr",
               use_full_blocks=True, return_lse=False, scale=None, num_warps=4, num_stages=2,
-              launch_metadata=None):
+              launch_metadata=None, pipeline=None):
     """Forward-only block-sparse attention.
 
-    ``num_warps`` / ``num_stages`` are accepted for signature compatibility with
-    the reference's tunable Triton kernel and validated, but the sm_100a kernel
-    has one fixed warp-specialised configuration.  ``launch_metadata`` (a dict)
-    receives the static resource figures of that configuration.
+    ``pipeline`` selects the forward kernel variant (see ``flash_fwd``); it is the knob the
+    configuration search turns on this hardware.  ``num_warps`` / ``num_stages`` are
+    accepted for signature compatibility with the reference's tunable Triton kernel and
+    validated, but the sm_100a kernels have fixed warp-specialised layouts.
+    ``launch_metadata`` (a dict) receives the static resource figures of the variant used.
     """
     _check_inputs(q, k, v, allow_grad=False)
     if num_warps not in (1, 2, 4, 8) or num_stages not in (1, 2, 3, 4):
@@ -288,11 +301,13 @@ def attention(q, k, v, schedule, spec, *, document_ids=None, implementation="csr
     B, H, N, D = q.shape
     out = torch.empty_like(q)
     lse = torch.empty(B, H, N, dtype=torch.float32, device=q.device) if return_lse else None
-    flash_fwd(q, k, v, out, lse, mask, D ** -0.5 if scale is None else scale)
+    flash_fwd(q, k, v, out, lse, mask, D ** -0.5 if scale is None else scale, pipeline)
     if launch_metadata is not None:
+        two = D == 64 and pipeline != "one_stream"
         launch_metadata.update({
-            "kernel_name": f"attn_fwd_kernel<{D}>", "threads": 192, "tile": KERNEL_TILE,
-            "tensor_memory_columns": 512,
+            "kernel_name": f"attn_fwd2_kernel<{D}>" if two else f"attn_fwd_kernel<{D}>",
+            "pipeline": ("one_stream" if not two else pipeline or "two_stream"),
+            "threads": 384 if two else 192, "tile": KERNEL_TILE, "tensor_memory_columns": 512,
             "source": "static configuration of the sm_100a kernel; not a profiler measurement",
         })
     return (out, lse) if return_lse else out

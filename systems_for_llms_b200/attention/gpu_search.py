@@ -22,7 +22,7 @@ from . import benchmark
 from .masks import MaskSpec
 from .search import CandidateResult, default_configs, search
 
-_CONFIG_FIELDS = ("block_q", "block_k", "implementation", "use_full_blocks")
+_CONFIG_FIELDS = ("block_q", "block_k", "implementation", "use_full_blocks", "pipeline")
 
 
 def _as_result(measurement: dict) -> CandidateResult:
@@ -42,10 +42,10 @@ def _measure(case: dict, config) -> tuple[dict, float]:
     return measurement, (time.perf_counter() - begin) * 1000
 
 
-def run_experiment(*, budget: int = 12, method: str = "evolution", search_seed: int = 0,
+def run_experiment(*, budget: int = 12, method: str = "descent", search_seed: int = 0,
                    **case) -> dict:
     """``case`` holds the arguments of ``benchmark.run_case`` that are not searched."""
-    candidates = default_configs()
+    candidates = default_configs(case.get("dim", 64))
     if type(budget) is not int or not 1 <= budget <= len(candidates):
         raise ValueError(f"budget must be between 1 and {len(candidates)}")
     if set(_CONFIG_FIELDS) & case.keys():
@@ -90,7 +90,7 @@ def spec_for(mask: str, window_left: int, window_right: int) -> MaskSpec:
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__,
                                      formatter_class=argparse.RawDescriptionHelpFormatter)
-    parser.add_argument("--method", choices=["evolution", "random"], default="evolution")
+    parser.add_argument("--method", choices=["descent", "random"], default="descent")
     parser.add_argument("--budget", type=int, default=12)
     parser.add_argument("--search-seed", type=int, default=0)
     parser.add_argument("--input-seed", type=int, default=0)

@@ -75,10 +75,14 @@ def _workload(name, length, dim, pattern, *, dtype="bfloat16", heads=8, window=1
             "document_ids": packed_documents(length) if spec.same_document else None}
 
 
-def _case(workload, seed, variant, block=(128, 128), *, flex=False, selection=None) -> dict:
+def _case(workload, seed, variant, block=(128, 128), *, flex=False, selection=None,
+          pipeline=None) -> dict:
     implementation, full = VARIANTS[variant]
-    config = asdict(KernelConfig(block[0], block[1], implementation, full))
+    pipeline = pipeline or ("two_stream" if workload["dim"] == 64 else "one_stream")
+    config = asdict(KernelConfig(block[0], block[1], implementation, full, pipeline))
     tag = f"{block[0]}x{block[1]}"
+    if pipeline != ("two_stream" if workload["dim"] == 64 else "one_stream"):
+        tag += "-" + pipeline.replace("_", "")
     return {**workload, "case_id": f"{workload['workload_id']}-s{seed}-{variant}-{tag}",
             "seed": seed, "variant": variant, "config": config, "include_flex": flex,
             "selection": selection}
@@ -87,13 +91,16 @@ def _case(workload, seed, variant, block=(128, 128), *, flex=False, selection=No
 def _config_case(workload, seed, config: KernelConfig, *, flex=False, selection=None) -> dict:
     variant = next(name for name, pair in VARIANTS.items()
                    if pair == (config.implementation, config.use_full_blocks))
+    # head dimension 128 has one forward pipeline whatever a transferred configuration says
+    pipeline = "one_stream" if workload["dim"] == 128 else config.pipeline
     return _case(workload, seed, variant, (config.block_q, config.block_k), flex=flex,
-                 selection=selection)
+                 selection=selection, pipeline=pipeline)
 
 
-def _family_configs(pattern: str) -> list[KernelConfig]:
-    """Document masks have no interval form, so their space is the CSR half."""
-    return [c for c in default_configs() if pattern != "document" or c.implementation == "csr"]
+def _family_configs(pattern: str, dim: int = 64) -> list[KernelConfig]:
+    """The space of one workload: the forward pipelines its head dimension has, and for
+    document masks (which have no interval form) only the CSR configurations."""
+    return [c for c in default_configs(dim) if pattern != "document" or c.implementation == "csr"]
 
 
 def build_plan(stage: str, *, winners: dict | None = None) -> dict:
@@ -133,7 +140,7 @@ def build_plan(stage: str, *, winners: dict | None = None) -> dict:
                          _workload("tune-window128", 4096, 64, "window"),
                          _workload("tune-window512", 4096, 128, "window", window=511),
                          _workload("tune-document", 4096, 64, "document")):
-            configs = _family_configs(workload["pattern"])
+            configs = _family_configs(workload["pattern"], workload["dim"])
             random.Random(2026).shuffle(configs)
             for index, config in enumerate(configs):
                 cases.append(_config_case(workload, 23, config, flex=index == 0))
@@ -201,7 +208,7 @@ def replay_search(records, *, budgets=(4, 8, 12), seeds=20) -> dict:
     reports = []
     for workload, group in sorted(groups.items()):
         table = {KernelConfig(**r["case"]["config"]): r["measurement"] for r in group}
-        space = set(_family_configs(group[0]["case"]["pattern"]))
+        space = set(_family_configs(group[0]["case"]["pattern"], group[0]["case"]["dim"]))
         if set(table) != space:
             reports.append({"workload_id": workload, "status": "incomplete_table",
                             "measured_configs": len(table)})
@@ -217,7 +224,7 @@ def replay_search(records, *, budgets=(4, 8, 12), seeds=20) -> dict:
             return CandidateResult(eligible(measured), measured.get("latency_ms"),
                                    error=measured.get("error"))
 
-        for method in ("random", "evolution"):
+        for method in ("random", "descent"):
             for budget in budgets:
                 for seed in range(seeds):
                     best = search(lookup, sorted(space, key=lambda c: astuple_key(c)),
@@ -237,7 +244,8 @@ def replay_search(records, *, budgets=(4, 8, 12), seeds=20) -> dict:
 
 
 def astuple_key(config: KernelConfig) -> tuple:
-    return (config.block_q, config.block_k, config.implementation, config.use_full_blocks)
+    return (config.block_q, config.block_k, config.implementation, config.use_full_blocks,
+            config.pipeline)
 
 
 def is_fatal(measurement: dict) -> bool:

@@ -2113,7 +2113,21 @@ extern "C" int sfl_attn_fwd(const SflAttnTensor* q, const SflAttnTensor* k, cons
                             const SflAttnTensor* o, float* lse, int B, int H, int N, int D,
                             float scale, const SflAttnMask* mask, int is_fp16, int* status,
                             void* stream_) {
+  return sfl_attn_fwd_pipeline(q, k, v, o, lse, B, H, N, D, scale, mask, is_fp16, 0, status,
+                               stream_);
+}
+
+// pipeline: 0 = default (two work streams per CTA with P in tensor memory for head dimension
+// 64, one stream for 128; SFL_ATTN_FWD=1|2|3 overrides the default for A/B runs), 1 = one
+// stream per CTA, 2 = two streams, P in tensor memory, 3 = two streams, P in shared memory.
+// Head dimension 128 always runs the one-stream kernel.
+extern "C" int sfl_attn_fwd_pipeline(const SflAttnTensor* q, const SflAttnTensor* k,
+                                     const SflAttnTensor* v, const SflAttnTensor* o, float* lse,
+                                     int B, int H, int N, int D, float scale,
+                                     const SflAttnMask* mask, int is_fp16, int pipeline,
+                                     int* status, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (pipeline < 0 || pipeline > 3) return -2;
   if ((D != 64 && D != 128) || B <= 0 || H <= 0 || N <= 0 || mask == nullptr) return -2;
   if (!strides_ok(*q) || !strides_ok(*k) || !strides_ok(*v) || !strides_ok(*o)) return -2;
   CUtensorMap tq, tk, tv;
@@ -2126,13 +2140,12 @@ extern "C" int sfl_attn_fwd(const SflAttnTensor* q, const SflAttnTensor* k, cons
   p.o = o->ptr; p.o_sb = o->stride_b; p.o_sh = o->stride_h; p.o_st = o->stride_t;
   p.lse = lse; p.is_fp16 = is_fp16; p.status = status;
   const int items = ((N + kTile - 1) / kTile) * B * H;
-  // SFL_ATTN_FWD: 1 = one work stream per CTA (the only form for head dimension 128),
-  // 2 = two streams with P in tensor memory (default for head dimension 64),
-  // 3 = two streams with P in shared memory.
-  static const int variant = [] {
+  static const int default_variant = [] {
     const char* v = getenv("SFL_ATTN_FWD");
-    return v == nullptr ? 2 : atoi(v);
+    const int chosen = v == nullptr ? 2 : atoi(v);
+    return chosen >= 1 && chosen <= 3 ? chosen : 2;
   }();
+  const int variant = pipeline != 0 ? pipeline : default_variant;
   if (D == 64 && variant != 1) {
     const int slots = (items + 1) / 2;
     dim3 grid2(slots < attn_sm_count() ? slots : attn_sm_count());

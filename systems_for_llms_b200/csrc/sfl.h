@@ -143,6 +143,13 @@ typedef struct SflAttnMask {
 int sfl_attn_fwd(const SflAttnTensor* q, const SflAttnTensor* k, const SflAttnTensor* v,
                  const SflAttnTensor* o, float* lse, int B, int H, int N, int D, float scale,
                  const SflAttnMask* mask, int is_fp16, int* status, void* stream);
+/* Same with the forward kernel variant chosen by the caller: 0 = default, 1 = one work
+ * stream per CTA, 2 = two streams per CTA with P kept in tensor memory, 3 = two streams with
+ * P in shared memory (2 and 3 exist for head dimension 64; 128 always runs variant 1). */
+int sfl_attn_fwd_pipeline(const SflAttnTensor* q, const SflAttnTensor* k, const SflAttnTensor* v,
+                          const SflAttnTensor* o, float* lse, int B, int H, int N, int D,
+                          float scale, const SflAttnMask* mask, int is_fp16, int pipeline,
+                          int* status, void* stream);
 /* Gradients of the above.  delta is fp32 [B,H,N] scratch owned by the caller (the
  * query-owned kernel fills it, the key-owned kernel reads it).  With rope_cos and
  * rope_sin (fp32 [N, D/2], 16-byte aligned; both or neither) dq and dk are written

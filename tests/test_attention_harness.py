@@ -18,28 +18,36 @@ from systems_for_llms_b200.attention import (analyze_extensions, analyze_study, 
                                              block_benchmark, decode_study, gpu_search, launcher,
                                              study)
 from systems_for_llms_b200.attention.masks import MaskSpec
-from systems_for_llms_b200.attention.search import (CandidateResult, KernelConfig, default_configs,
-                                                    hamming, replay, sanitize, search,
-                                                    select_parents)
+from systems_for_llms_b200.attention.search import (FIELD_ORDER, CandidateResult, KernelConfig,
+                                                    default_configs, differing_fields, replay,
+                                                    sanitize, search)
 
 
 # ------------------------------------------------------------------ search ------
 def latency_of(config: KernelConfig) -> float:
+    """A separable cost with one clear optimum: two streams, interval, wide key blocks."""
     return (1.0 + 0.01 * config.block_q / 64 + 0.02 * (128 // config.block_k)
             + (0.3 if config.implementation == "csr" else 0.0)
-            + (0.1 if not config.use_full_blocks else 0.0))
+            + (0.1 if not config.use_full_blocks else 0.0)
+            + {"two_stream": 0.0, "two_stream_smem_p": 0.05, "one_stream": 0.4}[config.pipeline])
 
 
 def fake_evaluate(config):
     return CandidateResult(True, latency_of(config))
 
 
-def test_space_has_24_distinct_candidates():
-    configs = default_configs()
-    assert len(configs) == 24 and len(set(configs)) == 24
+def test_space_sizes_per_head_dimension():
+    wide = default_configs(64)
+    assert len(wide) == 42 and len(set(wide)) == 42
+    assert {c.pipeline for c in wide} == {"two_stream", "two_stream_smem_p", "one_stream"}
+    narrow = default_configs(128)
+    assert len(narrow) == 14 and {c.pipeline for c in narrow} == {"one_stream"}
+    # the interval form has no schedule granularity: it appears once per remaining setting
+    assert sum(c.implementation == "interval" for c in wide) == 6
+    assert all((c.block_q, c.block_k) == (128, 128) for c in wide if c.implementation == "interval")
 
 
-@pytest.mark.parametrize("method", ["random", "evolution"])
+@pytest.mark.parametrize("method", ["random", "descent"])
 def test_search_respects_budget_and_never_repeats(method):
     result = search(fake_evaluate, budget=9, method=method, seed=3)
     configs = [o.config for o in result.history]
@@ -49,21 +57,45 @@ def test_search_respects_budget_and_never_repeats(method):
 
 
 def test_search_is_deterministic_per_seed():
-    a = search(fake_evaluate, budget=12, method="evolution", seed=5)
-    b = search(fake_evaluate, budget=12, method="evolution", seed=5)
+    a = search(fake_evaluate, budget=12, method="descent", seed=5)
+    b = search(fake_evaluate, budget=12, method="descent", seed=5)
     assert [o.config for o in a.history] == [o.config for o in b.history]
+    c = search(fake_evaluate, budget=12, method="descent", seed=6)
+    assert [o.config for o in a.history] != [o.config for o in c.history]
 
 
-def test_evolution_mutates_exactly_one_field_of_a_measured_parent():
-    result = search(fake_evaluate, budget=16, method="evolution", seed=1, restart_probability=0.0)
-    mutations = [o for o in result.history if o.origin == "mutation"]
-    assert mutations
-    seen = set()
-    for observation in result.history:
-        if observation.origin == "mutation":
-            assert observation.parent in seen
-            assert hamming(observation.parent, observation.config) == 1
-        seen.add(observation.config)
+def test_descent_sweeps_one_field_at_a_time_from_the_incumbent():
+    start = KernelConfig(64, 32, "csr", False, "one_stream")
+    result = search(fake_evaluate, budget=20, method="descent", seed=1, start=start)
+    first, *rest = result.history
+    assert first.origin == "start" and first.config == start and first.parent is None
+    incumbent, incumbent_ms = first.config, first.result.latency_ms
+    swept = []
+    for observation in rest:
+        if not observation.origin.startswith("sweep:"):
+            break
+        name = observation.origin.split(":")[1]
+        assert name in FIELD_ORDER and observation.parent is not None
+        assert differing_fields(observation.parent, observation.config) == 1
+        assert getattr(observation.parent, name) != getattr(observation.config, name)
+        # a sweep step is always taken from a configuration at least as fast as all before it
+        assert latency_of(observation.parent) <= incumbent_ms + 1e-12
+        incumbent_ms = min(incumbent_ms, latency_of(observation.parent))
+        swept.append(name)
+    assert swept[0] == "pipeline" and len(set(swept)) >= 3
+    # on a separable cost the descent reaches the global optimum well inside the budget
+    assert result.best.result.latency_ms == pytest.approx(min(map(latency_of, default_configs())))
+
+
+def test_descent_restarts_far_from_what_it_measured():
+    flat = search(lambda c: CandidateResult(True, 1.0), budget=42, method="descent", seed=0)
+    restarts = [o for o in flat.history if o.origin == "restart"]
+    assert restarts and len(flat.history) == 42
+    for observation in restarts:
+        before = [o.config for o in flat.history[:observation.evaluation - 1]]
+        reach = min(differing_fields(observation.config, c) for c in before)
+        others = [c for c in default_configs() if c not in before]
+        assert reach == max(min(differing_fields(c, m) for m in before) for c in others)
 
 
 def test_failures_spend_budget_and_are_recorded():
@@ -72,11 +104,12 @@ def test_failures_spend_budget_and_are_recorded():
             raise RuntimeError("out of resources")
         return fake_evaluate(config)
 
-    result = search(flaky, budget=24, method="random", seed=0)
-    failed = [o for o in result.history if not o.result.eligible]
-    assert len(result.history) == 24 and len(failed) == 8
-    assert all("out of resources" in o.result.error for o in failed)
-    assert result.best.config.block_k != 32
+    for method in ("random", "descent"):
+        result = search(flaky, budget=42, method=method, seed=0)
+        failed = [o for o in result.history if not o.result.eligible]
+        assert len(result.history) == 42 and len(failed) == 12
+        assert all("out of resources" in o.result.error for o in failed)
+        assert result.best.config.block_k != 32
 
 
 def test_sanitize_rejects_malformed_results():
@@ -88,13 +121,6 @@ def test_sanitize_rejects_malformed_results():
     assert not CandidateResult(True, 1.0, error="late failure").eligible
 
 
-def test_parent_selection_is_fastest_then_most_distant():
-    history = search(fake_evaluate, budget=24, method="random", seed=0).history
-    parents = select_parents(list(history), 3)
-    assert parents[0] == min(history, key=lambda o: o.result.latency_ms).config
-    assert len(set(parents)) == 3
-
-
 def test_bad_arguments_raise():
     with pytest.raises(ValueError):
         search(fake_evaluate, budget=-1)
@@ -102,16 +128,23 @@ def test_bad_arguments_raise():
         search(fake_evaluate, budget=2, method="grid")
     with pytest.raises(TypeError):
         search(fake_evaluate, [("not", "a config")], budget=1)
+    with pytest.raises(TypeError):
+        search(fake_evaluate, budget=1, start="fastest")
     with pytest.raises(ValueError):
         KernelConfig(0, 64)
+    with pytest.raises(ValueError):
+        KernelConfig(64, 64, pipeline="three_stream")
 
 
 def test_offline_replay_matches_a_live_search():
-    live = search(fake_evaluate, budget=24, method="random", seed=0)
-    again = replay(live.to_dict()["history"], budget=8, method="evolution", seed=2)
-    direct = search(fake_evaluate, [o.config for o in live.history], budget=8, method="evolution",
+    live = search(fake_evaluate, budget=42, method="random", seed=0)
+    again = replay(live.to_dict()["history"], budget=8, method="descent", seed=2)
+    direct = search(fake_evaluate, [o.config for o in live.history], budget=8, method="descent",
                     seed=2)
     assert again.best.config == direct.best.config
+    partial = replay(live.to_dict()["history"][:5], budget=10, method="random", seed=0,
+                     configs=default_configs())
+    assert sum(o.result.eligible for o in partial.history) <= 5
 
 
 # --------------------------------------------------------------- gpu_search ------
@@ -157,7 +190,7 @@ def test_spec_for_mask_names():
 # -------------------------------------------------------------------- study ------
 def test_plans_are_deterministic_with_expected_sizes():
     sizes = {stage: len(study.build_plan(stage)["cases"]) for stage in study.STAGES}
-    assert sizes == {"smoke": 20, "ablation": 120, "flex_hints": 24, "tuning": 84,
+    assert sizes == {"smoke": 20, "ablation": 120, "flex_hints": 24, "tuning": 134,
                      "confirmation": 12}
     assert study.build_plan("ablation") == study.build_plan("ablation")
     with pytest.raises(ValueError):
@@ -277,8 +310,7 @@ def test_block_plan_freezes_configurations():
     plan = block_benchmark.build_block_plan()
     assert len(plan["cases"]) == 8
     assert all(c["selection"]["policy"] == "fixed_default" for c in plan["cases"])
-    winner = {"tune-causal": {"case_id": "x", "config": asdict(KernelConfig(64, 32, "interval",
-                                                                            False))}}
+    winner = {"tune-causal": {"case_id": "x", "config": asdict(KernelConfig(64, 32, "csr", False))}}
     plan = block_benchmark.build_block_plan(winner)
     causal = [c for c in plan["cases"] if c["pattern"] == "causal"]
     assert all(c["config"]["block_k"] == 32 and c["selection"]["source_case_id"] == "x"
@@ -356,7 +388,7 @@ def test_analysis_of_tuning_confirmation_and_block_runs(tmp_path):
     stages = {s["stage"]: s for s in summary["studies"]}
     assert set(stages) == {"tuning", "confirmation", "block"}
     tuning = stages["tuning"]["tuning"]
-    assert tuning[0]["valid_configurations"] in (12, 24)
+    assert tuning[0]["valid_configurations"] in (14, 36, 42)
     assert stages["tuning"]["search_replay"]["groups"]
     confirmation = stages["confirmation"]["confirmation"][0]
     assert confirmation["paired_cases"] == 12 and confirmation["geomean_speedup"] >= 1.0
