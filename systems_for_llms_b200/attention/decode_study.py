@@ -3,12 +3,13 @@
 Same two stages as the reference's decode study
 (attention_lab/cuda_decode/study.py:73-261):
 
-``smoke``   for both kernel variants, 2 dtypes x D in {64, 128} x GQA ratio in
+``smoke``   for every kernel variant, 2 dtypes x D in {64, 128} x GQA ratio in
             {1, 2, 4, 8} x cache length in {1, 31, 32, 33, 127, 513} x splits in
             {1, 3, 8} on a ragged batch (lengths 0, 1, half, full), plus three
             special cases: 128 splits with a custom scale, launch on a caller's
             non-default stream, and CUDA-graph replay after the lengths tensor was
-            edited in place: 288 + 3 checks per variant, 582 in all.
+            edited in place: 288 + 3 checks per variant - 582 for the two
+            CUDA-core schedules the reference has, 873 with the tensor-core one.
 ``study``   the smoke sweep as a pre-flight, then ten serving-like shapes x three
             input seeds: every (variant, splits) combination is checked against
             an fp32 oracle and timed by CUDA-graph replay, next to SDPA (flash
@@ -33,7 +34,8 @@ from pathlib import Path
 from .decode import prepare
 from .study import write_json
 
-VARIANTS = ("token", "tile")
+REFERENCE_VARIANTS = ("token", "tile")      # softmax schedules on the CUDA cores
+VARIANTS = REFERENCE_VARIANTS + ("mma",)     # + scores and P V on the tensor cores
 SMOKE_LENGTHS = (1, 31, 32, 33, 127, 513)
 SMOKE_SPLITS = (1, 3, 8)
 STUDY_SPLITS = (1, 2, 4, 8, 16, 32)
@@ -204,7 +206,8 @@ def summarise_case(record: dict) -> None:
     best_ms = timings[best]["median_ms"]
     by_variant = {variant: min((n for n in ours if n.startswith(f"cuda_{variant}_")),
                                key=lambda name: timings[name]["median_ms"])
-                  for variant in VARIANTS}
+                  for variant in VARIANTS
+                  if any(n.startswith(f"cuda_{variant}_") for n in ours)}
     record.update({
         "best_observed": best, "best_observed_by_variant": by_variant,
         "best_tile_over_best_token": (timings[by_variant["token"]]["median_ms"]

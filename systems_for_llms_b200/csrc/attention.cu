@@ -37,7 +37,7 @@ namespace sfl {
 
 constexpr int kTile = 128;          // rows and columns of a score tile
 constexpr int kAttnThreads = 192;   // forward: producer warp, MMA warp, 4 softmax warps
-constexpr int kBwdThreads = 320;    // backward: producer, MMA, 8 compute warps (2 per TMEM lane quarter)
+constexpr int kBwdThreads = 320;    // backward: producer, MMA, two compute warpgroups
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -251,18 +251,6 @@ __device__ __forceinline__ void store_row_swizzled(uint8_t* tile, int row,
   }
 }
 
-// Same layout, one 32-column chunk (16 packed pairs) at a time.
-__device__ __forceinline__ void store_chunk_swizzled(uint8_t* tile, int row, int chunk,
-                                                     const uint32_t (&packed)[16]) {
-  uint8_t* base = tile + (chunk >> 1) * (kTile * 128) + row * 128;
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    const int c16 = (chunk & 1) * 4 + c;
-    *reinterpret_cast<uint4*>(base + ((c16 ^ (row & 7)) << 4)) =
-        make_uint4(packed[c * 4 + 0], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
-  }
-}
-
 // Descriptors of the k-th 16-wide reduction step.
 //   K-major tile of [rows][W] 16-bit elements stored as W/64 column halves.
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t base, int rows, int k) {
@@ -275,9 +263,6 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t base, int k) {
 
 __device__ __forceinline__ void named_barrier_128() {
   asm volatile("bar.sync 1, 128;" ::: "memory");
-}
-__device__ __forceinline__ void named_barrier_bwd() {  // the backward kernel's compute warps
-  asm volatile("bar.sync 1, %0;" ::"n"(kBwdThreads - 64) : "memory");
 }
 
 __device__ __forceinline__ void tmem_ld_32x32f(uint32_t taddr, float* dst) {
@@ -781,8 +766,16 @@ __device__ __forceinline__ void named_barrier_slot(int slot) {
 // [6] waiting for the previous P V product; MMA warp of slot 0 - [8] waiting for P and V,
 // [9] issuing a P V product, [10] waiting for the score tile to be free and for K (and Q),
 // [11] issuing a score product, [12] tiles.
+// Backward (sfl_attn_bwd_trace_read; 16 entries for the dQ kernel, then 16 for the dK/dV
+// kernel; CTA (0, 0), the heaviest one under a causal mask): compute warp 2 - [0] tile set-up,
+// [1] waiting for a score half, [2] waiting for the P / dS half to be free, [3] loading
+// scores and dP, [4] exponentials, dS and the shared-memory stores, [5] halves, [6] epilogue;
+// MMA warp - [8] waiting for the streamed tile and issuing scores, [9] waiting for P / dS,
+// [10] issuing the accumulations, [12] halves; [13] cycles and [15] nanoseconds in the kernel;
+// with -DSFL_ATTN_TRACE_SERIAL the MMA warp also waits for each batch it issued and adds up
+// [11] issue-to-completion cycles of the score batches and [14] of the accumulation batches.
 #ifdef SFL_ATTN_TRACE
-__device__ unsigned long long g_attn_trace[16];
+__device__ unsigned long long g_attn_trace[48];
 __device__ unsigned long long g_attn_stamps[64];  // globaltimer of CTA 0: see SFL_STAMP uses
 __device__ __forceinline__ void attn_stamp(int at) {
   unsigned long long t;
@@ -801,10 +794,23 @@ __device__ __forceinline__ void attn_stamp(int at) {
   }
 #define SFL_TRACE_COUNT(slot) \
   if (tracing_) atomicAdd(&g_attn_trace[slot], 1ull);
+#define SFL_TRACE_TOTAL(cond, base)                                                            \
+  if (cond) {                                                                                  \
+    unsigned long long ns1_;                                                                   \
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(ns1_));                                    \
+    atomicAdd(&g_attn_trace[(base) + 13], static_cast<unsigned long long>(clock64() - t0_));   \
+    atomicAdd(&g_attn_trace[(base) + 15], ns1_ - ns0_);                                        \
+  }
+#define SFL_TRACE_BEGIN()                                  \
+  const long long t0_ = clock64();                         \
+  unsigned long long ns0_;                                 \
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(ns0_));
 #else
 #define SFL_TRACE_DECL(cond)
 #define SFL_TRACE_MARK(slot)
 #define SFL_TRACE_COUNT(slot)
+#define SFL_TRACE_TOTAL(cond, base)
+#define SFL_TRACE_BEGIN()
 #define SFL_STAMP(cond, at)
 #endif
 
@@ -1585,25 +1591,28 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
 }
 
 // ============================================================= backward ====
-// Shared layout of the two backward kernels: an "owned" pair of resident tiles,
-// a ring of streamed tile pairs, and two [128 x 128] tiles written by the compute
-// warps (probabilities and dS) for the accumulation MMAs.
+// Shared layout of the two backward kernels: an "owned" pair of resident tiles and a
+// ring of streamed tile pairs, each stage with the per-column statistics (and document
+// labels) of its streamed tile.  Probabilities and dS never touch shared memory: the
+// compute warps write them back into tensor memory, over the scores they were made
+// from, and the accumulation MMAs read them from there as their A operand.
 template <int D>
 struct BwdSmem {
   static constexpr int kTileBytes = kTile * D * 2;
-  static constexpr int kPBytes = kTile * kTile * 2;
-  static constexpr int kStages = (D == 64) ? 2 : 1;
-  static constexpr int kBytes =
-      2 * kTileBytes + kStages * 2 * kTileBytes + 2 * kPBytes + 1024 + 3072 + 256;
+  static constexpr int kStages = (D == 64) ? 4 : 2;
+  static constexpr int kStatBytes = kStages * (2 * kTile * 4 + kTile * 4);
+  static constexpr int kBytes = 2 * kTileBytes + kStages * 2 * kTileBytes + kStatBytes + 1024 + 256;
 };
 
 struct BwdBarriers {
   uint64_t own_full;
-  uint64_t in_full[2], in_empty[2];
-  // Each streamed tile is processed as two halves of 64 columns; index = half.
-  uint64_t sp_full[2];    // score and dP accumulator halves ready
-  uint64_t pds_ready[2];  // P and dS half tiles written (128 arrivals)
-  uint64_t acc_done[2];   // accumulation MMAs of the half finished
+  uint64_t in_full[4], in_empty[4];
+  // Each streamed tile is processed as two halves of 64 columns, one per compute
+  // warpgroup; the halves rotate through up to three score buffers; index = buffer.
+  uint64_t sp_full[3];    // score and dP accumulator halves ready
+  uint64_t pds_ready[3];  // P and dS of the half written to tensor memory (128 arrivals)
+  uint64_t acc_done;      // every accumulation MMA finished
+  uint64_t probe;         // -DSFL_ATTN_TRACE_SERIAL only: completion of one batch of MMAs
   uint32_t tmem_base;
   int abort;
 };
@@ -1614,6 +1623,19 @@ struct BwdBarriers {
 // dQ kernel (KV_OWNED = false): CTA owns a query tile; streams (K, V) tiles.
 //   S = Q K^T, dP = dO V^T, P = exp(S - lse_q), dS = P (dP - delta_q)
 //   dQ += dS K
+//
+// Roles: warp 0 streams tiles (TMA) and stages the statistics of their columns, warp 1
+// issues the MMAs, warps 2-5 and 6-9 are two compute warpgroups.  Warpgroup g owns
+// columns [64 g, 64 g + 64) of every streamed tile: it waits for that half of S and dP,
+// turns it into P and dS, stores them as packed 16-bit pairs over the first 32 columns
+// of the half it just read, and signals the MMA warp, which accumulates from tensor
+// memory.  The stream of halves rotates through kBufs score buffers in tensor memory
+// (three where 3 x 128 columns fit beside the accumulators, else two): the scores of
+// half h + kBufs are issued right after the accumulation of half h, so with three
+// buffers a warpgroup finds its next half computed when it finishes one and the
+// exponentials, not the hand-overs, set the pace.  A 128 x 64 x 16 product with both
+// operands in shared memory is bound by the 6 KB it reads (48 cycles measured); with A
+// in tensor memory it runs at the pipe's 32 cycles.
 template <int D, bool FP16, bool KV_OWNED>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or Q
@@ -1625,15 +1647,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
+  constexpr int ST = L::kStages;
   uint8_t* sOwnA = smem;
   uint8_t* sOwnB = sOwnA + L::kTileBytes;
   uint8_t* sIn = sOwnB + L::kTileBytes;  // stages x (A, B)
-  uint8_t* sP = sIn + L::kStages * 2 * L::kTileBytes;
-  uint8_t* sDS = sP + L::kPBytes;
-  float* sStats = reinterpret_cast<float*>(sDS + L::kPBytes);  // 2 x (-lse[128], delta[128])
-  int* sDoc = reinterpret_cast<int*>(sStats + 4 * kTile);       // 2 x labels of a streamed tile
-  BwdBarriers* bars = reinterpret_cast<BwdBarriers*>(reinterpret_cast<uint8_t*>(sStats) + 3072);
+  float* sStats = reinterpret_cast<float*>(sIn + ST * 2 * L::kTileBytes);  // stages x (-lse[128], delta[128])
+  int* sDoc = reinterpret_cast<int*>(sStats + ST * 2 * kTile);             // stages x labels[128]
+  BwdBarriers* bars = reinterpret_cast<BwdBarriers*>(sDoc + ST * kTile);
 
+  SFL_TRACE_BEGIN()
+  constexpr int kTr = KV_OWNED ? 32 : 16;  // base of this kernel's phase timers
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_tiles = (p.N + kTile - 1) / kTile;
   const int own_tile = KV_OWNED ? blockIdx.x : num_tiles - 1 - blockIdx.x;
@@ -1641,19 +1664,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
   const int b = bh / p.H, h = bh % p.H;
   const TileRange range = tile_range(p.sched, own_tile, p.N, KV_OWNED);
   const int n_tiles = range.end - range.begin;
-  constexpr int ST = L::kStages;
+  const long stat_base = (static_cast<long>(b) * p.H + h) * p.N;
+  const bool have_doc = p.sched.doc != nullptr;
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->own_full, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&bars->in_full[s], 1);
+    for (int s = 0; s < ST; ++s) {
+      mbar_init(&bars->in_full[s], 1 + 32);  // the TMA transaction and the 32 staging lanes
       mbar_init(&bars->in_empty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < 3; ++s) {
       mbar_init(&bars->sp_full[s], 1);
-      mbar_init(&bars->pds_ready[s], kBwdThreads - 64);
-      mbar_init(&bars->acc_done[s], 1);
+      mbar_init(&bars->pds_ready[s], 128);
     }
+    mbar_init(&bars->acc_done, 1);
+    mbar_init(&bars->probe, 1);
     bars->abort = 0;
     mbar_fence_init();
   }
@@ -1667,40 +1692,61 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
   const uint32_t tmem = bars->tmem_base;
   pdl_launch_dependents();
   pdl_wait();
-  const uint32_t tS = tmem;         // scores
-  const uint32_t tDP = tmem + 128;  // dP
-  const uint32_t tAcc0 = tmem + 256;      // dV (kv-owned) or dQ
-  const uint32_t tAcc1 = tmem + 256 + D;  // dK (kv-owned)
+  // Score buffer i: S in columns [128 i, 128 i + 64), dP in the next 64; P and dS are
+  // written over the first 32 columns of each.  The accumulators follow the buffers.
+  constexpr int kBufs = (KV_OWNED && D == 128) ? 2 : 3;
+  const uint32_t tAcc0 = tmem + kBufs * 128;      // dV (kv-owned) or dQ
+  const uint32_t tAcc1 = tmem + kBufs * 128 + D;  // dK (kv-owned)
   volatile int* abort = &bars->abort;
 
   if (warp == 0) {
-    if (lane == 0 && n_tiles > 0) {
-      mbar_expect_tx(&bars->own_full, 2 * L::kTileBytes);
-      load_rows<D>(sOwnA, &tmOwnA, &bars->own_full, own_tile * kTile, h, b);
-      load_rows<D>(sOwnB, &tmOwnB, &bars->own_full, own_tile * kTile, h, b);
+    // ------------------------------------------------------ producer ----
+    if (n_tiles > 0) {
+      if (lane == 0) {
+        mbar_expect_tx(&bars->own_full, 2 * L::kTileBytes);
+        load_rows<D>(sOwnA, &tmOwnA, &bars->own_full, own_tile * kTile, h, b);
+        load_rows<D>(sOwnB, &tmOwnB, &bars->own_full, own_tile * kTile, h, b);
+      }
       for (int j = 0; j < n_tiles; ++j) {
         const TileInfo t = tile_info(p.sched, range, j);
         const int s = j % ST;
         if (!bounded_wait(&bars->in_empty[s], ((j / ST) & 1) ^ 1, abort, p.status,
                           kStatusTimeoutEmpty))
           break;
-        mbar_expect_tx(&bars->in_full[s], 2 * L::kTileBytes);
-        uint8_t* dst = sIn + s * 2 * L::kTileBytes;
-        load_rows<D>(dst, &tmInA, &bars->in_full[s], t.other * kTile, h, b);
-        load_rows<D>(dst + L::kTileBytes, &tmInB, &bars->in_full[s], t.other * kTile, h, b);
+        if (lane == 0) {
+          mbar_expect_tx(&bars->in_full[s], 2 * L::kTileBytes);
+          uint8_t* dst = sIn + s * 2 * L::kTileBytes;
+          load_rows<D>(dst, &tmInA, &bars->in_full[s], t.other * kTile, h, b);
+          load_rows<D>(dst + L::kTileBytes, &tmInB, &bars->in_full[s], t.other * kTile, h, b);
+        }
+        // Per-column data of the streamed tile, four columns per lane: (negated, log-2)
+        // log-sum-exp and delta of the query columns for the key-owned kernel, document
+        // labels for both.  They travel with the tile: the lanes arrive on its barrier.
+        if (KV_OWNED || have_doc) {
+          float* stats = sStats + s * (2 * kTile);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int col = lane * 4 + e;
+            const int ci = t.other * kTile + col;
+            if constexpr (KV_OWNED) {
+              float ls = ci < p.N ? p.lse[stat_base + ci] * kLog2e : INFINITY;
+              if (ls == -INFINITY) ls = INFINITY;  // query without keys: P = 0
+              stats[col] = -ls;
+              stats[kTile + col] = ci < p.N ? p.delta[stat_base + ci] : 0.f;
+            }
+            if (have_doc) sDoc[s * kTile + col] = ci < p.N ? p.sched.doc[ci] : -1;
+          }
+        }
+        mbar_arrive(&bars->in_full[s]);
       }
     }
   } else if (warp == 1) {
+    // ---------------------------------------------------- MMA issuer ----
     // The whole warp walks the loop; one elected lane issues, so that descriptors and
     // tensor-memory addresses stay in uniform registers (see attn_fwd2_kernel).
     if (n_tiles > 0) {
-      // The streamed tile is handled as two halves of 64 columns so that the tensor
-      // pipe works on the scores of half h+1 and the accumulation of half h-1 while
-      // the compute warps turn half h into probabilities: TMEM columns and the
-      // shared P / dS tiles are already stored as two 64-column halves.
       constexpr uint32_t idesc_s = idesc_16bit(FP16, kTile, 64, false, false);
       constexpr uint32_t idesc_acc = idesc_16bit(FP16, kTile, D, false, true);
-      const int halves = 2 * n_tiles;
       // Descriptors are built once and stepped by constant offsets (see
       // umma_desc_advance): per MMA the issuing thread then only adds and issues.
       uint64_t own_a[D / 16], own_b[D / 16];
@@ -1711,86 +1757,108 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
       }
       const uint64_t in_k0 = desc_kmajor(smem_u32(sIn), kTile, 0);   // streamed tile, K-major view
       const uint64_t in_mn0 = desc_mnmajor(smem_u32(sIn), 0);        // same tile, MN-major view
-      const uint64_t p_k0 = desc_kmajor(smem_u32(sP), kTile, 0);
-      const uint64_t ds_k0 = desc_kmajor(smem_u32(sDS), kTile, 0);
+      // scores and dP of half h of the stream (tile h / 2, columns 64 (h % 2) ...)
+      const int halves = 2 * n_tiles;
       auto issue_scores = [&](int h) -> bool {
-        const int j = h >> 1, hh = h & 1, s = j % ST;
-        if (hh == 0 &&
+        const int j = h >> 1, g = h & 1, s = j % ST, buf = h % kBufs;
+        if (g == 0 &&
             !bounded_wait(&bars->in_full[s], (j / ST) & 1, abort, p.status, kStatusTimeoutFull))
           return false;
         tc_fence_after();
-        // rows [64 hh, 64 hh + 64) of the streamed pair (A then B, kTileBytes apart)
-        const uint64_t in_a = umma_desc_advance(in_k0, s * 2 * L::kTileBytes + hh * 64 * 128);
+        // rows [64 g, 64 g + 64) of the streamed pair (A then B, kTileBytes apart)
+        const uint64_t in_a = umma_desc_advance(in_k0, s * 2 * L::kTileBytes + g * 64 * 128);
         const uint64_t in_b = umma_desc_advance(in_a, L::kTileBytes);
+        const uint32_t tS = tmem + buf * 128, tDP = tS + 64;
+#ifdef SFL_ATTN_TRACE_SERIAL
+        const long long issue_t0 = clock64();
+#endif
         if (elect_one()) {
 #pragma unroll
           for (int k = 0; k < D / 16; ++k)  // S^T = K Q^T   or   S = Q K^T
-            umma_bf16_ss(tS + hh * 64, own_a[k],
+            umma_bf16_ss(tS, own_a[k],
                          umma_desc_advance(in_a, (k >> 2) * (kTile * 128) + (k & 3) * 32), idesc_s,
                          k != 0);
 #pragma unroll
           for (int k = 0; k < D / 16; ++k)  // dP^T = V dO^T  or  dP = dO V^T
-            umma_bf16_ss(tDP + hh * 64, own_b[k],
+            umma_bf16_ss(tDP, own_b[k],
                          umma_desc_advance(in_b, (k >> 2) * (kTile * 128) + (k & 3) * 32), idesc_s,
                          k != 0);
-          umma_commit(&bars->sp_full[hh]);
+          umma_commit(&bars->sp_full[buf]);
         }
         __syncwarp();
+#ifdef SFL_ATTN_TRACE_SERIAL
+        {  // [7] cycles spent issuing a score batch into an idle pipe, [11] from then to its completion
+          const long long t0 = clock64();
+          if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0)
+            atomicAdd(&g_attn_trace[kTr + 7], static_cast<unsigned long long>(t0 - issue_t0));
+          bounded_wait(&bars->sp_full[buf], (h / kBufs) & 1, abort, p.status, kStatusTimeoutTmemFull);
+          if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0)
+            atomicAdd(&g_attn_trace[kTr + 11], static_cast<unsigned long long>(clock64() - t0));
+        }
+#endif
         return true;
       };
       bool ok = bounded_wait(&bars->own_full, 0, abort, p.status, kStatusTimeoutFull);
-      if (ok) ok = issue_scores(0);
+      for (int h = 0; h < kBufs && h < halves && ok; ++h) ok = issue_scores(h);
+      SFL_TRACE_DECL(blockIdx.x == 0 && blockIdx.y == 0 && lane == 0)
       for (int h = 0; h < halves && ok; ++h) {
-        const int j = h >> 1, hh = h & 1, s = j % ST;
-        // The score halves of h+1 reuse the TMEM columns of h-1, which the compute
-        // warps released when they signalled pds_ready for h-1 (waited on in the
-        // previous iteration).  With a single stage of streamed tiles the next tile
-        // only arrives after this tile's accumulation, so its scores wait for that.
-        const bool more = h + 1 < halves;
-        const bool early = more && !(ST == 1 && hh == 1);
-        if (early && !issue_scores(h + 1)) break;
-        if (!bounded_wait(&bars->pds_ready[hh], j & 1, abort, p.status, kStatusTimeoutTmemFull))
+        const int j = h >> 1, g = h & 1, s = j % ST, buf = h % kBufs;
+        if (!bounded_wait(&bars->pds_ready[buf], (h / kBufs) & 1, abort, p.status,
+                          kStatusTimeoutTmemFull))
           break;
         tc_fence_after();
+        SFL_TRACE_MARK(kTr + 9)
         // MN-major views of the streamed pair: 16 reduction rows per step, 2048 B apart
-        const uint64_t mn_a = umma_desc_advance(in_mn0, s * 2 * L::kTileBytes + hh * 4 * 2048);
+        const uint64_t mn_a = umma_desc_advance(in_mn0, s * 2 * L::kTileBytes + g * 4 * 2048);
         const uint64_t mn_b = umma_desc_advance(mn_a, L::kTileBytes);
-        const uint64_t p_half = umma_desc_advance(p_k0, hh * (kTile * 128));
-        const uint64_t ds_half = umma_desc_advance(ds_k0, hh * (kTile * 128));
+        const uint32_t a_p = tmem + buf * 128, a_ds = a_p + 64;  // 16 reduction columns = 8 words
         if (elect_one()) {
           if constexpr (KV_OWNED) {
 #pragma unroll
             for (int k = 0; k < 4; ++k)  // dV += P^T dO
-              umma_bf16_ss(tAcc0, umma_desc_advance(p_half, k * 32),
-                           umma_desc_advance(mn_b, k * 2048), idesc_acc, (h | k) != 0);
+              umma_bf16_ts(tAcc0, a_p + k * 8, umma_desc_advance(mn_b, k * 2048), idesc_acc,
+                           (h | k) != 0);
 #pragma unroll
             for (int k = 0; k < 4; ++k)  // dK += dS^T Q
-              umma_bf16_ss(tAcc1, umma_desc_advance(ds_half, k * 32),
-                           umma_desc_advance(mn_a, k * 2048), idesc_acc, (h | k) != 0);
+              umma_bf16_ts(tAcc1, a_ds + k * 8, umma_desc_advance(mn_a, k * 2048), idesc_acc,
+                           (h | k) != 0);
           } else {
 #pragma unroll
             for (int k = 0; k < 4; ++k)  // dQ += dS K
-              umma_bf16_ss(tAcc0, umma_desc_advance(ds_half, k * 32),
-                           umma_desc_advance(mn_a, k * 2048), idesc_acc, (h | k) != 0);
+              umma_bf16_ts(tAcc0, a_ds + k * 8, umma_desc_advance(mn_a, k * 2048), idesc_acc,
+                           (h | k) != 0);
           }
-          if (hh == 1) umma_commit(&bars->in_empty[s]);
-          umma_commit(&bars->acc_done[hh]);
+          if (g == 1) umma_commit(&bars->in_empty[s]);
+          if (h + 1 == halves) umma_commit(&bars->acc_done);
+#ifdef SFL_ATTN_TRACE_SERIAL
+          umma_commit(&bars->probe);
+#endif
         }
         __syncwarp();
-        if (more && !early && !issue_scores(h + 1)) break;
+#ifdef SFL_ATTN_TRACE_SERIAL
+        {  // [14] the same for a batch of accumulation products
+          const long long t0 = clock64();
+          bounded_wait(&bars->probe, h & 1, abort, p.status, kStatusTimeoutTmemFull);
+          if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0)
+            atomicAdd(&g_attn_trace[kTr + 14], static_cast<unsigned long long>(clock64() - t0));
+        }
+#endif
+        SFL_TRACE_MARK(kTr + 10)
+        SFL_TRACE_COUNT(kTr + 12)
+        // The buffer's next half: the tensor pipe is in order, so it overwrites this
+        // half's P and dS only after the products above have read them.
+        if (h + kBufs < halves && !issue_scores(h + kBufs)) break;
+        SFL_TRACE_MARK(kTr + 8)
       }
     }
   } else {
-    // Two warps share each TMEM lane quarter (rows): `part` picks which 32-column
-    // chunk of every 64-column half a warp turns into probabilities, and which
-    // column chunks of the final accumulators it writes out.
+    // ------------------------------------------------ compute warpgroups ----
     const int quarter = warp & 3;
-    const int part = (warp - 2) >> 2;
+    const int wg = (warp - 2) >> 2;  // the 64-column half of every streamed tile this warp works on
     const int row = quarter * 32 + lane;
     const int own_pos = own_tile * kTile + row;  // key index (kv-owned) or query index
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const float scale_log2 = p.scale * kLog2e;
-    const long stat_base = (static_cast<long>(b) * p.H + h) * p.N;
     float my_lse = 0.f, my_delta = 0.f;
     if constexpr (!KV_OWNED) {
       // lse in log2 units; +inf for padding rows makes P vanish.
@@ -1815,98 +1883,65 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
             my_delta = fmaf(x.y, y.y, my_delta);
           }
         }
-        if (part == 0) p.delta[stat_base + own_pos] = my_delta;
+        if (wg == 0) p.delta[stat_base + own_pos] = my_delta;
       }
     }
+    const float neg_lse = -my_lse;
     bool ok = true;
-    float next_ls = 0.f, next_dl = 0.f;
-    if constexpr (KV_OWNED) {
-      if (part == 0 && n_tiles > 0) {
-        const int c0 = tile_info(p.sched, range, 0).other * kTile + row;
-        float ls = c0 < p.N ? p.lse[stat_base + c0] * kLog2e : INFINITY;
-        if (ls == -INFINITY) ls = INFINITY;
-        next_ls = -ls;
-        next_dl = c0 < p.N ? p.delta[stat_base + c0] : 0.f;
-      }
-    }
-    // state of the current streamed tile, set up when its first half starts
-    bool masked = false, use_doc = false;
-    RowMask rm{0, 0u};
-    uint32_t group_bits = 0xffu;
-    int my_doc = -2;
-    for (int h = 0; h < 2 * n_tiles && ok; ++h) {
-      const int j = h >> 1, hh = h & 1;
-      if (hh == 0) {
-        const TileInfo t = tile_info(p.sched, range, j);
-        const int other0 = t.other * kTile;
-        const bool ragged = (other0 + kTile > p.N) || (own_tile * kTile + kTile > p.N);
-        masked = !t.full || ragged;
-        use_doc = masked && p.sched.doc != nullptr;
-        if (KV_OWNED || use_doc) {
-          // Per-column data of this tile: (negated) log-sum-exp and delta of the
-          // query columns for the key-owned kernel, document labels for both.  The
-          // key-owned statistics were fetched from global memory one tile ahead
-          // (next_ls / next_dl), so only the shared-memory hand-over is paid here;
-          // the table is double buffered by tile parity, which makes one barrier
-          // per tile enough (a buffer is rewritten two tiles after it was read, and
-          // every thread passes the barrier in between).
-          float* stats = sStats + (j & 1) * (2 * kTile);
-          const int ci = other0 + row;
-          if (part == 0) {
-            if constexpr (KV_OWNED) {
-              stats[row] = next_ls;
-              stats[kTile + row] = next_dl;
-            }
-            if (use_doc) sDoc[(j & 1) * kTile + row] = ci < p.N ? p.sched.doc[ci] : -1;
-          }
-          named_barrier_bwd();
-          if constexpr (KV_OWNED) {
-            if (part == 0 && j + 1 < n_tiles) {  // statistics of the next streamed tile
-              const int cn = tile_info(p.sched, range, j + 1).other * kTile + row;
-              float ls = cn < p.N ? p.lse[stat_base + cn] * kLog2e : INFINITY;
-              if (ls == -INFINITY) ls = INFINITY;
-              next_ls = -ls;
-              next_dl = cn < p.N ? p.delta[stat_base + cn] : 0.f;
-            }
-          }
-        }
-        rm = RowMask{0, 0u};
-        group_bits = 0xffu;
-        my_doc = -2;
-        if (masked) {
-          // The bitmap is indexed (query sub-block, key sub-block).
-          if constexpr (KV_OWNED) {
-            rm = row_mask_for_key(p.sched, own_pos, other0, p.N);
-            group_bits = 0;
+    SFL_TRACE_DECL(blockIdx.x == 0 && blockIdx.y == 0 && warp == 2 && lane == 0)
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int s = j % ST;
+      const TileInfo t = tile_info(p.sched, range, j);
+      const int other0 = t.other * kTile;
+      const bool ragged = (other0 + kTile > p.N) || (own_tile * kTile + kTile > p.N);
+      const bool masked = !t.full || ragged;
+      const bool use_doc = masked && have_doc;
+      RowMask rm{0, 0u};
+      uint32_t group_bits = 0xffu;
+      int my_doc = -2;
+      if (masked) {
+        // The bitmap is indexed (query sub-block, key sub-block).
+        if constexpr (KV_OWNED) {
+          rm = row_mask_for_key(p.sched, own_pos, other0, p.N);
+          group_bits = 0;
 #pragma unroll
-            for (int g = 0; g < 8; ++g)
-              group_bits |= static_cast<uint32_t>((t.bitmap >> (g * 8 + (row >> 4))) & 1ull) << g;
-          } else {
-            rm = row_mask_for_query(p.sched, own_pos, other0, p.N);
-            group_bits = static_cast<uint32_t>(t.bitmap >> ((row >> 4) * 8)) & 0xffu;
-          }
-          if (use_doc && own_pos < p.N) my_doc = p.sched.doc[own_pos];
+          for (int g = 0; g < 8; ++g)
+            group_bits |= static_cast<uint32_t>((t.bitmap >> (g * 8 + (row >> 4))) & 1ull) << g;
+        } else {
+          rm = row_mask_for_query(p.sched, own_pos, other0, p.N);
+          group_bits = static_cast<uint32_t>(t.bitmap >> ((row >> 4) * 8)) & 0xffu;
         }
+        if (use_doc && own_pos < p.N) my_doc = p.sched.doc[own_pos];
       }
-      if (!bounded_wait(&bars->sp_full[hh], j & 1, abort, p.status, kStatusTimeoutTmemFull)) {
+      const int hs = 2 * j + wg;  // position in the stream of halves
+      const int buf = hs % kBufs;
+      const uint32_t tS = tmem + buf * 128, tDP = tS + 64;
+      SFL_TRACE_MARK(kTr + 0)
+      if (!bounded_wait(&bars->sp_full[buf], (hs / kBufs) & 1, abort, p.status,
+                        kStatusTimeoutTmemFull)) {
+        ok = false;
+        break;
+      }
+      // The staged statistics were published on the tile's own barrier, which completed
+      // before the scores were issued: this wait returns at once and orders the reads.
+      if ((KV_OWNED || use_doc) &&
+          !bounded_wait(&bars->in_full[s], (j / ST) & 1, abort, p.status, kStatusTimeoutFull)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      // Half hh of the P and dS tiles is free once the accumulation MMAs of the
-      // previous tile's same half are done.
-      if (j > 0 && !bounded_wait(&bars->acc_done[hh], (j - 1) & 1, abort, p.status,
-                                 kStatusTimeoutTmemFull)) {
-        ok = false;
-        break;
-      }
-      {
-        const int c = 2 * hh + part;
+      SFL_TRACE_MARK(kTr + 1)
+      const float* stats = sStats + s * (2 * kTile);
+      const int* docs = sDoc + s * kTile;
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = 2 * wg + cc;  // 32-column chunk of the tile
         float sv[32], dp[32];
         uint32_t pp[16], dd[16];
-        tmem_ld_32x32f(tS + lane_base + c * 32, sv);
-        tmem_ld_32x32f(tDP + lane_base + c * 32, dp);
+        tmem_ld_32x32f(tS + lane_base + cc * 32, sv);
+        tmem_ld_32x32f(tDP + lane_base + cc * 32, dp);
         tmem_ld_wait();
+        SFL_TRACE_MARK(kTr + 3)
         if (masked) {
 #pragma unroll
           for (int g = 0; g < 2; ++g) {
@@ -1917,27 +1952,26 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
           }
           if (use_doc) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              sv[i] = sDoc[(j & 1) * kTile + c * 32 + i] == my_doc ? sv[i] : -INFINITY;
+            for (int i = 0; i < 32; ++i) sv[i] = docs[c * 32 + i] == my_doc ? sv[i] : -INFINITY;
           }
         }
-        // Statistics of the 32 columns: the key-owned kernel reads them from the
-        // shared table (the same address for every lane, so 16-byte loads), the
-        // query-owned kernel has them in registers.
-        const float* col_ls = sStats + (j & 1) * (2 * kTile) + c * 32;
+        // Statistics of the 32 columns: the key-owned kernel reads them from the staged
+        // table (the same address for every lane, so 16-byte loads), the query-owned
+        // kernel has them in registers.
+        const float* col_ls = stats + c * 32;
         const float* col_dl = col_ls + kTile;
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
           float nl[4], dl[4];
           if constexpr (KV_OWNED) {
             const float4 a = *reinterpret_cast<const float4*>(col_ls + i);
-            const float4 b = *reinterpret_cast<const float4*>(col_dl + i);
+            const float4 b4 = *reinterpret_cast<const float4*>(col_dl + i);
             nl[0] = a.x; nl[1] = a.y; nl[2] = a.z; nl[3] = a.w;
-            dl[0] = b.x; dl[1] = b.y; dl[2] = b.z; dl[3] = b.w;
+            dl[0] = b4.x; dl[1] = b4.y; dl[2] = b4.z; dl[3] = b4.w;
           } else {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              nl[e] = -my_lse;
+              nl[e] = neg_lse;
               dl[e] = my_delta;
             }
           }
@@ -1953,16 +1987,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
           dd[i >> 1] = pack2<FP16>(ds[0], ds[1]);
           dd[(i >> 1) + 1] = pack2<FP16>(ds[2], ds[3]);
         }
-        if constexpr (KV_OWNED) store_chunk_swizzled(sP, row, c, pp);
-        store_chunk_swizzled(sDS, row, c, dd);
+        // 32 columns of 16-bit values are 16 words: chunk cc of the half lands in
+        // columns [16 cc, 16 cc + 16) of the half, all of which this warp has read.
+        if constexpr (KV_OWNED) tmem_st_32x16(tS + lane_base + cc * 16, pp);
+        tmem_st_32x16(tDP + lane_base + cc * 16, dd);
+        SFL_TRACE_MARK(kTr + 4)
       }
-      fence_proxy_async_smem();
+      tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&bars->pds_ready[hh]);
+      mbar_arrive(&bars->pds_ready[buf]);
+      SFL_TRACE_MARK(kTr + 2)
+      SFL_TRACE_COUNT(kTr + 5)
     }
-    if (ok && n_tiles > 0)  // the tensor pipe is in order: the last half finishing ends them all
-      ok = bounded_wait(&bars->acc_done[1], (n_tiles - 1) & 1, abort, p.status,
-                        kStatusTimeoutTmemFull);
+    if (ok && n_tiles > 0)
+      ok = bounded_wait(&bars->acc_done, 0, abort, p.status, kStatusTimeoutTmemFull);
     if (ok) {
       tc_fence_after();
       const long goff = 2 * (b * p.g_sb + h * p.g_sh + static_cast<long>(own_pos) * p.g_st);
@@ -1970,7 +2008,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
         uint8_t* dst = static_cast<uint8_t*>(dst_base) + goff;
 #pragma unroll
         for (int c0 = 0; c0 < D / 32; c0 += 2) {
-          const int c = c0 + part;
+          const int c = c0 + wg;
           float a[32];
           if (n_tiles > 0) {
             tmem_ld_32x32f(taddr + lane_base + c * 32, a);
@@ -2024,9 +2062,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
         write_acc(tAcc0, p.dq, p.scale, rotate);
       }
     }
+    SFL_TRACE_MARK(kTr + 6)
   }
   tc_fence_before();
   __syncthreads();
+  SFL_TRACE_TOTAL(blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0, kTr)
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
@@ -2251,6 +2291,20 @@ extern "C" int sfl_attn_trace_read(unsigned long long* out16) {
   return static_cast<int>(cudaMemcpyToSymbol(g_attn_trace, zero, sizeof(zero)));
 #else
   (void)out16;
+  return -1;
+#endif
+}
+
+// The same for the two backward kernels: 16 entries of the dQ kernel, then 16 of dK/dV.
+extern "C" int sfl_attn_bwd_trace_read(unsigned long long* out32) {
+#ifdef SFL_ATTN_TRACE
+  unsigned long long zero[32] = {};
+  const size_t at = 16 * sizeof(unsigned long long);
+  cudaError_t e = cudaMemcpyFromSymbol(out32, g_attn_trace, sizeof(zero), at);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return static_cast<int>(cudaMemcpyToSymbol(g_attn_trace, zero, sizeof(zero), at));
+#else
+  (void)out32;
   return -1;
 #endif
 }

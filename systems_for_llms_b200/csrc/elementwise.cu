@@ -98,6 +98,43 @@ __global__ void rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __r
   }
 }
 
+// The same with the row held in registers (dim = 128 NCH): every load of the row is in
+// flight at once and x is read a single time.  Same arithmetic, in the same order.
+template <int NCH>
+__global__ void __launch_bounds__(128)
+rmsnorm_fwd_vec_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                       __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int rows,
+                       float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int dim = NCH * 128;
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  if (!SFL_BOUNDS_OK(row >= 0, nullptr)) return;
+  const float* xr = x + static_cast<long>(row) * dim;
+  __nv_bfloat16* yr = y + static_cast<long>(row) * dim;
+  float4 xv[NCH], g[NCH];
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) xv[c] = *reinterpret_cast<const float4*>(xr + c * 128 + lane * 4);
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) g[c] = *reinterpret_cast<const float4*>(w + c * 128 + lane * 4);
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c)
+    ss += xv[c].x * xv[c].x + xv[c].y * xv[c].y + xv[c].z * xv[c].z + xv[c].w * xv[c].w;
+  ss = warp_sum(ss);
+  const float rms = sqrtf(ss / static_cast<float>(dim) + eps);
+  if (lane == 0 && rstd != nullptr) rstd[row] = 1.0f / rms;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    uint2 o;
+    o.x = pack_bf16(xv[c].x / rms * g[c].x, xv[c].y / rms * g[c].y);
+    o.y = pack_bf16(xv[c].z / rms * g[c].z, xv[c].w / rms * g[c].w);
+    *reinterpret_cast<uint2*>(yr + c * 128 + lane * 4) = o;
+  }
+}
+
 constexpr int kNormBwdBlocks = 296;  // two CTAs per SM on a 148-SM part
 constexpr int kNormBwdThreads = 256;
 
@@ -182,6 +219,91 @@ rmsnorm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const float* __rest
   }
 }
 
+// The same with a row shared by two warps (NCH even): each warp holds half as many
+// registers, so two CTAs fit on an SM and twice as many rows are in flight; the two
+// halves of the row's dot product meet in shared memory and are added in a fixed order.
+template <int NCH>
+__global__ void __launch_bounds__(kNormBwdThreads, 2)
+rmsnorm_bwd_pair_kernel(const __nv_bfloat16* __restrict__ dy, const float* __restrict__ x,
+                        const float* __restrict__ w, const float* __restrict__ rstd,
+                        const float* __restrict__ dres_in, float* __restrict__ dx_out,
+                        __nv_bfloat16* __restrict__ dx_bf16, float* __restrict__ dw_partial,
+                        int rows) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int dim = NCH * 128;
+  constexpr int HC = NCH / 2;
+  constexpr int kPairs = kNormBwdThreads / 64;
+  extern __shared__ float dw_smem[];  // [pairs, dim]
+  __shared__ float pair_dot[2][kPairs][2];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int pair = warp >> 1, half = warp & 1;
+  const int col0 = half * HC * 128 + lane * 4;
+  float4 wv[HC], dwv[HC];
+#pragma unroll
+  for (int c = 0; c < HC; ++c) {
+    wv[c] = *reinterpret_cast<const float4*>(w + col0 + c * 128);
+    dwv[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  int parity = 0;
+  for (int row = blockIdx.x * kPairs + pair; row < rows; row += gridDim.x * kPairs, parity ^= 1) {
+    const long off = static_cast<long>(row) * dim + col0;
+    const float inv = rstd[row];
+    float4 xh[HC], g[HC], res[HC];
+    float dot = 0.f;
+#pragma unroll
+    for (int c = 0; c < HC; ++c)
+      res[c] = dres_in != nullptr ? *reinterpret_cast<const float4*>(dres_in + off + c * 128)
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int c = 0; c < HC; ++c) {
+      const float4 xv = *reinterpret_cast<const float4*>(x + off + c * 128);
+      const uint2 dq = *reinterpret_cast<const uint2*>(dy + off + c * 128);
+      const float2 d01 = unpack_bf16(dq.x), d23 = unpack_bf16(dq.y);
+      xh[c] = make_float4(xv.x * inv, xv.y * inv, xv.z * inv, xv.w * inv);
+      g[c] = make_float4(d01.x, d01.y, d23.x, d23.y);
+      dot += g[c].x * wv[c].x * xh[c].x + g[c].y * wv[c].y * xh[c].y +
+             g[c].z * wv[c].z * xh[c].z + g[c].w * wv[c].w * xh[c].w;
+    }
+    dot = warp_sum(dot);
+    if (lane == 0) pair_dot[parity][pair][half] = dot;
+    // the two warps of the pair meet; buffers alternate, so a slot is rewritten only after
+    // both warps have passed the barrier that follows their last read of it
+    asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory");
+    dot = (pair_dot[parity][pair][0] + pair_dot[parity][pair][1]) / static_cast<float>(dim);
+#pragma unroll
+    for (int c = 0; c < HC; ++c) {
+      float4 d;
+      d.x = inv * (g[c].x * wv[c].x - xh[c].x * dot);
+      d.y = inv * (g[c].y * wv[c].y - xh[c].y * dot);
+      d.z = inv * (g[c].z * wv[c].z - xh[c].z * dot);
+      d.w = inv * (g[c].w * wv[c].w - xh[c].w * dot);
+      d.x += res[c].x; d.y += res[c].y; d.z += res[c].z; d.w += res[c].w;
+      *reinterpret_cast<float4*>(dx_out + off + c * 128) = d;
+      if (dx_bf16 != nullptr) {
+        uint2 o;
+        o.x = pack_bf16(d.x, d.y);
+        o.y = pack_bf16(d.z, d.w);
+        *reinterpret_cast<uint2*>(dx_bf16 + off + c * 128) = o;
+      }
+      dwv[c].x += g[c].x * xh[c].x;
+      dwv[c].y += g[c].y * xh[c].y;
+      dwv[c].z += g[c].z * xh[c].z;
+      dwv[c].w += g[c].w * xh[c].w;
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < HC; ++c)
+    *reinterpret_cast<float4*>(dw_smem + static_cast<long>(pair) * dim + col0 + c * 128) = dwv[c];
+  __syncthreads();
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < kPairs; ++k) s += dw_smem[static_cast<long>(k) * dim + i];
+    dw_partial[static_cast<long>(blockIdx.x) * dim + i] = s;
+  }
+}
+
 // Generic fallback for any row width.
 __global__ void __launch_bounds__(kNormBwdThreads)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const float* __restrict__ x,
@@ -224,10 +346,11 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const float* __restrict
   }
 }
 
-// Each CTA folds 32 columns over all partial rows: eight warps take every eighth
-// row (independent loads in flight), then one warp adds the eight sums in a
-// fixed order, so the result does not depend on scheduling.
-constexpr int kDwReduceWarps = 8;
+// Each CTA folds 32 columns over all partial rows: 32 warps take every 32nd row
+// (independent loads in flight: about ten rows per warp for 296 partials, so the whole
+// fold is three round trips to L2), then one warp adds the 32 sums in a fixed order,
+// so the result does not depend on scheduling.
+constexpr int kDwReduceWarps = 32;
 __global__ void __launch_bounds__(32 * kDwReduceWarps)
 rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, int blocks, float* __restrict__ dw,
                          int dim, int accumulate) {
@@ -628,6 +751,19 @@ using namespace sfl;
 extern "C" int sfl_rmsnorm_fwd(const float* x, const float* w, void* y, float* rstd, int rows,
                                int dim, float eps, void* stream) {
   if (rows <= 0 || dim <= 0) return -2;
+  static const bool plain = getenv("SFL_NORM_PLAIN") != nullptr;  // the one-warp-per-row loops
+  if (!plain && dim % 128 == 0 && dim <= 1024) {
+    const int vw = 4;
+#define SFL_NORM_FWD(NCH)                                                                        \
+  case NCH:                                                                                      \
+    return launch_pdl(rmsnorm_fwd_vec_kernel<NCH>, dim3((rows + vw - 1) / vw), dim3(vw * 32), 0, \
+                      SFL_STREAM(stream), x, w, static_cast<__nv_bfloat16*>(y), rstd, rows, eps);
+    switch (dim / 128) {
+      SFL_NORM_FWD(1) SFL_NORM_FWD(2) SFL_NORM_FWD(3) SFL_NORM_FWD(4)
+      SFL_NORM_FWD(5) SFL_NORM_FWD(6) SFL_NORM_FWD(7) SFL_NORM_FWD(8)
+    }
+#undef SFL_NORM_FWD
+  }
   const int warps = 8;
   return launch_pdl(rmsnorm_fwd_kernel, dim3((rows + warps - 1) / warps), dim3(warps * 32), 0,
                     SFL_STREAM(stream), x, w, static_cast<__nv_bfloat16*>(y), rstd, rows, dim, eps);
@@ -659,6 +795,16 @@ extern "C" int sfl_rmsnorm_bwd(const void* dy, const float* x, const float* w, c
   case NCH:                                                                                   \
     return launch_pdl(rmsnorm_bwd_vec_kernel<NCH>, dim3(blocks), dim3(kNormBwdThreads), smem, \
                       st, dyp, x, w, rstd, dres_in, dx_out, dxb, dw_partial, rows);
+  static const bool plain = getenv("SFL_NORM_PLAIN") != nullptr;
+#define SFL_NORM_PAIR(NCH)                                                                     \
+  case NCH:                                                                                    \
+    return launch_pdl(rmsnorm_bwd_pair_kernel<NCH>, dim3(blocks), dim3(kNormBwdThreads),       \
+                      static_cast<size_t>(kNormBwdThreads / 64) * dim * sizeof(float), st, dyp, \
+                      x, w, rstd, dres_in, dx_out, dxb, dw_partial, rows);
+  if (!plain && dim % 256 == 0 && dim <= 1024) {
+    switch (dim / 128) { SFL_NORM_PAIR(2) SFL_NORM_PAIR(4) SFL_NORM_PAIR(6) SFL_NORM_PAIR(8) }
+  }
+#undef SFL_NORM_PAIR
   if (dim % 128 == 0 && dim <= 1024) {
     switch (dim / 128) {
       SFL_NORM_BWD(1) SFL_NORM_BWD(2) SFL_NORM_BWD(3) SFL_NORM_BWD(4)

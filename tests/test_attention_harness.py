@@ -525,7 +525,8 @@ def test_backward_plan_sizes():
 
 
 def test_decode_smoke_plan_is_582_checks_and_reference_handles_empty_rows():
-    assert len(decode_study.VARIANTS) * decode_study.smoke_case_count() == 582
+    assert len(decode_study.REFERENCE_VARIANTS) * decode_study.smoke_case_count() == 582
+    assert len(decode_study.VARIANTS) * decode_study.smoke_case_count() == 873
     torch.manual_seed(0)
     q = torch.randn(2, 4, 8)
     k, v = torch.randn(2, 2, 5, 8), torch.randn(2, 2, 5, 8)
