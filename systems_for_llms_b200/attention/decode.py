@@ -9,8 +9,9 @@ captured in a CUDA graph, and ``lengths`` may be edited in place between calls;
 launch.  Three variants: ``"token"`` and ``"tile"`` are the reference's two softmax
 schedules on the CUDA cores (csrc/decode.cu); ``"mma"`` computes the scores of a GQA
 group and the weighted value sum as tcgen05 matrix products fed by TMA
-(csrc/attention.cu, ``decode_mma_kernel``) - the one that keeps up with HBM when
-several query heads share a KV head.
+(csrc/attention.cu, ``decode_mma2_kernel``: cached tokens are the rows of the score
+tile, the head group its 16 columns) - the one that keeps up with HBM when several
+query heads share a KV head.
 """
 
 from __future__ import annotations
@@ -109,7 +110,7 @@ def prepare(q, k, v, lengths=None, *, splits=1, scale=None, variant="token") -> 
     prepared operations because scratch and output are owned by the object.
     """
     if variant not in VARIANTS:
-        raise ValueError("variant must be 'token', 'tile' or 'mma'")
+        raise ValueError("variant must be one of " + ", ".join(VARIANTS))
     for tensor in (q, k, v):
         if not isinstance(tensor, torch.Tensor) or not tensor.is_cuda:
             raise ValueError("all tensors must be on the same CUDA device")

@@ -1234,41 +1234,30 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
 // ====================================================== decode on tensor cores ====
 // Single-token attention over a KV cache with grouped queries, split over the cache.
-// The scores of one (batch, KV head) are a [query heads of the group] x [cached tokens]
-// matrix product and the output a [heads] x [tokens] x [D] one, so a split of the cache
-// is processed exactly like a query tile of the forward kernel above: K and V tiles of
-// 128 tokens stream in through TMA, S = Q K^T and O += P V run on tcgen05 with the
-// accumulators in tensor memory, P goes back into tensor memory as the A operand.  The
-// "query tile" holds the G <= 8 heads of the group, spread over the four lane quarters
-// (head g sits in row 32 (g mod 4) + g / 4) so that all four softmax warps have rows to
-// work on; its other rows are zero and their results are never read.  Scalar-FMA decode
-// needs about 125 warp instructions per cached token for eight heads at D = 128 and is
-// bound by the issue rate at a quarter of the memory bandwidth; here the arithmetic per
-// token is a handful of instructions and the kernel is bound by the K/V stream.
+// The scores of one (batch, KV head) are a [cached tokens] x [query heads of the group]
+// matrix product and the output a [heads] x [tokens] x [D] one: K and V tiles of 128
+// tokens stream in through TMA, S^T = K Q^T and O += P^T V run on tcgen05 with the
+// accumulators in tensor memory.  Scalar-FMA decode needs about 125 warp instructions per
+// cached token for eight heads at D = 128 and is bound by the issue rate at a quarter of
+// the memory bandwidth; here the arithmetic per token is a handful of instructions and the
+// kernel is bound by the K/V stream.
 //
 // A CTA handles one (batch, KV head, split) and leaves (m, l, u) in the log-2 domain for
 // the merge, which the last CTA of a (batch, KV head) to finish performs (decode.cu has the
 // same protocol).  Partitioning follows the reference (attention_lab/cuda_decode/
 // decode.cu:50-52): split s covers tokens [s chunk, min(length, (s + 1) chunk)) with
 // chunk = ceil(capacity / splits); empty partitions contribute (-inf, 0, 0).
-constexpr int kDecThreads = 192;  // TMA warp, MMA warp, four softmax warps
-
-template <int D>
-struct DecSmem {
-  static constexpr int kTileBytes = kTile * D * 2;
-  static constexpr int kStages = 2;
-  static constexpr int kBytes = kTileBytes * (1 + 2 * kStages) + 1024 + 1024;
-};
-
-struct DecBarriers {
-  uint64_t q_ready;  // 128 arrivals: the query tile is written
-  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
-  uint64_t s_full, s_free, p_ready, pv_done;
-  uint32_t tmem_base;
-  int abort;
-  int is_last;
-};
-
+//
+// The score product has the 128 cached tokens of a tile as its rows and the (padded) head
+// group as its N = 16 columns, so a softmax thread owns one token and touches G <= 8 scores
+// per tile.  (With the head group as the rows of a 128-row query tile every thread owns a
+// row of which all but G are padding and pays 128 exponentials per tile: that layout was
+// built first and measured 15 % slower on every shape.)  The per-head maximum over the tile's tokens is a warp
+// redux.sync on order-preserving integer keys plus one exchange through shared memory; the
+// running maximum is the same in every thread.  P goes to shared memory transposed (heads
+// as rows of a K-major tile of which only 16 rows exist; the product reads 128 and the
+// rows beyond the group produce values nobody reads) and O[heads, D] += P^T V accumulates
+// in tensor memory.
 struct DecParams {
   const void* q;       // [B, Hq, D]
   const int* lengths;  // [B]
@@ -1284,18 +1273,64 @@ struct DecParams {
 
 __device__ __forceinline__ float dec_merge_exp2(float x) { return fast_exp2(x); }
 
+constexpr int kDec2Threads = 192;  // TMA warp, MMA warp, four softmax warps (thread = token)
+
+template <int D>
+struct Dec2Smem {
+  static constexpr int kTileBytes = kTile * D * 2;
+  static constexpr int kStages = D == 64 ? 5 : 3;
+  static constexpr int kQBytes = 16 * D * 2;        // [D / 64 atoms][16 heads][128 B]
+  static constexpr int kPBytes = 2 * 16 * 128;      // one buffer: [2 atoms][16 heads][128 B]
+  // the A operand of P^T V is read as 128 rows: 16 KB past each atom must be mapped, which
+  // the K/V ring behind the P buffers provides
+  static constexpr int kBytes = kQBytes + 2 * kPBytes + 2 * kStages * kTileBytes + 1024 + 1024;
+};
+
+struct Dec2Barriers {
+  uint64_t q_ready;  // 128 arrivals: the query tile is written
+  uint64_t k_full[5], k_empty[5], v_full[5], v_empty[5];
+  uint64_t s_full[2], s_free[2], p_ready[2], pv_done[2];
+  uint32_t tmem_base;
+  int abort;
+  int is_last;
+  alignas(16) int tile_max[2][4][8];  // order-preserving keys of the per-warp maxima, by tile parity
+  alignas(16) float row_sum[4][8];
+};
+
+__device__ __forceinline__ int float_key(float x) {  // signed-integer order == float order
+  const int i = __float_as_int(x);
+  return i ^ ((i >> 31) & 0x7fffffff);
+}
+__device__ __forceinline__ float key_float(int k) {
+  return __int_as_float(k ^ ((k >> 31) & 0x7fffffff));
+}
+__device__ __forceinline__ int warp_max_s32(int v) {
+  int r;
+  asm volatile("redux.sync.max.s32 %0, %1, 0xffffffff;" : "=r"(r) : "r"(v));
+  return r;
+}
+__device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]),
+                 "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+
 template <int D, bool FP16>
-__global__ void __launch_bounds__(kDecThreads, D == 64 ? 1 : 1)
-decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                  const DecParams p) {
-  using L = DecSmem<D>;
+__global__ void __launch_bounds__(kDec2Threads, 1)
+decode_mma2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                   const DecParams p) {
+  using L = Dec2Smem<D>;
+  constexpr int ST = L::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sQ = smem;
-  uint8_t* sK = sQ + L::kTileBytes;
-  uint8_t* sV = sK + L::kStages * L::kTileBytes;
-  DecBarriers* bars = reinterpret_cast<DecBarriers*>(sV + L::kStages * L::kTileBytes);
+  uint8_t* sP = sQ + L::kQBytes;
+  uint8_t* sK = sP + 2 * L::kPBytes;
+  uint8_t* sV = sK + ST * L::kTileBytes;
+  Dec2Barriers* bars = reinterpret_cast<Dec2Barriers*>(sV + ST * L::kTileBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -1308,23 +1343,25 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_ready, 128);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < ST; ++s) {
       mbar_init(&bars->k_full[s], 1);
       mbar_init(&bars->k_empty[s], 1);
       mbar_init(&bars->v_full[s], 1);
       mbar_init(&bars->v_empty[s], 1);
     }
-    mbar_init(&bars->s_full, 1);
-    mbar_init(&bars->s_free, 128);
-    mbar_init(&bars->p_ready, 128);
-    mbar_init(&bars->pv_done, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->s_full[s], 1);
+      mbar_init(&bars->s_free[s], 128);
+      mbar_init(&bars->p_ready[s], 128);
+      mbar_init(&bars->pv_done[s], 1);
+    }
     bars->abort = 0;
     mbar_fence_init();
     prefetch_tensormap(&tmK);
     prefetch_tensormap(&tmV);
   }
-  // 192 + D columns are used; with D = 64 two CTAs can share an SM's tensor memory
-  constexpr uint32_t kTmemCols = D == 64 ? 256 : 512;
+  // columns: two score buffers of 16, then the output [heads, D]
+  constexpr uint32_t kTmemCols = D == 64 ? 128 : 256;
   if (warp == 1) {
     tmem_alloc(&bars->tmem_base, kTmemCols);
     tmem_relinquish();
@@ -1334,15 +1371,14 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
   volatile int* abort = &bars->abort;
-  // tensor memory: scores [0,128), P as 16-bit pairs [128,192), output [192, 192 + D)
-  const uint32_t tS = tmem, tP = tmem + 128, tO = tmem + 192;
+  const uint32_t tO = tmem + 32;
 
   if (warp == 0) {
     // ---------------------------------------------------- TMA producer ----
     if (lane == 0) {
       for (int j = 0; j < n_tiles; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = ((j >> 1) & 1) ^ 1;
+        const int s = j % ST;
+        const uint32_t ph = ((j / ST) & 1) ^ 1;
         const int row0 = begin + j * kTile;
         if (!bounded_wait(&bars->k_empty[s], ph, abort, p.status, kStatusTimeoutEmpty)) break;
         mbar_expect_tx(&bars->k_full[s], L::kTileBytes);
@@ -1355,162 +1391,205 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------------------------------ MMA issuer ----
     if (n_tiles > 0) {
-      constexpr uint32_t idesc_qk = idesc_16bit(FP16, kTile, kTile, false, false);
+      constexpr uint32_t idesc_qk = idesc_16bit(FP16, kTile, 16, false, false);
       constexpr uint32_t idesc_pv = idesc_16bit(FP16, kTile, D, false, true);
-      const uint64_t q_desc0 = desc_kmajor(smem_u32(sQ), kTile, 0);
+      const uint64_t q_desc0 = desc_kmajor(smem_u32(sQ), 16, 0);
       const uint64_t k_desc0 = desc_kmajor(smem_u32(sK), kTile, 0);
+      const uint64_t p_desc0 = desc_kmajor(smem_u32(sP), 16, 0);
       const uint64_t v_desc0 = desc_mnmajor(smem_u32(sV), 0);
-      auto issue_qk = [&](int j) -> bool {  // scores of tile j
-        const int s = j & 1;
-        if (j > 0 &&
-            !bounded_wait(&bars->s_free, (j - 1) & 1, abort, p.status, kStatusTimeoutTmemEmpty))
-          return false;
-        if (!bounded_wait(&bars->k_full[s], (j >> 1) & 1, abort, p.status, kStatusTimeoutFull))
-          return false;
-        tc_fence_after();
-        const uint64_t kd = umma_desc_advance(k_desc0, s * L::kTileBytes);
-        if (elect_one()) {
-#pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint32_t off = (k >> 2) * (kTile * 128) + (k & 3) * 32;
-            umma_bf16_ss(tS, umma_desc_advance(q_desc0, off), umma_desc_advance(kd, off), idesc_qk,
-                         k != 0);
-          }
-          umma_commit(&bars->s_full);
-        }
-        __syncwarp();
-        return true;
-      };
       bool ok = bounded_wait(&bars->q_ready, 0, abort, p.status, kStatusTimeoutFull);
-      if (ok) ok = issue_qk(0);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j + 1 < n_tiles) {
-          ok = issue_qk(j + 1);
-          if (!ok) break;
-        }
-        const int s = j & 1;
-        if (!bounded_wait(&bars->p_ready, j & 1, abort, p.status, kStatusTimeoutTmemFull) ||
-            !bounded_wait(&bars->v_full[s], (j >> 1) & 1, abort, p.status, kStatusTimeoutFull)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const uint64_t vd = umma_desc_advance(v_desc0, s * L::kTileBytes);
-        if (elect_one()) {
+      for (int j = 0; j <= n_tiles && ok; ++j) {
+        if (j < n_tiles) {  // S^T(j) = K(j) Q^T into score buffer j & 1
+          const int s = j % ST, sb = j & 1;
+          if (j >= 2 && !bounded_wait(&bars->s_free[sb], ((j >> 1) - 1) & 1, abort, p.status,
+                                      kStatusTimeoutTmemEmpty)) {
+            ok = false;
+            break;
+          }
+          if (!bounded_wait(&bars->k_full[s], (j / ST) & 1, abort, p.status, kStatusTimeoutFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t kd = umma_desc_advance(k_desc0, s * L::kTileBytes);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < kTile / 16; ++k)
-            umma_bf16_ts(tO, tP + k * 8, umma_desc_advance(vd, k * 2048), idesc_pv, (j | k) != 0);
-          umma_commit(&bars->pv_done);
+            for (int k = 0; k < D / 16; ++k)
+              umma_bf16_ss(tmem + sb * 16,
+                           umma_desc_advance(kd, (k >> 2) * (kTile * 128) + (k & 3) * 32),
+                           umma_desc_advance(q_desc0, (k >> 2) * (16 * 128) + (k & 3) * 32), idesc_qk,
+                           k != 0);
+            umma_commit(&bars->s_full[sb]);
+            umma_commit(&bars->k_empty[s]);
+          }
+          __syncwarp();
         }
-        __syncwarp();
+        if (j >= 1) {  // O += P^T(j - 1) V(j - 1)
+          const int i = j - 1, s = i % ST, pb = i & 1;
+          if (!bounded_wait(&bars->p_ready[pb], (i >> 1) & 1, abort, p.status, kStatusTimeoutTmemFull) ||
+              !bounded_wait(&bars->v_full[s], (i / ST) & 1, abort, p.status, kStatusTimeoutFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t pd = umma_desc_advance(p_desc0, pb * L::kPBytes);
+          const uint64_t vd = umma_desc_advance(v_desc0, s * L::kTileBytes);
+          if (elect_one()) {
+#pragma unroll
+            for (int k = 0; k < kTile / 16; ++k)
+              umma_bf16_ss(tO, umma_desc_advance(pd, (k >> 2) * (16 * 128) + (k & 3) * 32),
+                           umma_desc_advance(vd, k * 2048), idesc_pv, (i | k) != 0);
+            umma_commit(&bars->pv_done[pb]);
+            umma_commit(&bars->v_empty[s]);
+          }
+          __syncwarp();
+        }
       }
     }
   } else {
     // ------------------------------------------------ softmax + partials ----
     const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;
-    // head of the group held by this row, or -1 for a padding row
-    const int g = lane < 2 && (lane * 4 + quarter) < p.G ? lane * 4 + quarter : -1;
-    const bool leader = quarter == 0 && lane == 0;
+    const int row = quarter * 32 + lane;  // token of the tile
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const float scale_log2 = p.scale * kLog2e;
-    const long head = static_cast<long>(b) * p.Hq + static_cast<long>(kvh) * p.G + (g < 0 ? 0 : g);
-    // The query tile: this thread's row in the K-major swizzled layout (zero when padding).
-    {
-      const uint8_t* qrow = static_cast<const uint8_t*>(p.q) + head * D * 2;
-#pragma unroll
-      for (int half = 0; half < D / 64; ++half) {
-        uint8_t* base = sQ + half * (kTile * 128) + row * 128;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint4 v = g >= 0 ? *reinterpret_cast<const uint4*>(qrow + half * 128 + c * 16)
-                                 : make_uint4(0, 0, 0, 0);
-          *reinterpret_cast<uint4*>(base + ((c ^ (row & 7)) << 4)) = v;
-        }
-      }
-      fence_proxy_async_smem();
-      mbar_arrive(&bars->q_ready);
+    const long head0 = static_cast<long>(b) * p.Hq + static_cast<long>(kvh) * p.G;
+    // The query tile [16 heads][D], K-major and swizzled; rows beyond the group are zero.
+    for (int idx = threadIdx.x - 64; idx < 16 * (D / 8); idx += 128) {
+      const int g = idx / (D / 8), c = idx % (D / 8);  // head, 16-byte chunk of its row
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (g < p.G)
+        v = *reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.q) +
+                                            (head0 + g) * D * 2 + c * 16);
+      *reinterpret_cast<uint4*>(sQ + (c >> 3) * (16 * 128) + g * 128 + (((c & 7) ^ (g & 7)) << 4)) = v;
     }
-    float m_used = -INFINITY;
-    float l = 0.f;
+    fence_proxy_async_smem();
+    mbar_arrive(&bars->q_ready);
+
+    float m[8], l_part[8];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      m[g] = -INFINITY;
+      l_part[g] = 0.f;
+    }
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
-      if (!bounded_wait(&bars->s_full, j & 1, abort, p.status, kStatusTimeoutTmemFull)) {
+      const int sb = j & 1;
+      if (!bounded_wait(&bars->s_full[sb], (j >> 1) & 1, abort, p.status, kStatusTimeoutTmemFull)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      if (leader) mbar_arrive(&bars->k_empty[j & 1]);
-      float x[kTile];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32f(tS + lane_base + c * 32, x + c * 32);
+      uint32_t raw[8];
+      tmem_ld_32x8(tmem + lane_base + sb * 16, raw);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(&bars->s_free);
-      const int valid = end - (begin + j * kTile);  // tokens of this tile inside the partition
-      if (valid < kTile) {
+      mbar_arrive(&bars->s_free[sb]);
+      const bool live = begin + j * kTile + row < end;  // token inside the partition
+      float x[8];
+      int key[8];
 #pragma unroll
-        for (int c = 0; c < kTile; ++c) x[c] = c < valid ? x[c] : -INFINITY;
+      for (int g = 0; g < 8; ++g) {
+        x[g] = live && g < p.G ? __uint_as_float(raw[g]) * scale_log2 : -INFINITY;
+        key[g] = warp_max_s32(float_key(x[g]));
       }
-      float mx8[8];
+      if (lane == 0) {
+        *reinterpret_cast<int4*>(&bars->tile_max[sb][quarter][0]) = make_int4(key[0], key[1], key[2], key[3]);
+        *reinterpret_cast<int4*>(&bars->tile_max[sb][quarter][4]) = make_int4(key[4], key[5], key[6], key[7]);
+      }
+      named_barrier_128();
+      bool grow = false;
+      float alpha[8];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) mx8[c] = fmaxf(x[2 * c], x[2 * c + 1]);
-#pragma unroll
-      for (int c = 16; c < kTile; c += 2)
-        mx8[(c >> 1) & 7] = fmax3(mx8[(c >> 1) & 7], x[c], x[c + 1]);
-      float mx = fmax3(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(mx8[3], mx8[4], mx8[5]),
-                       fmaxf(mx8[6], mx8[7]));
-      mx *= scale_log2;
-      if (j > 0) {
-        if (!bounded_wait(&bars->pv_done, (j - 1) & 1, abort, p.status, kStatusTimeoutTmemFull)) {
-          ok = false;
-          break;
+      for (int g = 0; g < 8; ++g) {
+        int k = bars->tile_max[sb][0][g];
+        k = max(k, bars->tile_max[sb][1][g]);
+        k = max(k, bars->tile_max[sb][2][g]);
+        k = max(k, bars->tile_max[sb][3][g]);
+        const float mx = key_float(k);
+        alpha[g] = 1.0f;
+        if (mx > m[g] + 8.0f) {  // a stale maximum is kept until it is off by 2^8
+          alpha[g] = fast_exp2(m[g] - mx);  // 0 for the first tile
+          m[g] = mx;
+          grow = true;
         }
-        tc_fence_after();
-        if (leader) mbar_arrive(&bars->v_empty[(j - 1) & 1]);
       }
-      const bool grow = mx > m_used + 8.0f;
-      if (__any_sync(0xffffffffu, grow)) {
-        if (j > 0) {
-          const float alpha = grow ? fast_exp2(m_used - mx) : 1.0f;
+      // the P buffer of this parity was last read by the product of tile j - 2
+      if (j >= 2 && !bounded_wait(&bars->pv_done[sb], ((j >> 1) - 1) & 1, abort, p.status,
+                                  kStatusTimeoutTmemFull)) {
+        ok = false;
+        break;
+      }
+      if (grow) {  // the same decision in every thread: the maxima are CTA-wide
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            float o[32];
-            tmem_ld_32x32f(tO + lane_base + c * 32, o);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] *= alpha;
-            tmem_st_32x32(tO + lane_base + c * 32, o);
+        for (int g = 0; g < 8; ++g) l_part[g] *= alpha[g];
+        if (j >= 1) {
+          if (!bounded_wait(&bars->pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort, p.status,
+                            kStatusTimeoutTmemFull)) {
+            ok = false;
+            break;
           }
-          l *= alpha;
-        }
-        if (grow) m_used = mx;
-      }
-      const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+          tc_fence_after();
+          if (quarter == 0) {  // output rows (heads) live in lanes 0 .. G-1
+            float a = 1.0f;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t packed[16];
+            for (int g = 0; g < 8; ++g) a = lane == g ? alpha[g] : a;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float p0 = fast_exp2(fmaf(x[c * 32 + i], scale_log2, neg_m));
-          const float p1 = fast_exp2(fmaf(x[c * 32 + i + 1], scale_log2, neg_m));
-          sum4[(i >> 1) & 3] += p0 + p1;
-          packed[i >> 1] = pack2<FP16>(p0, p1);
+            for (int c = 0; c < D / 32; ++c) {
+              float o[32];
+              tmem_ld_32x32f(tO + c * 32, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] *= a;
+              tmem_st_32x32(tO + c * 32, o);
+            }
+            tmem_st_wait();
+          }
         }
-        tmem_st_32x16(tP + lane_base + c * 16, packed);
       }
-      tmem_st_wait();
-      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      // P^T: head g is row g of a K-major tile whose 128 columns are this tile's tokens
+      uint8_t* pt = sP + sb * L::kPBytes + (row >> 6) * (16 * 128);
+      const int chunk16 = (row & 63) >> 3, within = (row & 7) * 2;
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        const float neg_m = m[g] == -INFINITY ? 0.f : -m[g];
+        const float pr = fast_exp2(x[g] + neg_m);
+        l_part[g] += pr;
+        uint16_t bits;
+        if constexpr (FP16)
+          bits = __half_as_ushort(__float2half_rn(pr));
+        else
+          bits = __bfloat16_as_ushort(__float2bfloat16_rn(pr));
+        *reinterpret_cast<uint16_t*>(pt + g * 128 + ((chunk16 ^ g) << 4) + within) = bits;
+      }
+      fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(&bars->p_ready);
+      mbar_arrive(&bars->p_ready[sb]);
     }
     if (ok && n_tiles > 0)
-      ok = bounded_wait(&bars->pv_done, (n_tiles - 1) & 1, abort, p.status, kStatusTimeoutTmemFull);
-    if (ok) {
+      ok = bounded_wait(&bars->pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort, p.status,
+                        kStatusTimeoutTmemFull);
+    // row sums: lanes, then the four warps in a fixed order
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      float v = l_part[g];
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+      if (lane == 0) bars->row_sum[quarter][g] = v;
+    }
+    named_barrier_128();
+    if (ok && quarter == 0) {
       // tcgen05.ld is a warp-wide instruction: every lane loads its row, only the lanes
       // that hold a head store it
       tc_fence_after();
+      const int g = lane;
+      const bool real = g < p.G;
+      float l = 0.f, mg = -INFINITY;
+      if (g < 8) {
+        l = (bars->row_sum[0][g] + bars->row_sum[1][g]) + (bars->row_sum[2][g] + bars->row_sum[3][g]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mg = g == i ? m[i] : mg;
+      }
+      const long head = head0 + (real ? g : 0);
       const long slot = head * p.splits + split;
       const bool direct = p.splits == 1;
       const float inv = l > 0.f ? 1.0f / l : 0.f;
@@ -1518,13 +1597,13 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       for (int c = 0; c < D / 32; ++c) {
         float o[32];
         if (n_tiles > 0) {
-          tmem_ld_32x32f(tO + lane_base + c * 32, o);
+          tmem_ld_32x32f(tO + c * 32, o);
           tmem_ld_wait();
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = 0.f;
         }
-        if (g < 0) continue;
+        if (!real) continue;
         if (direct) {
           uint8_t* orow = static_cast<uint8_t*>(p.out) + head * D * 2;
 #pragma unroll
@@ -1544,8 +1623,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
                 make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
         }
       }
-      if (!direct && g >= 0) {
-        p.part_m[slot] = l > 0.f ? m_used : -INFINITY;
+      if (!direct && real) {
+        p.part_m[slot] = l > 0.f ? mg : -INFINITY;
         p.part_l[slot] = l;
       }
     }
@@ -2157,8 +2236,9 @@ extern "C" int sfl_attn_fwd(const SflAttnTensor* q, const SflAttnTensor* k, cons
                                stream_);
 }
 
-// pipeline: 0 = default (two work streams per CTA with P in tensor memory for head dimension
-// 64, one stream for 128; SFL_ATTN_FWD=1|2|3 overrides the default for A/B runs), 1 = one
+// pipeline: 0 = default (for head dimension 64 two work streams per CTA with P in tensor
+// memory, unless the pairs would not fill the GPU and rows are long; one stream for 128;
+// SFL_ATTN_FWD=1|2|3 overrides the default for A/B runs), 1 = one
 // stream per CTA, 2 = two streams, P in tensor memory, 3 = two streams, P in shared memory.
 // Head dimension 128 always runs the one-stream kernel.
 extern "C" int sfl_attn_fwd_pipeline(const SflAttnTensor* q, const SflAttnTensor* k,
@@ -2180,12 +2260,21 @@ extern "C" int sfl_attn_fwd_pipeline(const SflAttnTensor* q, const SflAttnTensor
   p.o = o->ptr; p.o_sb = o->stride_b; p.o_sh = o->stride_h; p.o_st = o->stride_t;
   p.lse = lse; p.is_fp16 = is_fp16; p.status = status;
   const int items = ((N + kTile - 1) / kTile) * B * H;
-  static const int default_variant = [] {
+  static const int env_variant = [] {
     const char* v = getenv("SFL_ATTN_FWD");
-    const int chosen = v == nullptr ? 2 : atoi(v);
-    return chosen >= 1 && chosen <= 3 ? chosen : 2;
+    const int chosen = v == nullptr ? 0 : atoi(v);
+    return chosen >= 1 && chosen <= 3 ? chosen : 0;
   }();
-  const int variant = pipeline != 0 ? pipeline : default_variant;
+  int variant = pipeline != 0 ? pipeline : env_variant;
+  if (variant == 0) {
+    // Two streams per CTA halve the number of work items.  When the pairs no longer fill
+    // the GPU and the rows are long (an unbounded causal mask: the heaviest pair is twice
+    // the average), one query tile per CTA balances better - 1.49x at B1 H8 N4096.
+    variant = 2;
+    const int q_tiles = (N + kTile - 1) / kTile;
+    const bool long_rows = mask->mode == 1 && mask->window_left < 0 && q_tiles >= 16;
+    if (long_rows && (items + 1) / 2 <= attn_sm_count()) variant = 1;
+  }
   if (D == 64 && variant != 1) {
     const int slots = (items + 1) / 2;
     dim3 grid2(slots < attn_sm_count() ? slots : attn_sm_count());
@@ -2319,9 +2408,9 @@ extern "C" int sfl_attn_stamps_read(unsigned long long* out64) {
 #endif
 }
 
-// Tensor-core split-KV decode (see decode_mma_kernel).  Same contract as sfl_decode:
-// q [B, Hq, D], k / v [B, Hkv, N, D] contiguous, lengths [B], scratch for splits > 1,
-// counters zero between launches; Hq / Hkv in {1, 2, 4, 8}; D in {64, 128}.
+// Tensor-core split-KV decode (decode_mma2_kernel).  Same contract as sfl_decode: q
+// [B, Hq, D], k / v [B, Hkv, N, D] contiguous, lengths [B], scratch for splits > 1, counters
+// zero between launches; Hq / Hkv in {1, 2, 4, 8}; D in {64, 128}.
 extern "C" int sfl_decode_mma(const void* q, const void* k, const void* v, const int* lengths,
                               float* part_m, float* part_l, float* part_u, int* counters,
                               void* out, int B, int Hq, int Hkv, int N, int D, int splits,
@@ -2351,12 +2440,12 @@ extern "C" int sfl_decode_mma(const void* q, const void* k, const void* v, const
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.N = N; p.splits = splits; p.G = G;
   p.scale = scale; p.status = status;
   dim3 grid(B, Hkv, splits);
-#define SFL_DEC(D_, F_)                                                                  \
-  {                                                                                      \
-    auto kern = decode_mma_kernel<D_, F_>;                                               \
-    int rc = set_smem(kern, DecSmem<D_>::kBytes);                                        \
-    if (rc) return rc;                                                                   \
-    kern<<<grid, kDecThreads, DecSmem<D_>::kBytes, stream>>>(tk, tv, p);                 \
+#define SFL_DEC(D_, F_)                                                                \
+  {                                                                                    \
+    auto kern = decode_mma2_kernel<D_, F_>;                                            \
+    int rc = set_smem(kern, Dec2Smem<D_>::kBytes);                                     \
+    if (rc) return rc;                                                                 \
+    kern<<<grid, kDec2Threads, Dec2Smem<D_>::kBytes, stream>>>(tk, tv, p);             \
   }
   if (D == 64) { if (is_fp16) SFL_DEC(64, true) else SFL_DEC(64, false) }
   else { if (is_fp16) SFL_DEC(128, true) else SFL_DEC(128, false) }

@@ -174,10 +174,9 @@ int sfl_decode(const void* q, const void* k, const void* v, const int* lengths, 
                float* part_l, float* part_u, int* counters, void* out, int B, int Hq, int Hkv,
                int N, int D, int splits, float scale, int tile_variant, int is_fp16, void* stream);
 
-/* The same split-KV decode on the tensor cores (csrc/attention.cu, decode_mma_kernel): the
- * heads of a GQA group form the rows of a 128-row query tile, K / V tiles of 128 cached
- * tokens stream in through TMA, scores and P V are tcgen05 products with accumulators in
- * tensor memory.  Same arguments, scratch layout and partitioning as sfl_decode, plus the
+/* The same split-KV decode on the tensor cores (csrc/attention.cu, decode_mma2_kernel): K / V
+ * tiles of 128 cached tokens stream in through TMA; the scores are a [tokens] x [head group]
+ * tcgen05 product, P^T V accumulates in tensor memory.  Same arguments, scratch layout and partitioning as sfl_decode, plus the
  * status word for its bounded waits; k and v must be 16-byte aligned. */
 int sfl_decode_mma(const void* q, const void* k, const void* v, const int* lengths, float* part_m,
                    float* part_l, float* part_u, int* counters, void* out, int B, int Hq, int Hkv,

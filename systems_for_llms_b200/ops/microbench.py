@@ -6,6 +6,9 @@
     python -m systems_for_llms_b200.ops.microbench step        # per-kernel table of one step
     python -m systems_for_llms_b200.ops.microbench once NAME   # a few launches of one op
     python -m systems_for_llms_b200.ops.microbench mma         # tcgen05.mma issue-rate test
+    SFL_LIBRARY=/tmp/libsfl_trace.so python -m systems_for_llms_b200.ops.microbench \
+        attention-phases                                       # phase timers, needs a library built with
+                                                               # ops.build -DSFL_ATTN_TRACE --output /tmp/libsfl_trace.so
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
         -m systems_for_llms_b200.ops.microbench tp             # GEMM + all-reduce, one kernel vs two
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
@@ -420,10 +423,81 @@ def mma_issue_rate() -> str:
                               timeout=120).stdout
 
 
+def attention_phases(batch: int = 8, heads: int = 16, length: int = 4096, dim: int = 64,
+                     repeats: int = 5) -> str:
+    """Phase timers of the attention kernels (cycles of one traced CTA, per tile).
+
+    Needs a library built with ``-DSFL_ATTN_TRACE`` (``SFL_LIBRARY`` points at it); the
+    ordinary build has no timers and the readers return -1.
+    """
+    import ctypes
+
+    from ..attention import flash, masks
+    from . import lib as L
+    handle = L.lib()
+    q, k, v, d_out = (torch.randn(batch, heads, length, dim, device="cuda").bfloat16()
+                      for _ in range(4))
+    out, lse = torch.empty_like(q), torch.empty(batch, heads, length, device="cuda")
+    dq, dk, dv = (torch.empty_like(q) for _ in range(3))
+    mask = flash.prepare_mask(q, None, masks.MaskSpec(causal=True), None, "interval")
+    scale = dim ** -0.5
+
+    def forward():
+        flash.flash_fwd(q, k, v, out, lse, mask, scale)
+
+    def backward():
+        flash.flash_bwd(q, k, v, out, d_out, lse, dq, dk, dv, mask, scale)
+
+    for _ in range(2):
+        forward()
+        backward()
+    torch.cuda.synchronize()
+    fwd, bwd = (ctypes.c_ulonglong * 16)(), (ctypes.c_ulonglong * 32)()
+    if handle.sfl_attn_trace_read(fwd) != 0 or handle.sfl_attn_bwd_trace_read(bwd) != 0:
+        raise SystemExit("this library has no phase timers: build one with "
+                         "python -m systems_for_llms_b200.ops.build -DSFL_ATTN_TRACE --output PATH "
+                         "and point SFL_LIBRARY at it")
+    lines = []
+    pairs = batch * heads * (length // 128) * (length // 128 + 1) / 2
+    for name, call, reader, buffer in (("forward", forward, handle.sfl_attn_trace_read, fwd),
+                                       ("backward", backward, handle.sfl_attn_bwd_trace_read, bwd)):
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(repeats):
+            call()
+        end.record()
+        torch.cuda.synchronize()
+        ms = begin.elapsed_time(end) / repeats
+        reader(buffer)
+        lines.append(f"{name}: B{batch} H{heads} N{length} D{dim} causal, {ms:.3f} ms per call, "
+                     f"{ms * 1e6 * 148 / pairs:.0f} ns per 128 x 128 tile and SM")
+        if name == "forward":
+            t = [x / repeats for x in buffer]
+            tiles, products = max(t[5], 1), max(t[12], 1)
+            lines.append(f"  softmax warp, per tile: wait scores {t[0] / tiles:.0f}, load {t[1] / tiles:.0f}, "
+                         f"maximum {t[2] / tiles:.0f}, wait P V {t[6] / tiles:.0f}, exponentials + store "
+                         f"{t[3] / tiles:.0f} cycles ({tiles:.0f} tiles)")
+            lines.append(f"  MMA warp, per tile: wait P / V {t[8] / products:.0f}, issue P V "
+                         f"{t[9] / products:.0f}, wait K / free scores {t[10] / products:.0f}, issue Q K "
+                         f"{t[11] / products:.0f} cycles")
+            continue
+        for kernel, base in (("dQ kernel", 0), ("dK/dV kernel", 16)):
+            t = [x / repeats for x in buffer[base:base + 16]]
+            tiles, halves = max(t[5], 1), max(t[12], 1)
+            lines.append(f"  {kernel}, compute warpgroup 0, per tile: set-up {t[0] / tiles:.0f}, wait scores "
+                         f"{t[1] / tiles:.0f}, load S and dP {t[3] / tiles:.0f}, exponentials + dS + store "
+                         f"{t[4] / tiles:.0f}, publish {t[2] / tiles:.0f} cycles ({tiles:.0f} tiles)")
+            lines.append(f"  {kernel}, MMA warp, per 64-column half: wait P / dS {t[9] / halves:.0f}, issue "
+                         f"accumulation {t[10] / halves:.0f}, wait tile + issue scores {t[8] / halves:.0f} "
+                         f"cycles; SM clock {t[13] / max(t[15], 1):.2f} GHz")
+    return "\n".join(lines) + "\n"
+
+
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__,
                                      formatter_class=argparse.RawDescriptionHelpFormatter)
-    parser.add_argument("what", choices=[*SUITES, "step", "once", "mma", "tp", "comm"])
+    parser.add_argument("what", choices=[*SUITES, "step", "once", "mma", "tp", "comm",
+                                         "attention-phases"])
     parser.add_argument("name", nargs="?", help="operation for 'once' (e.g. w13_swiglu, attn_bwd)")
     parser.add_argument("--repeat", type=int, default=3)
     parser.add_argument("--json", action="store_true")
@@ -432,6 +506,9 @@ def main() -> None:
         raise SystemExit("a CUDA GPU is required")
     if args.what == "mma":
         print(mma_issue_rate(), end="")
+        return
+    if args.what == "attention-phases":
+        print(attention_phases(), end="")
         return
     if args.what == "comm":
         table = collective_table()

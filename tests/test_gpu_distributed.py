@@ -135,7 +135,10 @@ def test_wider_groups_match_single(tmp_path, tmp_path_factory, world, mode, extr
     need(world)
     reference = single_run(tmp_path_factory, "wide")
     micro = "1" if mode != "tp" else "2"
-    run = launch(tmp_path, "case", mode, world, WIDE, ["--microbatch-size", micro, *extra])
+    # tensor parallelism here stays on GEMM + reduction kernel; the fused form has its own test
+    env = {"SFL_TP_FUSE_WIDE": "0"} if mode == "tp" else None
+    run = launch(tmp_path, "case", mode, world, WIDE, ["--microbatch-size", micro, *extra],
+                 env_extra=env)
     assert_same_training(run, reference, update_tolerance=UPDATE_TOLERANCE.get(mode, 5e-2))
     assert run["meta"]["execution_path"] == "sm_100a fused engine"
     if mode in ("zero1", "fsdp"):
@@ -161,8 +164,7 @@ def test_tensor_parallel_fused_owned_tiles_match_single(tmp_path, tmp_path_facto
     """More than two ranks: the owned-tile form of the fused GEMM + all-reduce."""
     need(world)
     reference = single_run(tmp_path_factory, "wide")
-    run = launch(tmp_path, "tp", "tp", world, WIDE, ["--microbatch-size", "2"],
-                 env_extra={"SFL_TP_FUSE_WIDE": "1"})
+    run = launch(tmp_path, "tp", "tp", world, WIDE, ["--microbatch-size", "2"])
     assert run["meta"]["tensor_parallel_reduction"].startswith("inside the GEMM kernels")
     assert_same_training(run, reference, update_tolerance=UPDATE_TOLERANCE["tp"])
 
