@@ -50,7 +50,9 @@ __device__ __forceinline__ void background(uint32_t tmem, const uint8_t* smem, v
   if (sink == 0x12345678u) *stop = 2;
 }
 
-template <int N, int MODE, int BG = 0>  // MODE 0 lane-0 branch, 1 elected lane of a converged warp, 2 = 1 + A in TMEM
+// MODE 0 lane-0 branch, 1 elected lane of a converged warp, 2 = 1 + A in TMEM; MODE 3 / 4 are
+// 1 / 2 with the B operand MN-major (N contiguous, as the V tile of an attention P V product)
+template <int N, int MODE, int BG = 0>
 __global__ void __launch_bounds__(384, 1) bench(long long* out, int iters, int two) {
   __shared__ int stop_flag;
   if (threadIdx.x == 0) stop_flag = 0;
@@ -64,7 +66,8 @@ __global__ void __launch_bounds__(384, 1) bench(long long* out, int iters, int t
   fence_proxy_async_smem();
   tc_fence_before(); __syncthreads(); tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  constexpr uint32_t idesc = umma_idesc_bf16(128, N, false, false);
+  constexpr bool kBmn = MODE >= 3;
+  constexpr uint32_t idesc = umma_idesc_bf16(128, N, false, kBmn);
   if (MODE == 0) {
     if (lane == 0 && (warp == 0 || (two && warp == 1))) {
       const uint64_t a = umma_smem_desc(smem_u32(smem), 16, 1024);
@@ -85,17 +88,20 @@ __global__ void __launch_bounds__(384, 1) bench(long long* out, int iters, int t
     background<BG>(tmem, smem, &stop_flag);
   } else if (warp == 0 || (two && warp == 1)) {
     const uint64_t a = umma_smem_desc(smem_u32(smem), 16, 1024);
-    const uint64_t b = umma_smem_desc(smem_u32(smem) + 16384, 16, 1024);
+    // MN-major B: 16 reduction rows of 128 B per step (2 KB apart), 64-wide N blocks 16 KB apart
+    const uint64_t b = kBmn ? umma_smem_desc(smem_u32(smem) + 16384, 16384, 1024)
+                            : umma_smem_desc(smem_u32(smem) + 16384, 16, 1024);
+    constexpr int kBStep = kBmn ? 2048 : 32;
     const uint32_t acc = tmem + warp * 256, a_tmem = tmem + warp * 256 + 192;
     long long t0 = clock64();
     for (int i = 0; i < iters; ++i) {
       if (elect_one()) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          if (MODE == 2)
-            umma_bf16_ts(acc, a_tmem + k * 8, umma_desc_advance(b, k * 32), idesc, (i | k) != 0);
+          if (MODE == 2 || MODE == 4)
+            umma_bf16_ts(acc, a_tmem + k * 8, umma_desc_advance(b, k * kBStep), idesc, (i | k) != 0);
           else
-            umma_bf16_ss(acc, umma_desc_advance(a, k * 32), umma_desc_advance(b, k * 32), idesc, (i | k) != 0);
+            umma_bf16_ss(acc, umma_desc_advance(a, k * 32), umma_desc_advance(b, k * kBStep), idesc, (i | k) != 0);
         }
       }
       __syncwarp();
@@ -122,7 +128,8 @@ template <int N, int MODE = 0, int BG = 0> void run(int two) {
   long long h[4]; cudaMemcpy(h, d, 32, cudaMemcpyDeviceToHost);
   cudaError_t e = cudaDeviceSynchronize();
   printf("%s%s N=%3d threads=%d: issue %.1f cyc/MMA, complete %.1f cyc/MMA (thread1: %.1f / %.1f) %s\n",
-         MODE == 0 ? "lane-0 branch " : MODE == 1 ? "elected lane  " : "elected, A TMEM",
+         MODE == 0 ? "lane-0 branch " : MODE == 1 ? "elected lane  " : MODE == 2 ? "elected, A TMEM"
+         : MODE == 3 ? "elected, B MN-major" : "elected, A TMEM, B MN-major",
          BG == 0 ? "" : BG == 1 ? " + 8 warps tcgen05.ld" : BG == 2 ? " + 8 warps tcgen05.ld/st" : " + 8 warps ld.shared", N, two + 1,
          h[0] / (4.0 * iters), h[1] / (4.0 * iters), h[2] / (4.0 * iters), h[3] / (4.0 * iters), cudaGetErrorString(e));
   cudaFree(d);
@@ -136,5 +143,6 @@ int main() {
   run<64, 1, 1>(0); run<64, 1, 2>(0); run<64, 1, 3>(0);
   run<64, 2, 1>(0); run<64, 2, 2>(0); run<64, 2, 3>(0);
   run<128, 1, 2>(0);
+  run<64, 3>(0); run<64, 4>(0); run<128, 3>(0); run<128, 4>(0);
   return 0;
 }
