@@ -768,8 +768,8 @@ __device__ __forceinline__ void named_barrier_slot(int slot) {
 // [11] issuing a score product, [12] tiles.
 // Backward (sfl_attn_bwd_trace_read; 16 entries for the dQ kernel, then 16 for the dK/dV
 // kernel; CTA (0, 0), the heaviest one under a causal mask): compute warp 2 - [0] tile set-up,
-// [1] waiting for a score half, [2] waiting for the P / dS half to be free, [3] loading
-// scores and dP, [4] exponentials, dS and the shared-memory stores, [5] halves, [6] epilogue;
+// [1] waiting for a score half, [3] loading scores and dP, [4] exponentials, dS and the stores
+// to tensor memory, [2] waiting for those stores and publishing, [5] halves, [6] epilogue;
 // MMA warp - [8] waiting for the streamed tile and issuing scores, [9] waiting for P / dS,
 // [10] issuing the accumulations, [12] halves; [13] cycles and [15] nanoseconds in the kernel;
 // with -DSFL_ATTN_TRACE_SERIAL the MMA warp also waits for each batch it issued and adds up
