@@ -22,7 +22,7 @@ N x N score matrix the mask keeps; "dense-causal equivalent" uses density 0.5
 whatever the mask keeps, i.e. it is the rate a dense-causal kernel would need to
 finish in the same time.
 
-    python -m systems_for_llms_b200.attention.config5 --output gpurun_out/config5.json
+    python -m systems_for_llms_b200.attention.config5 --output config5.json
 """
 
 from __future__ import annotations
