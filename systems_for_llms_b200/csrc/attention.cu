@@ -1736,6 +1736,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA,  // K (kv-owned) or 
 
   SFL_TRACE_BEGIN()
   constexpr int kTr = KV_OWNED ? 32 : 16;  // base of this kernel's phase timers
+  (void)kTr;  // referenced only by the timers
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_tiles = (p.N + kTile - 1) / kTile;
   const int own_tile = KV_OWNED ? blockIdx.x : num_tiles - 1 - blockIdx.x;
