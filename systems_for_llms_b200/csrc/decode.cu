@@ -18,6 +18,7 @@
 // scores are scaled after the dot product, zero-length rows return zeros,
 // "token" rescales the running state after every token and "tile" once per
 // group of tokens.
+#include <atomic>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -352,7 +353,9 @@ static __device__ __align__(256) unsigned char g_decode_scratch[kStaticBytes];
 // address a kernel may dereference; the real device address is looked up once
 // per device and remembered here.
 constexpr int kMaxDevices = 64;
-static void* g_scratch_address[kMaxDevices] = {};
+// (atomic: two host threads may make their first call on a device at the same time; both
+// resolve the same address)
+static std::atomic<void*> g_scratch_address[kMaxDevices] = {};
 static thread_local char g_static_error[256] = "";
 
 int fail_static(int code, const char* message) {
@@ -397,7 +400,8 @@ extern "C" int sfl_decode_static(const void* q, const void* k, const void* v, co
   cudaError_t err = cudaGetDevice(&device);
   if (err != cudaSuccess || device < 0 || device >= kMaxDevices)
     return fail_static(-11, "sfl_decode_static: cannot identify the current device");
-  if (g_scratch_address[device] == nullptr) {
+  void* resolved = g_scratch_address[device].load(std::memory_order_acquire);
+  if (resolved == nullptr) {
     // First call on this device: resolve the array's device address.  This is a
     // runtime query, not an allocation, but it may not be issued while a stream
     // is capturing, so make the first call before any capture.
@@ -405,10 +409,11 @@ extern "C" int sfl_decode_static(const void* q, const void* k, const void* v, co
     err = cudaGetSymbolAddress(&address, g_decode_scratch);
     if (err != cudaSuccess || address == nullptr)
       return fail_static(-12, "sfl_decode_static: cudaGetSymbolAddress failed");
-    g_scratch_address[device] = address;
+    g_scratch_address[device].store(address, std::memory_order_release);
+    resolved = address;
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  float* base = static_cast<float*>(g_scratch_address[device]);
+  float* base = static_cast<float*>(resolved);
   float* part_m = base;
   float* part_l = base + kStaticSlots;
   float* part_u = base + 2 * kStaticSlots;
