@@ -74,7 +74,8 @@ Saved carve_saved(const Dims& s, void* base) {
 
 // Temporaries of the backward pass.
 struct Scratch {
-  uint8_t *dres_bf16, *d13, *dh2, *dres2, *dres2_bf16, *d_attn, *dqkv, *delta, *dh1, *partial;
+  uint8_t *dres_bf16, *d13, *dh2, *dres2, *dres2_bf16, *d_attn, *dqkv, *delta, *dh1, *partial,
+      *partial1;
   long bytes;
 };
 
@@ -97,6 +98,7 @@ Scratch carve_scratch(const Dims& s, void* base) {
   v.delta = take(static_cast<long>(s.B) * s.H * s.T * 4);
   v.dh1 = take(s.M * s.d * 2);
   v.partial = take(static_cast<long>(sfl_rmsnorm_bwd_blocks(static_cast<int>(s.M))) * s.d * 4);
+  v.partial1 = take(static_cast<long>(sfl_rmsnorm_bwd_blocks(static_cast<int>(s.M))) * s.d * 4);
   v.bytes = off;
   return v;
 }
@@ -241,7 +243,9 @@ extern "C" int sfl_block_backward(const SflBlockArgs* a, void* stream) {
   const int M = static_cast<int>(s.M);
   const int d = static_cast<int>(s.d), aw = static_cast<int>(s.aw), dff = static_cast<int>(s.dff);
   const int blocks = sfl_rmsnorm_bwd_blocks(M);
+  // weight-gradient partials of the two norms; both are folded by one launch at the end
   float* partial = reinterpret_cast<float*>(t.partial);
+  float* partial1 = reinterpret_cast<float*>(t.partial1);
 
   const void* dres_bf16 = a->d_out_bf16;
   if (dres_bf16 == nullptr) {
@@ -266,7 +270,6 @@ extern "C" int sfl_block_backward(const SflBlockArgs* a, void* stream) {
   SFL_TRY(sfl_rmsnorm_bwd(t.dh2, reinterpret_cast<const float*>(v.x_mid), a->norm2,
                           reinterpret_cast<const float*>(v.rstd2), a->d_out,
                           reinterpret_cast<float*>(t.dres2), t.dres2_bf16, partial, M, d, stream));
-  SFL_TRY(sfl_rmsnorm_dw_reduce(partial, blocks, a->g_norm2, d, a->acc_norm2, stream));
 
   // ---- attention half
   plain = epilogue(kBf16, t.d_attn, s.aw, a->status);
@@ -302,8 +305,9 @@ extern "C" int sfl_block_backward(const SflBlockArgs* a, void* stream) {
   SFL_TRY(sfl_gemm_wgrad_grouped(w, 4, a->status, stream));
 
   SFL_TRY(sfl_rmsnorm_bwd(t.dh1, a->x, a->norm1, reinterpret_cast<const float*>(v.rstd1),
-                          reinterpret_cast<const float*>(t.dres2), a->dx, a->dx_bf16, partial, M,
+                          reinterpret_cast<const float*>(t.dres2), a->dx, a->dx_bf16, partial1, M,
                           d, stream));
-  SFL_TRY(sfl_rmsnorm_dw_reduce(partial, blocks, a->g_norm1, d, a->acc_norm1, stream));
+  SFL_TRY(sfl_rmsnorm_dw_reduce2(partial, a->g_norm2, a->acc_norm2, partial1, a->g_norm1,
+                                 a->acc_norm1, blocks, d, stream));
   return 0;
 }

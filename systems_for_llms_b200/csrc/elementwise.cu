@@ -354,11 +354,19 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const float* __restrict
 // fold is three round trips to L2), then one warp adds the 32 sums in a fixed order,
 // so the result does not depend on scheduling.
 constexpr int kDwReduceWarps = 32;
+// blockIdx.y selects one of up to two folds done by the same launch (the two norms of a
+// transformer block).
 __global__ void __launch_bounds__(32 * kDwReduceWarps)
 rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, int blocks, float* __restrict__ dw,
-                         int dim, int accumulate) {
+                         int dim, int accumulate, const float* __restrict__ partial_b,
+                         float* __restrict__ dw_b, int accumulate_b) {
   pdl_launch_dependents();
   pdl_wait();
+  if (blockIdx.y == 1) {
+    partial = partial_b;
+    dw = dw_b;
+    accumulate = accumulate_b;
+  }
   __shared__ float part[kDwReduceWarps][32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int i = blockIdx.x * 32 + lane;
@@ -824,7 +832,18 @@ extern "C" int sfl_rmsnorm_bwd(const void* dy, const float* x, const float* w, c
 extern "C" int sfl_rmsnorm_dw_reduce(const float* partial, int blocks, float* dw, int dim,
                                      int accumulate, void* stream) {
   return launch_pdl(rmsnorm_dw_reduce_kernel, dim3((dim + 31) / 32), dim3(32 * kDwReduceWarps), 0,
-                    SFL_STREAM(stream), partial, blocks, dw, dim, accumulate);
+                    SFL_STREAM(stream), partial, blocks, dw, dim, accumulate,
+                    static_cast<const float*>(nullptr), static_cast<float*>(nullptr), 0);
+}
+
+// Two folds of the same shape in one launch.
+extern "C" int sfl_rmsnorm_dw_reduce2(const float* partial_a, float* dw_a, int accumulate_a,
+                                      const float* partial_b, float* dw_b, int accumulate_b,
+                                      int blocks, int dim, void* stream) {
+  if (partial_a == nullptr || partial_b == nullptr || dw_a == nullptr || dw_b == nullptr) return -2;
+  return launch_pdl(rmsnorm_dw_reduce_kernel, dim3((dim + 31) / 32, 2), dim3(32 * kDwReduceWarps),
+                    0, SFL_STREAM(stream), partial_a, blocks, dw_a, dim, accumulate_a, partial_b,
+                    dw_b, accumulate_b);
 }
 
 extern "C" int sfl_cross_entropy(const void* logits, long ld, const int64_t* targets,

@@ -86,6 +86,10 @@ int sfl_rmsnorm_bwd(const void* dy_bf16, const float* x, const float* w, const f
                     int rows, int dim, void* stream);
 int sfl_rmsnorm_dw_reduce(const float* dw_partial, int blocks, float* dw, int dim, int accumulate,
                           void* stream);
+/* The same for two partial buffers of the same shape in one launch. */
+int sfl_rmsnorm_dw_reduce2(const float* partial_a, float* dw_a, int accumulate_a,
+                           const float* partial_b, float* dw_b, int accumulate_b, int blocks,
+                           int dim, void* stream);
 
 /* --------------------------------------------------------- cross entropy -- */
 /* logits bf16 [rows, vocab] (pitch ld).  Writes per-row loss (fp32) and, when

@@ -103,7 +103,7 @@ def register_signature(name: str, argtypes: list) -> None:
 
 
 # Kernels launched per call of each entry point (default 1, 0 for host-only calls).
-_KERNELS_PER_CALL = {"sfl_attn_bwd": 2, "sfl_embedding_bwd": 2, "sfl_block_forward": 7, "sfl_block_backward": 12,
+_KERNELS_PER_CALL = {"sfl_attn_bwd": 2, "sfl_embedding_bwd": 2, "sfl_block_forward": 7, "sfl_block_backward": 11,
                      "sfl_block_saved_bytes": 0, "sfl_block_scratch_bytes": 0, "sfl_rmsnorm_bwd_blocks": 0, "sfl_sqnorm_blocks": 0,
                      "sfl_ipc_alloc": 0, "sfl_ipc_free": 0, "sfl_ipc_get_handle": 0,
                      "sfl_ipc_open_handle": 0, "sfl_ipc_close_handle": 0,
