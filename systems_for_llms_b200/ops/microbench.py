@@ -7,6 +7,7 @@
     python -m systems_for_llms_b200.ops.microbench step        # per-kernel table of one step
     python -m systems_for_llms_b200.ops.microbench once NAME   # a few launches of one op
     python -m systems_for_llms_b200.ops.microbench mma         # tcgen05.mma issue-rate test
+    python -m systems_for_llms_b200.ops.microbench sfu         # exponentials per tile: ex2 forms, polynomials
     SFL_LIBRARY=/tmp/libsfl_trace.so python -m systems_for_llms_b200.ops.microbench \
         attention-phases                                       # phase timers, needs a library built with
                                                                # ops.build -DSFL_ATTN_TRACE --output /tmp/libsfl_trace.so
@@ -430,15 +431,15 @@ def collective_table(iters: int = 10) -> dict:
     return {"rank": rank, "world": world, "elements": n, "rows": rows}
 
 
-def mma_issue_rate() -> str:
-    """Compile ops/mma_issue_rate.cu for sm_100a into a temporary directory and run it."""
+def mma_issue_rate(name: str = "mma_issue_rate") -> str:
+    """Compile ops/<name>.cu for sm_100a into a temporary directory and run it."""
     import subprocess
     import tempfile
 
     from . import build as builder
-    source = Path(__file__).with_name("mma_issue_rate.cu")
+    source = Path(__file__).with_name(f"{name}.cu")
     with tempfile.TemporaryDirectory() as scratch:
-        binary = Path(scratch) / "mma_issue_rate"
+        binary = Path(scratch) / name
         subprocess.run(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17",
                         "--expt-relaxed-constexpr", "-I", str(builder.CSRC), "-o", str(binary),
                         str(source)], check=True)
@@ -519,7 +520,7 @@ def attention_phases(batch: int = 8, heads: int = 16, length: int = 4096, dim: i
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__,
                                      formatter_class=argparse.RawDescriptionHelpFormatter)
-    parser.add_argument("what", choices=[*SUITES, "step", "once", "mma", "tp", "comm",
+    parser.add_argument("what", choices=[*SUITES, "step", "once", "mma", "sfu", "tp", "comm",
                                          "attention-phases"])
     parser.add_argument("name", nargs="?", help="operation for 'once' (e.g. w13_swiglu, attn_bwd)")
     parser.add_argument("--repeat", type=int, default=3)
@@ -529,6 +530,9 @@ def main() -> None:
         raise SystemExit("a CUDA GPU is required")
     if args.what == "mma":
         print(mma_issue_rate(), end="")
+        return
+    if args.what == "sfu":
+        print(mma_issue_rate("sfu_rate"), end="")
         return
     if args.what == "attention-phases":
         print(attention_phases(), end="")
