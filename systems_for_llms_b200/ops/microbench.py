@@ -514,6 +514,11 @@ def attention_phases(batch: int = 8, heads: int = 16, length: int = 4096, dim: i
             lines.append(f"  {kernel}, MMA warp, per 64-column half: wait P / dS {t[9] / halves:.0f}, issue "
                          f"accumulation {t[10] / halves:.0f}, wait tile + issue scores {t[8] / halves:.0f} "
                          f"cycles; SM clock {t[13] / max(t[15], 1):.2f} GHz")
+            if t[7] or t[11] or t[14]:      # library also built with -DSFL_ATTN_TRACE_SERIAL
+                lines.append(f"  {kernel}, MMA warp waiting for each batch it issued: a score batch takes "
+                             f"{t[7] / halves:.0f} cycles to issue into the idle pipe and completes "
+                             f"{t[11] / halves:.0f} later; an accumulation batch completes "
+                             f"{t[14] / halves:.0f} after its issue")
     return "\n".join(lines) + "\n"
 
 
