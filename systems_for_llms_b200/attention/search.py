@@ -31,7 +31,7 @@ from __future__ import annotations
 import json
 import math
 import random
-from dataclasses import asdict, dataclass, fields, replace
+from dataclasses import asdict, dataclass, fields
 from typing import Callable, Iterable
 
 IMPLEMENTATIONS = ("csr", "interval")
